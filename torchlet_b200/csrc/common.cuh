@@ -1,0 +1,71 @@
+// Shared helpers of the hand-written sm_100a kernels.
+//
+// Every launcher is an extern "C" function that takes raw device pointers, sizes
+// and a CUDA stream, launches on that stream and returns the cudaError_t of the
+// launch as an int (0 = success).  Element types are passed as codes:
+//   0 = float32, 1 = bfloat16.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define TL_DTYPE_F32 0
+#define TL_DTYPE_BF16 1
+
+// Returned by launchers for arguments a kernel refuses (never a wrong result).
+#define TL_ERR_UNSUPPORTED 10001
+
+#define TL_LAUNCH_CHECK() ((int)cudaGetLastError())
+
+namespace tl {
+
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_float(float v);
+template <> __device__ __forceinline__ float from_float<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float v) {
+  return __float2bfloat16_rn(v);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of NT threads (NT a multiple of 32, at most 1024); every thread
+// gets the result.  The order of additions depends only on NT.
+template <int NT> __device__ __forceinline__ float block_sum(float v, float* scratch /*[32]*/) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  float t = (lane < NT / 32) ? scratch[lane] : 0.f;
+  return warp_sum(t);
+}
+
+// 8 consecutive elements as floats (pointer 16- or 32-byte aligned by construction).
+__device__ __forceinline__ void load8(const float* p, float (&out)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p);
+  const float4 b = *reinterpret_cast<const float4*>(p + 4);
+  out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+  out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+}
+__device__ __forceinline__ void load8(const __nv_bfloat16* p, float (&out)[8]) {
+  const uint4 raw = *reinterpret_cast<const uint4*>(p);
+  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    out[2 * i] = __uint_as_float(w[i] << 16);
+    out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+}  // namespace tl

@@ -1,0 +1,164 @@
+// Row-wise and element-wise kernels: embedding gather, RMSNorm, rotary position
+// encoding fused with the write of keys and values into cache pages, SwiGLU.
+// All arithmetic is float32; T is the storage type of activations and weights.
+//
+// Reference counterparts (Triton): v10_triton_paged_gqa/kernel/rms_norm.py:6-22,
+// kernel/rope.py:5-41, kernel/kvcache.py:5-50; nn.Embedding in model/qwen2_5.py:56;
+// F.silu(g) * u in v08_paged_gqa_py/layer/ffn_swiglu.py:15.
+#include "common.cuh"
+
+namespace {
+
+using namespace tl;
+
+// ---------------------------------------------------------------- embedding
+// acc[t, :] = float(table[ids[t], :]);  the residual stream starts in float32.
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ acc, int hidden, int vocab) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  const bool ok = id >= 0 && id < vocab;
+  const T* row = table + (size_t)(ok ? id : 0) * hidden;
+  float* out = acc + (size_t)t * hidden;
+  for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[j] = ok ? to_float(row[j]) : 0.f;
+}
+
+// ------------------------------------------------------------------ RMSNorm
+// out[r, :] = acc[row(r), :] * rsqrt(mean(acc[row(r), :]^2) + eps) * w
+// row(r) = rows ? rows[r] : r.  One block per row; the order of the additions
+// depends only on the width, never on which other rows are in the batch.
+template <typename T, int NT>
+__global__ void rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w,
+                                const int* __restrict__ rows, T* __restrict__ out, int hidden,
+                                float eps) {
+  __shared__ float scratch[32];
+  const int r = blockIdx.x;
+  const float* x = acc + (size_t)(rows ? rows[r] : r) * hidden;
+  float ss = 0.f;
+  for (int j = threadIdx.x; j < hidden; j += NT) {
+    const float v = x[j];
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum<NT>(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  T* o = out + (size_t)r * hidden;
+  for (int j = threadIdx.x; j < hidden; j += NT) o[j] = from_float<T>(x[j] * inv * w[j]);
+}
+
+// ------------------------------------------------- rotary + cache page write
+// qkv: [T, (nh + 2 nkv) d] rows of q heads, k heads, v heads.  For token t at
+// position p (angle_i = float(p) * inv_freq[i], split-half pairing i <-> i + d/2):
+//   q heads are rotated in place;
+//   k heads are rotated and written to the page of (request, p);
+//   v heads are copied to the page.
+// Page layout of one cache layer: [page][2 (k, v)][kv head][slot in page][d].
+template <typename T>
+__global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
+                               const int* __restrict__ token_req,
+                               const int* __restrict__ block_table, int table_width,
+                               T* __restrict__ pages, const float* __restrict__ inv_freq, int nh,
+                               int nkv, int d, int page_size, int write_kv) {
+  const int t = blockIdx.x;
+  const int h = blockIdx.y;
+  const int half = d >> 1;
+  const int pos = positions[t];
+  T* row = qkv + (size_t)t * (nh + 2 * nkv) * d + (size_t)h * d;
+  T* dst = row;
+  const bool is_v = h >= nh + nkv;
+  if (h >= nh) {
+    if (!write_kv) return;
+    const int kvh = is_v ? h - nh - nkv : h - nh;
+    const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+    dst = pages + ((((size_t)page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + pos % page_size) * d;
+  }
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float x1 = to_float(row[i]);
+    const float x2 = to_float(row[i + half]);
+    if (is_v) {
+      dst[i] = row[i];
+      dst[i + half] = row[i + half];
+    } else {
+      const float angle = (float)pos * inv_freq[i];
+      float s, c;
+      sincosf(angle, &s, &c);
+      dst[i] = from_float<T>(x1 * c - x2 * s);
+      dst[i + half] = from_float<T>(x2 * c + x1 * s);
+    }
+  }
+}
+
+// ------------------------------------------------------------------- SwiGLU
+// out[t, j] = silu(gu[t, j]) * gu[t, I + j],  silu(a) = a * sigmoid(a)
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
+                              size_t total) {
+  const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total) return;
+  const size_t t = idx / inter;
+  const int j = (int)(idx - t * inter);
+  const float g = to_float(gu[t * 2 * inter + j]);
+  const float u = to_float(gu[t * 2 * inter + inter + j]);
+  out[idx] = from_float<T>(g / (1.f + expf(-g)) * u);
+}
+
+}  // namespace
+
+extern "C" {
+
+int tl_embed(const void* table, int dtype, const int* ids, float* acc, int tokens, int hidden,
+             int vocab, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int nt = hidden >= 1024 ? 256 : 128;
+  if (dtype == TL_DTYPE_F32)
+    embed_kernel<float><<<tokens, nt, 0, stream>>>((const float*)table, ids, acc, hidden, vocab);
+  else
+    embed_kernel<__nv_bfloat16><<<tokens, nt, 0, stream>>>((const __nv_bfloat16*)table, ids, acc, hidden, vocab);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_rms_norm(const float* acc, const float* weight, const int* rows, void* out, int out_dtype,
+                int num_rows, int hidden, float eps, cudaStream_t stream) {
+  if (num_rows <= 0) return 0;
+  if (out_dtype == TL_DTYPE_F32)
+    rms_norm_kernel<float, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (float*)out, hidden, eps);
+  else
+    rms_norm_kernel<__nv_bfloat16, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_rope_kv(void* qkv, int dtype, const int* positions, const int* token_req,
+               const int* block_table, int table_width, void* pages, const float* inv_freq,
+               int tokens, int nh, int nkv, int d, int page_size, int write_kv,
+               cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (d % 2) return TL_ERR_UNSUPPORTED;
+  const int heads = write_kv ? nh + 2 * nkv : nh;
+  if (heads > 65535) return TL_ERR_UNSUPPORTED;
+  int nt = ((d / 2 + 31) / 32) * 32;
+  if (nt > 128) nt = 128;
+  dim3 grid(tokens, heads);
+  if (dtype == TL_DTYPE_F32)
+    rope_kv_kernel<float><<<grid, nt, 0, stream>>>((float*)qkv, positions, token_req, block_table,
+                                                   table_width, (float*)pages, inv_freq, nh, nkv, d,
+                                                   page_size, write_kv);
+  else
+    rope_kv_kernel<__nv_bfloat16><<<grid, nt, 0, stream>>>(
+        (__nv_bfloat16*)qkv, positions, token_req, block_table, table_width, (__nv_bfloat16*)pages,
+        inv_freq, nh, nkv, d, page_size, write_kv);
+  return TL_LAUNCH_CHECK();
+}
+
+int tl_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter,
+              cudaStream_t stream) {
+  const size_t total = (size_t)tokens * inter;
+  if (total == 0) return 0;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (dtype == TL_DTYPE_F32)
+    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+  else
+    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+  return TL_LAUNCH_CHECK();
+}
+
+}  // extern "C"

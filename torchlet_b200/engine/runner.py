@@ -1,0 +1,236 @@
+"""The step function: one batch of (request, its next tokens) through the model.
+
+A step runs only the tokens it is given — portions of prompts beside single decoded
+tokens, cut anywhere — as one ragged batch against the cache that earlier steps left,
+and returns float32 logits at the wanted places.  The ragged layout (flat tokens plus
+``req_indptr``) is the reference's (v10_triton_paged_gqa/scheduler.py:182-223); unlike
+the reference, which runs whole prompts and single decode tokens as two separate
+forwards (v10_triton_paged_gqa/engine.py:105-133), every entry here has a cached
+length before it (``kv_before``) and any number of new tokens.
+
+Per step the host builds ONE int32 block (tokens, positions, token->request map,
+request offsets, cached lengths, slots, logit rows, one block table per cache group) in
+pinned memory and copies it to the device once.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Hashable, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheError
+from ..cache.storage import CacheStorage
+from ..config.engine import EngineConfig
+from ..parts.model import LayeredModel
+
+TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
+
+
+class OutOfPages(CacheError):
+    """A step needs more pages than are free."""
+
+
+@dataclass
+class StepEntry:
+    request_id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()  # places among ``tokens`` whose logits are asked for
+
+
+class StepContext:
+    """Everything a part may read about the current step."""
+
+    def __init__(self, runner: "ModelRunner"):
+        self._runner = runner
+        self.dtype: torch.dtype = runner.dtype
+        self.device = runner.device
+        self.num_tokens = 0
+        self.num_requests = 0
+        self.max_q_len = 0
+        self.max_kv_len = 0
+        self.decode_only = False
+        # device int32 tensors
+        self.tokens = self.positions = self.token_req = None
+        self.req_indptr = self.kv_before = self.slots = self.logit_rows = None
+        # host copies (numpy int32) for parts that plan on the host
+        self.req_indptr_host = self.kv_before_host = self.slots_host = None
+
+    def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
+        return self._runner.buffer(name, shape, dtype)
+
+
+class ModelRunner:
+    def __init__(self, model: LayeredModel, config: EngineConfig):
+        if not torch.cuda.is_available():
+            raise RuntimeError("CUDA is required: the engine has no CPU path")
+        self.model = model
+        self.config = config.resolve(model.spec.max_position_embeddings)
+        self.device = torch.device(config.device)
+        self.dtype = TORCH_DTYPES[config.dtype]
+        if model.dtype != self.dtype:
+            raise ValueError(f"the model was loaded as {model.dtype}, the engine runs {self.dtype}")
+        self.vocab_size = model.spec.vocab_size
+        self.storage = CacheStorage(
+            model.cache_needs(), config.kv_block_size, config.max_decode_slots, config.max_num_blocks,
+            config.max_seq_len, self.device, self.dtype,
+        )
+        self.cache = self.storage.manager
+        self.num_groups = len(self.storage.groups)
+        self.token_capacity = max(config.max_num_batched_tokens, config.max_decode_slots)
+        self._buffers: dict[str, torch.Tensor] = {}
+        # two pinned staging blocks used in turn, each guarded by the event of its last copy
+        self._meta_host = [None, None]
+        self._meta_np = [None, None]
+        self._meta_event = [None, None]
+        self._meta_dev: Optional[torch.Tensor] = None
+        self._meta_turn = 0
+        self.steps_run = 0
+
+    # ------------------------------------------------------------- workspace
+    def buffer(self, name: str, shape: tuple, dtype: torch.dtype, exact: bool = False) -> torch.Tensor:
+        """A persistent scratch tensor; the first dimension is rows of the step.  It is
+        sized for the token budget at once (``exact``: for the rows asked) so that its
+        address stays the same from step to step."""
+        rows, rest = shape[0], tuple(shape[1:])
+        key = f"{name}|{rest}|{dtype}"
+        flat = self._buffers.get(key)
+        if flat is None or flat.shape[0] < rows:
+            capacity = rows if exact else max(rows, self.token_capacity)
+            flat = torch.empty((capacity, *rest), device=self.device, dtype=dtype)
+            self._buffers[key] = flat
+        return flat[:rows]
+
+    def _meta(self, words: int):
+        """A pinned host block and the device block of one step's int32 metadata."""
+        turn = self._meta_turn = self._meta_turn ^ 1
+        if self._meta_event[turn] is not None:
+            self._meta_event[turn].synchronize()  # its last copy has left the host block
+        if self._meta_host[turn] is None or self._meta_host[turn].numel() < words:
+            size = max(words, 1 << 14)
+            self._meta_host[turn] = torch.empty(size, dtype=torch.int32, pin_memory=True)
+            self._meta_np[turn] = self._meta_host[turn].numpy()
+        if self._meta_dev is None or self._meta_dev.numel() < words:
+            self._meta_dev = torch.empty(max(words, 1 << 14), dtype=torch.int32, device=self.device)
+        return self._meta_np[turn], self._meta_dev
+
+    def _upload_meta(self, words: int) -> None:
+        turn = self._meta_turn
+        self._meta_dev[:words].copy_(self._meta_host[turn][:words], non_blocking=True)
+        if self._meta_event[turn] is None:
+            self._meta_event[turn] = torch.cuda.Event()
+        self._meta_event[turn].record()
+
+    # -------------------------------------------------------------- requests
+    def admit(self, request_id: Hashable) -> int:
+        slot = self.cache.admit(request_id)
+        if self.storage.states:
+            self.storage.clear_slot(slot)
+        return slot
+
+    def finish(self, request_id: Hashable) -> None:
+        self.cache.finish(request_id)
+
+    def reserve(self, request_id: Hashable, new_len: int) -> bool:
+        """Pages for the request's tokens up to ``new_len``; False when a pool is short."""
+        return self.cache.extend(request_id, new_len)
+
+    # ------------------------------------------------------------------ step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries as one batch.  Returns float32 logits ``[wanted, vocab]`` in
+        the order of the entries and of their ``want`` (None if nothing is wanted).
+        The tensor is reused by the next step."""
+        entries = [e for e in entries if len(e.tokens) > 0]
+        if not entries:
+            return None
+        ctx, caches = self._build(entries)
+        with torch.no_grad():
+            acc = self.model.forward(ctx, caches)
+            logits = None
+            wanted = ctx.logit_rows.numel() if ctx.logit_rows is not None else 0
+            if wanted:
+                logits = self.buffer("logits", (wanted, self.vocab_size), torch.float32, exact=True)
+                self.model.logits(ctx, acc, ctx.logit_rows, logits)
+        for e in entries:
+            self.cache.advance(e.request_id, self.cache.num_tokens(e.request_id) + len(e.tokens))
+        self.steps_run += 1
+        return logits
+
+    def _build(self, entries):
+        cache = self.cache
+        n = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        T = sum(lens)
+        if T > self.token_capacity:
+            raise ValueError(f"a step of {T} tokens exceeds the token budget {self.token_capacity}")
+        kv_before = [cache.num_tokens(e.request_id) for e in entries]
+        seen = set()
+        for e, before, q in zip(entries, kv_before, lens):
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} appears twice in one step")
+            seen.add(e.request_id)
+            if not cache.extend(e.request_id, before + q):
+                raise OutOfPages(f"no pages left for request {e.request_id!r} ({before} + {q} tokens)")
+        want_rows = []
+        offset = 0
+        for e, q in zip(entries, lens):
+            for w in e.want:
+                if not 0 <= w < q:
+                    raise ValueError(f"wanted place {w} is outside the {q} tokens of request {e.request_id!r}")
+                want_rows.append(offset + w)
+            offset += q
+        m = len(want_rows)
+        width = max(1, max(-(-(b + q) // cache.page_size) for b, q in zip(kv_before, lens)))
+        G = self.num_groups
+        words = 3 * T + (n + 1) + 2 * n + m + G * n * width
+        host, dev = self._meta(words)
+        o = 0
+
+        def take(count):
+            nonlocal o
+            view = (host[o:o + count], dev[o:o + count])
+            o += count
+            return view
+
+        tok_h, tok_d = take(T)
+        pos_h, pos_d = take(T)
+        req_h, req_d = take(T)
+        ind_h, ind_d = take(n + 1)
+        kvb_h, kvb_d = take(n)
+        slot_h, slot_d = take(n)
+        row_h, row_d = take(m)
+        tables = [take(n * width) for _ in range(G)]
+
+        ind_h[0] = 0
+        np.cumsum(lens, out=ind_h[1:])
+        kvb_h[:] = kv_before
+        start = 0
+        vocab = self.vocab_size
+        for i, (e, before, q) in enumerate(zip(entries, kv_before, lens)):
+            tok_h[start:start + q] = e.tokens
+            pos_h[start:start + q] = np.arange(before, before + q, dtype=np.int32)
+            req_h[start:start + q] = i
+            slot_h[i] = cache.slot_of(e.request_id)
+            for g in range(G):
+                table = cache.table(e.request_id, g)
+                row = tables[g][0][i * width:(i + 1) * width]
+                row[:len(table)] = table[:width]
+                row[len(table):] = 0
+            start += q
+        if T and (tok_h[:T].min() < 0 or tok_h[:T].max() >= vocab):
+            raise ValueError(f"token ids must lie in [0, {vocab})")
+        row_h[:] = want_rows
+        self._upload_meta(words)
+
+        ctx = StepContext(self)
+        ctx.num_tokens, ctx.num_requests = T, n
+        ctx.max_q_len = max(lens)
+        ctx.max_kv_len = max(b + q for b, q in zip(kv_before, lens))
+        ctx.decode_only = ctx.max_q_len == 1
+        ctx.tokens, ctx.positions, ctx.token_req = tok_d, pos_d, req_d
+        ctx.req_indptr, ctx.kv_before, ctx.slots = ind_d, kvb_d, slot_d
+        ctx.logit_rows = row_d if m else None
+        ctx.req_indptr_host, ctx.kv_before_host, ctx.slots_host = ind_h.copy(), kvb_h.copy(), slot_h.copy()
+        block_tables = [t[1].view(n, width) for t in tables]
+        return ctx, self.storage.layer_caches(block_tables)

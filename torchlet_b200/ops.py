@@ -1,0 +1,178 @@
+"""Python entry to the hand-written CUDA kernels.
+
+Every function takes torch CUDA tensors (as containers only), hands raw pointers to
+an ``extern "C"`` launcher on torch's current stream, and raises on any error.  There
+is no CPU path and no library fallback: a tensor that is not on a CUDA device, a size
+a kernel refuses, or a missing library is an error here.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .csrc.build import load_library
+
+F32, BF16 = 0, 1
+_UNSUPPORTED = 10001
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, not {dtype}")
+
+
+_SIGNATURES = {
+    "elementwise": {
+        "tl_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "tl_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "tl_rope_kv": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    },
+    "gemm_simt": {
+        "tl_gemm_simt": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                         c_int, c_int, c_int, c_void_p],
+    },
+    "attention_generic": {
+        "tl_attention_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    },
+    "sampling": {
+        "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+    },
+}
+
+_functions: dict[str, ctypes._CFuncPtr] = {}
+
+
+def _fn(library: str, name: str):
+    fn = _functions.get(name)
+    if fn is None:
+        lib = load_library(library)
+        fn = getattr(lib, name)
+        fn.argtypes = _SIGNATURES[library][name]
+        fn.restype = c_int
+        _functions[name] = fn
+    return fn
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == _UNSUPPORTED:
+        raise KernelError(f"{what}: sizes or types not supported by this kernel")
+    raise KernelError(f"{what}: CUDA error {code} at launch")
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ptr(t) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+def _need_cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("kernels run on CUDA tensors only; there is no CPU path")
+
+
+# ------------------------------------------------------------------ wrappers
+def embed(table: torch.Tensor, ids: torch.Tensor, acc: torch.Tensor) -> None:
+    """acc[t] = float32(table[ids[t]]);  ids int32 [T], acc float32 [T, hidden]."""
+    _need_cuda(table, ids, acc)
+    tokens, hidden = acc.shape
+    assert ids.dtype == torch.int32 and acc.dtype == torch.float32 and acc.is_contiguous()
+    assert table.is_contiguous() and table.shape[1] == hidden
+    code = _fn("elementwise", "tl_embed")(
+        table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), acc.data_ptr(), tokens, hidden,
+        table.shape[0], _stream())
+    _check(code, "embed")
+
+
+def rms_norm(acc: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, rows=None) -> None:
+    """out[r] = rmsnorm(acc[rows[r] or r]) * weight;  acc float32, weight float32."""
+    _need_cuda(acc, weight, out, rows)
+    hidden = acc.shape[1]
+    num_rows = out.shape[0]
+    assert acc.dtype == torch.float32 and weight.dtype == torch.float32
+    assert acc.is_contiguous() and out.is_contiguous() and out.shape[1] == hidden
+    assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= num_rows)
+    code = _fn("elementwise", "tl_rms_norm")(
+        acc.data_ptr(), weight.data_ptr(), _ptr(rows), out.data_ptr(), dtype_code(out.dtype), num_rows,
+        hidden, float(eps), _stream())
+    _check(code, "rms_norm")
+
+
+def rope_kv(qkv, positions, token_req, block_table, pages, inv_freq, nh, nkv, d, page_size, write_kv=True):
+    """Rotate q (in place) and k by position, write k and v into cache pages."""
+    _need_cuda(qkv, positions, token_req, block_table, pages, inv_freq)
+    tokens = qkv.shape[0]
+    assert qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * d
+    assert pages.dtype == qkv.dtype and inv_freq.dtype == torch.float32 and inv_freq.numel() == d // 2
+    code = _fn("elementwise", "tl_rope_kv")(
+        qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), token_req.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], pages.data_ptr(), inv_freq.data_ptr(), tokens, nh, nkv,
+        d, page_size, 1 if write_kv else 0, _stream())
+    _check(code, "rope_kv")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out = silu(gate_up[:, :I]) * gate_up[:, I:]."""
+    _need_cuda(gate_up, out)
+    tokens, inter = out.shape
+    assert gate_up.shape == (tokens, 2 * inter) and gate_up.is_contiguous() and out.is_contiguous()
+    assert gate_up.dtype == out.dtype
+    code = _fn("elementwise", "tl_swiglu")(
+        gate_up.data_ptr(), out.data_ptr(), dtype_code(out.dtype), tokens, inter, _stream())
+    _check(code, "swiglu")
+
+
+def gemm_simt(x, w, out, bias=None, accumulate=False) -> None:
+    """out (+)= x @ w.T + bias on CUDA cores, float32 accumulation in ascending k."""
+    _need_cuda(x, w, out, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.shape == (M, N) and x.dtype == w.dtype
+    assert x.stride(1) == 1 and w.stride(1) == 1 and out.stride(1) == 1
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
+    assert not accumulate or out.dtype == torch.float32
+    code = _fn("gemm_simt", "tl_gemm_simt")(
+        x.data_ptr(), w.data_ptr(), dtype_code(x.dtype), _ptr(bias), out.data_ptr(), dtype_code(out.dtype),
+        1 if accumulate else 0, M, N, K, x.stride(0), w.stride(0), out.stride(0), _stream())
+    _check(code, "gemm_simt")
+
+
+def attention_generic(q, q_stride, pages, block_table, token_req, positions, out, tokens, nh, nkv, d,
+                      page_size, window, scale) -> None:
+    """Paged causal GQA attention, one warp per (token, head); q may be a view into qkv."""
+    _need_cuda(q, pages, block_table, token_req, positions, out)
+    assert q.dtype == pages.dtype == out.dtype and out.is_contiguous()
+    code = _fn("attention_generic", "tl_attention_generic")(
+        q.data_ptr(), q_stride, pages.data_ptr(), dtype_code(q.dtype), block_table.data_ptr(),
+        block_table.shape[1], token_req.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
+        tokens, nh, nkv, d, page_size, int(window or 0), float(scale), _stream())
+    _check(code, "attention_generic")
+
+
+def sample(logits, out, temperature=None, seed=None, counter=None) -> None:
+    """out[r] = argmax(logits[r]) or a seeded draw from softmax(logits[r] / temperature[r])."""
+    _need_cuda(logits, out, temperature, seed, counter)
+    rows, vocab = logits.shape
+    assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+    if temperature is not None:
+        assert temperature.dtype == torch.float32 and seed.dtype == torch.int64 and counter.dtype == torch.int32
+    code = _fn("sampling", "tl_sample")(
+        logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _ptr(counter),
+        out.data_ptr(), _stream())
+    _check(code, "sample")

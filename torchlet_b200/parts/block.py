@@ -1,0 +1,18 @@
+"""Arrangements of a layer's parts around the residual stream.
+
+"pre_norm": h = x + mixer(norm(x)); x' = h + feed_forward(norm(h))
+(v10_triton_paged_gqa/layer/transformer_block.py:37-40).  The stream ``acc`` is
+float32; mixer and feed-forward add into it.
+"""
+from __future__ import annotations
+
+from .base import BLOCKS, Block
+
+
+@BLOCKS.register("pre_norm")
+class PreNormBlock(Block):
+    def forward(self, ctx, acc, cache) -> None:
+        x = self.mixer_norm.forward(ctx, acc)
+        self.mixer.forward(ctx, x, acc, cache)
+        x = self.feed_forward_norm.forward(ctx, acc)
+        self.feed_forward.forward(ctx, x, acc)
