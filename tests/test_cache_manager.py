@@ -1,0 +1,118 @@
+"""The cache manager alone, on the CPU: no page lost, held twice or freed twice, under
+random orders of requests; windows give pages back; slots."""
+import random
+
+import pytest
+
+from torchlet_b200.cache import CacheError, CacheManager, GroupSpec, PagePool
+
+
+def make(num_pages=12, page=4, slots=3, window=None, max_seq=64, two_groups=False):
+    groups = [GroupSpec(2, 16, None, (0, 1), num_pages)]
+    if two_groups or window:
+        groups.append(GroupSpec(2, 16, window, (2,), num_pages))
+    return CacheManager(groups, page, slots, max_seq)
+
+
+def test_pool_refuses_double_free_and_overdraw():
+    pool = PagePool(4)
+    pages = pool.take(3)
+    assert sorted(pages) == [1, 2, 3] and pool.num_free == 0
+    with pytest.raises(CacheError):
+        pool.take(1)
+    pool.give_back([pages[0]])
+    with pytest.raises(CacheError):
+        pool.give_back([pages[0]])
+    with pytest.raises(CacheError):
+        pool.give_back([7])
+    pool.give_back([0])  # the null page is never held; giving it back is a no-op
+    assert pool.num_free == 1
+
+
+def test_extend_is_all_or_nothing_and_pages_are_used_again():
+    m = make(num_pages=5, page=4)  # 4 usable pages
+    m.admit("a"); m.admit("b")
+    assert m.extend("a", 9)  # 3 pages
+    assert not m.can_extend("b", 8) and not m.extend("b", 8)
+    assert m.table("b", 0) == [] and m.pools[0].num_free == 1
+    assert m.extend("b", 4)
+    a_pages = list(m.table("a", 0))
+    m.advance("a", 9)
+    m.finish("a")
+    m.check()
+    m.admit("c")
+    assert m.extend("c", 12)
+    assert set(m.table("c", 0)) == set(a_pages)
+    m.check()
+    with pytest.raises(CacheError):
+        m.advance("b", 5)  # no page for token 5
+
+
+def test_window_group_gives_pages_back_when_passed():
+    m = make(num_pages=20, page=4, window=6)
+    m.admit("a")
+    assert m.extend("a", 10)
+    assert m.advance("a", 10) == 1  # next query at 10 sees keys >= 5: page 0 (0..3) is passed
+    assert m.table("a", 1)[0] == 0 and m.table("a", 1)[1] != 0
+    assert m.table("a", 0)[0] != 0  # the group without window keeps everything
+    m.extend("a", 11); assert m.advance("a", 11) == 0  # keys >= 6: page 1 (4..7) still needed
+    m.extend("a", 14); assert m.advance("a", 14) == 1  # keys >= 9: page 1 passed
+    m.check()
+    held_window = [p for p in m.table("a", 1) if p]
+    assert len(held_window) == 2
+    m.finish("a"); m.check()
+    assert m.pools[1].num_free == 19
+
+
+def test_slots():
+    m = make(slots=2)
+    s0, s1 = m.admit("a"), m.admit("b")
+    assert {s0, s1} == {0, 1} and m.num_free_slots == 0
+    with pytest.raises(CacheError):
+        m.admit("c")
+    with pytest.raises(CacheError):
+        m.admit("a")
+    assert m.finish("a") == s0
+    assert m.admit("c") == s0
+    m.check()
+
+
+def test_length_limit():
+    m = make(max_seq=16)
+    m.admit("a")
+    with pytest.raises(CacheError):
+        m.extend("a", 17)
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_random_orders_keep_the_invariants(seed):
+    rng = random.Random(seed)
+    m = make(num_pages=rng.choice([6, 9, 17]), page=rng.choice([2, 4, 8]), slots=4,
+             window=rng.choice([None, 5, 11]), max_seq=80)
+    live, counter = {}, 0
+    for _ in range(400):
+        action = rng.random()
+        if action < 0.25 and m.num_free_slots:
+            rid = f"r{counter}"; counter += 1
+            m.admit(rid); live[rid] = 0
+        elif action < 0.8 and live:
+            rid = rng.choice(list(live))
+            new_len = min(80, live[rid] + rng.choice([1, 1, 1, 2, 5, 13]))
+            if m.extend(rid, new_len):
+                m.advance(rid, new_len); live[rid] = new_len
+            else:
+                before = [list(m.table(rid, g)) for g in range(len(m.groups))]
+                assert before == [list(m.table(rid, g)) for g in range(len(m.groups))]
+        elif live:
+            rid = rng.choice(list(live))
+            m.finish(rid); del live[rid]
+        m.check()
+        for rid, length in live.items():
+            assert m.num_tokens(rid) == length
+            for g, group in enumerate(m.groups):
+                table = m.table(rid, g)
+                lo = 0 if group.window is None else max(0, length - group.window + 1)
+                for pos in range(lo, length):  # every position the next token can see has a page
+                    assert table[pos // m.page_size] != 0
+    m.reset(); m.check()
+    assert all(pool.num_free == pool.num_pages - 1 for pool in m.pools)

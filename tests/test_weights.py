@@ -1,0 +1,76 @@
+import json
+
+import pytest
+import torch
+
+import tiny_configs
+from torchlet_b200.config import Qwen2Config, load_config
+from torchlet_b200.parts import expected_tensors
+from torchlet_b200.weights import (WeightsError, check_and_normalise, load_checkpoint, random_tensors,
+                                   write_random_model)
+
+
+def _expected(cfg_dict):
+    return expected_tensors(Qwen2Config.from_dict(cfg_dict).model_spec())
+
+
+def test_expected_names_are_the_checkpoint_names():
+    for cfg, _ in tiny_configs.ALL.values():
+        names = {t.name: t.shape for t in _expected(cfg) if not t.optional}
+        assert names == {n: s for n, s, _ in tiny_configs.tensor_shapes(cfg)}
+
+
+def test_one_error_lists_missing_unexpected_and_wrong_shapes():
+    cfg, init = tiny_configs.ALL["B"]
+    weights = tiny_configs.make_weights(cfg, **init)
+    del weights["model.layers.1.mlp.up_proj.weight"]
+    del weights["lm_head.weight"]
+    weights["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(5, 5)
+    weights["model.layers.9.extra.weight"] = torch.zeros(2)
+    with pytest.raises(WeightsError) as info:
+        check_and_normalise(weights, _expected(cfg))
+    err = info.value
+    assert set(err.missing) == {"model.layers.1.mlp.up_proj.weight", "lm_head.weight"}
+    assert err.unexpected == ["model.layers.9.extra.weight"]
+    assert err.wrong_shape[0][0] == "model.layers.0.self_attn.q_proj.weight"
+    text = str(err)
+    for piece in ("missing", "unexpected", "wrong shape", "lm_head.weight", "(5, 5)", "(96, 96)"):
+        assert piece in text
+
+
+def test_tied_head_may_be_absent_and_dtypes_are_kept():
+    cfg, init = tiny_configs.ALL["A"]
+    weights = tiny_configs.make_weights(cfg, dtype=torch.bfloat16, **init)
+    weights["model.norm.weight"] = weights["model.norm.weight"].float()
+    weights["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.ones(8)  # ignored buffer
+    out = check_and_normalise(weights, _expected(cfg))
+    assert "lm_head.weight" not in out
+    assert out["model.embed_tokens.weight"].dtype == torch.bfloat16
+    assert out["model.norm.weight"].dtype == torch.float32
+
+
+def test_integer_tables_become_int32():
+    from torchlet_b200.parts import TensorSpec
+
+    out = check_and_normalise({"t": torch.arange(4, dtype=torch.int64)}, [TensorSpec("t", (4,))])
+    assert out["t"].dtype == torch.int32
+
+
+def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
+    cfg = Qwen2Config.from_dict(tiny_configs.TINY_B)
+    folder = write_random_model(tmp_path / "m", cfg, seed=9, std=0.03, norm_std=0.02)
+    assert load_config(folder) == Qwen2Config.from_dict(json.loads((folder / "config.json").read_text()))
+    tensors = load_checkpoint(folder, _expected(tiny_configs.TINY_B))
+    assert all(t.dtype == torch.bfloat16 for t in tensors.values())
+    again = random_tensors(cfg, seed=9, std=0.03, norm_std=0.02)
+    other = random_tensors(cfg, seed=10, std=0.03, norm_std=0.02)
+    name = "model.layers.2.mlp.down_proj.weight"
+    assert torch.equal(tensors[name], again[name]) and not torch.equal(tensors[name], other[name])
+    norm = tensors["model.norm.weight"].float()
+    assert abs(norm.mean() - 1) < 0.02 and 0.005 < norm.std() < 0.05
+    assert abs(tensors[name].float().std() - 0.03) < 0.003
+
+
+def test_missing_files(tmp_path):
+    with pytest.raises(FileNotFoundError):
+        load_checkpoint(tmp_path, [])

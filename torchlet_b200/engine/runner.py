@@ -24,6 +24,8 @@ from ..cache.manager import CacheError
 from ..cache.storage import CacheStorage
 from ..config.engine import EngineConfig
 from ..parts.model import LayeredModel
+from ..sampling import SampleSpec
+from .. import ops
 
 TORCH_DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32}
 
@@ -37,6 +39,13 @@ class StepEntry:
     request_id: Hashable
     tokens: Sequence[int]
     want: Sequence[int] = ()  # places among ``tokens`` whose logits are asked for
+    sample: Optional[SampleSpec] = None  # sample a token from the logits of the last token
+
+
+@dataclass
+class StepResult:
+    logits: Optional[torch.Tensor]  # float32 [wanted, vocab]: ``want`` rows, then sampled rows
+    tokens: Optional[torch.Tensor]  # int32 [sampled entries], in the order of the entries
 
 
 class StepContext:
@@ -56,6 +65,9 @@ class StepContext:
         self.req_indptr = self.kv_before = self.slots = self.logit_rows = None
         # host copies (numpy int32) for parts that plan on the host
         self.req_indptr_host = self.kv_before_host = self.slots_host = None
+        # sampling rows of the step (device), None when every sampled row is greedy
+        self.num_sampled = 0
+        self.sample_temperature = self.sample_seed = self.sample_counter = None
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         return self._runner.buffer(name, shape, dtype)
@@ -141,21 +153,34 @@ class ModelRunner:
         """Run the entries as one batch.  Returns float32 logits ``[wanted, vocab]`` in
         the order of the entries and of their ``want`` (None if nothing is wanted).
         The tensor is reused by the next step."""
+        return self.run(entries).logits
+
+    def run(self, entries: Sequence[StepEntry]) -> StepResult:
+        """Run the entries as one batch: logits at the wanted places and, for entries
+        with ``sample`` set, a token sampled from the logits of their last token.
+        Both tensors are reused by the next step."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
-            return None
+            return StepResult(None, None)
         ctx, caches = self._build(entries)
         with torch.no_grad():
             acc = self.model.forward(ctx, caches)
-            logits = None
+            logits = tokens = None
             wanted = ctx.logit_rows.numel() if ctx.logit_rows is not None else 0
             if wanted:
                 logits = self.buffer("logits", (wanted, self.vocab_size), torch.float32, exact=True)
                 self.model.logits(ctx, acc, ctx.logit_rows, logits)
+            if ctx.num_sampled:
+                tokens = self.buffer("sampled", (ctx.num_sampled,), torch.int32)
+                rows = logits[wanted - ctx.num_sampled:]
+                if ctx.sample_temperature is None:
+                    ops.sample(rows, tokens)
+                else:
+                    ops.sample(rows, tokens, ctx.sample_temperature, ctx.sample_seed, ctx.sample_counter)
         for e in entries:
             self.cache.advance(e.request_id, self.cache.num_tokens(e.request_id) + len(e.tokens))
         self.steps_run += 1
-        return logits
+        return StepResult(logits, tokens)
 
     def _build(self, entries):
         cache = self.cache
@@ -180,10 +205,19 @@ class ModelRunner:
                     raise ValueError(f"wanted place {w} is outside the {q} tokens of request {e.request_id!r}")
                 want_rows.append(offset + w)
             offset += q
+        sampled = []
+        offset = 0
+        for e, q in zip(entries, lens):
+            if e.sample is not None:
+                sampled.append(e.sample)
+                want_rows.append(offset + q - 1)
+            offset += q
+        k = len(sampled)
+        hot = any(s.temperature > 0 for s in sampled)
         m = len(want_rows)
         width = max(1, max(-(-(b + q) // cache.page_size) for b, q in zip(kv_before, lens)))
         G = self.num_groups
-        words = 3 * T + (n + 1) + 2 * n + m + G * n * width
+        words = 3 * T + (n + 1) + 2 * n + m + G * n * width + (4 * k + 2 if hot else 0)
         host, dev = self._meta(words)
         o = 0
 
@@ -221,6 +255,14 @@ class ModelRunner:
         if T and (tok_h[:T].min() < 0 or tok_h[:T].max() >= vocab):
             raise ValueError(f"token ids must lie in [0, {vocab})")
         row_h[:] = want_rows
+        if hot:
+            o += o & 1  # the 64-bit seeds start on an 8-byte boundary
+            seed_h, seed_d = take(2 * k)
+            temp_h, temp_d = take(k)
+            count_h, count_d = take(k)
+            seed_h.view(np.int64)[:] = [s.seed & 0x7FFFFFFFFFFFFFFF for s in sampled]
+            temp_h.view(np.float32)[:] = [s.temperature for s in sampled]
+            count_h[:] = [s.counter for s in sampled]
         self._upload_meta(words)
 
         ctx = StepContext(self)
@@ -231,6 +273,10 @@ class ModelRunner:
         ctx.tokens, ctx.positions, ctx.token_req = tok_d, pos_d, req_d
         ctx.req_indptr, ctx.kv_before, ctx.slots = ind_d, kvb_d, slot_d
         ctx.logit_rows = row_d if m else None
+        ctx.num_sampled = k
+        ctx.sample_temperature = temp_d.view(torch.float32) if hot else None
+        ctx.sample_seed = seed_d.view(torch.int64) if hot else None
+        ctx.sample_counter = count_d if hot else None
         ctx.req_indptr_host, ctx.kv_before_host, ctx.slots_host = ind_h.copy(), kvb_h.copy(), slot_h.copy()
         block_tables = [t[1].view(n, width) for t in tables]
         return ctx, self.storage.layer_caches(block_tables)
