@@ -1,0 +1,440 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:
+//     out[M, N] (+)= x[M, K] . w[N, K]^T (+ bias)          float32 accumulation in TMEM
+//
+// One CTA computes a 128 x BLOCK_Q tile.  Warp 0 streams 128-byte-swizzled K-major tiles
+// of both operands into a ring of shared-memory stages with TMA; one thread of warp 1
+// issues tcgen05.mma (UMMA 128 x BLOCK_Q x 16) from shared-memory descriptors into an
+// accumulator in tensor memory and commits each stage back to the producer; warps 2-5
+// read the accumulator with tcgen05.ld and run the epilogue.
+//
+// Two orientations share the kernel:
+//   normal  (many tokens):  the 128 rows of the tile are tokens, the BLOCK_Q columns are
+//           weight rows; the epilogue writes the output directly (bias, accumulate into
+//           the float32 residual stream, SwiGLU over interleaved gate/up columns, or
+//           float32 logits).
+//   swapped (few tokens, decode): the 128 rows are WEIGHT rows, so that a handful of
+//           tokens still fills the tensor core's M; the tokens are the BLOCK_Q columns.
+//           K is split over blockIdx.z so that about one CTA per SM streams weights;
+//           each split writes a float32 partial [split][M][N], and a second small
+//           kernel adds the partials in a fixed order and applies the same epilogues.
+//
+// Reference counterparts: cuBLAS through nn.Linear (v10_triton_paged_gqa/layer/gqa.py:
+// 122-124, 84; model/qwen2_5.py:83-87) and the Triton GEMMs swiglu_kernel/down_kernel
+// (v10_triton_paged_gqa/kernel/ffn_swiglu.py:5-164).
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+#include "tcgen05.cuh"
+
+namespace {
+
+using namespace tc;
+
+constexpr int BLOCK_P = 128;  // tile rows = UMMA M
+constexpr int BLOCK_K = 64;   // bf16 per 128-byte row
+constexpr int UMMA_K = 16;
+constexpr int ROW_TILE_BYTES = BLOCK_P * BLOCK_K * 2;
+constexpr int THREADS = 192;
+
+enum Epilogue { EPI_STORE_BF16 = 0, EPI_ACCUM_F32 = 1, EPI_SWIGLU_BF16 = 2, EPI_STORE_F32 = 3 };
+
+__device__ int g_error_word = 0;
+
+struct Params {
+  int rows;  // extent of the row operand: tokens (normal) or weight rows (swapped)
+  int cols;  // extent of the column operand
+  int k_blocks, k_blocks_per_split;
+  const float* bias;
+  void* out;
+  long long ldo;
+  int epilogue;
+  float* partial;  // swapped: [splits][M = cols][N = rows]
+};
+
+__device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
+
+// 32 accumulator values of output row m, columns n0 .. n0+31 (normal orientation).
+__device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, const float (&v)[32]) {
+  const int N = p.cols;
+  if (p.epilogue == EPI_SWIGLU_BF16) {
+    // columns n0..n0+15 are gate j..j+15, n0+16..n0+31 the matching up values
+    if (n0 + 32 > N) return;  // N is a multiple of 32 by construction of the interleave
+    __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * p.ldo + (n0 >> 1);
+    uint32_t packed[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float a = silu(v[2 * j]) * v[2 * j + 16];
+      const float b = silu(v[2 * j + 1]) * v[2 * j + 17];
+      __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+      packed[j] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    uint4* dst = reinterpret_cast<uint4*>(o);
+    dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+    return;
+  }
+#pragma unroll
+  for (int c = 0; c < 32; c += 8) {
+    const int n = n0 + c;
+    if (n >= N) return;
+    float r[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) r[j] = v[c + j] + ((p.bias && n + j < N) ? p.bias[n + j] : 0.f);
+    const bool full = n + 8 <= N;
+    if (p.epilogue == EPI_STORE_BF16) {
+      __nv_bfloat16* o = (__nv_bfloat16*)p.out + (size_t)m * p.ldo + n;
+      if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 h = __floats2bfloat162_rn(r[2 * j], r[2 * j + 1]);
+          packed[j] = *reinterpret_cast<uint32_t*>(&h);
+        }
+        *reinterpret_cast<uint4*>(o) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      } else {
+        for (int j = 0; j < 8 && n + j < N; ++j) o[j] = __float2bfloat16_rn(r[j]);
+      }
+    } else {
+      float* o = (float*)p.out + (size_t)m * p.ldo + n;
+      const bool accum = p.epilogue == EPI_ACCUM_F32;
+      if (full && ((reinterpret_cast<uintptr_t>(o) & 15) == 0)) {
+        float4* o4 = reinterpret_cast<float4*>(o);
+        float4 a = make_float4(r[0], r[1], r[2], r[3]), b = make_float4(r[4], r[5], r[6], r[7]);
+        if (accum) {
+          const float4 x = o4[0], y = o4[1];
+          a.x += x.x; a.y += x.y; a.z += x.z; a.w += x.w;
+          b.x += y.x; b.y += y.y; b.z += y.z; b.w += y.w;
+        }
+        o4[0] = a;
+        o4[1] = b;
+      } else {
+        for (int j = 0; j < 8 && n + j < N; ++j) o[j] = accum ? o[j] + r[j] : r[j];
+      }
+    }
+  }
+}
+
+template <int BLOCK_Q, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
+               const Params p) {
+  constexpr int COL_TILE_BYTES = BLOCK_Q * BLOCK_K * 2;
+  constexpr int STAGE_BYTES = ROW_TILE_BYTES + COL_TILE_BYTES;
+  constexpr int TMEM_COLS = BLOCK_Q < 32 ? 32 : BLOCK_Q;
+  constexpr uint32_t IDESC = idesc_bf16_f32(BLOCK_P, BLOCK_Q);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+  uint64_t* empty = full + STAGES;
+  uint64_t* tmem_full = empty + STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int row0 = blockIdx.x * BLOCK_P, col0 = blockIdx.y * BLOCK_Q;
+  const int kb_begin = blockIdx.z * p.k_blocks_per_split;
+  const int kb_end = min(p.k_blocks, kb_begin + p.k_blocks_per_split);
+  const int num_kb = kb_end - kb_begin;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    mbar_init(tmem_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&map_row);
+    prefetch_tensormap(&map_col);
+  }
+  if (warp == 1) {
+    tmem_alloc<TMEM_COLS>(tmem_slot);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int it = 0; it < num_kb; ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
+        mbar_expect_tx(&full[s], STAGE_BYTES);
+        uint8_t* stage = smem + s * STAGE_BYTES;
+        const int k = (kb_begin + it) * BLOCK_K;
+        tma_load_2d(stage, &map_row, &full[s], k, row0);
+        tma_load_2d(stage + ROW_TILE_BYTES, &map_col, &full[s], k, col0);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int it = 0; it < num_kb; ++it) {
+        const int s = it % STAGES;
+        const uint32_t phase = (it / STAGES) & 1;
+        mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
+        fence_after_sync();
+        const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES);
+        const uint64_t a_desc = smem_desc_sw128(a_addr);
+        const uint64_t b_desc = smem_desc_sw128(a_addr + ROW_TILE_BYTES);
+#pragma unroll
+        for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
+          // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
+          mma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, it > 0 || k > 0);
+        }
+        mma_commit(&empty[s]);
+      }
+      mma_commit(tmem_full);
+    }
+  } else {
+    mbar_wait(tmem_full, 0, abort_flag, &g_error_word, 3);
+    fence_after_sync();
+    const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
+    const int row = row0 + quarter * 32 + lane;
+    const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16);
+    constexpr int CHUNK = BLOCK_Q < 32 ? 16 : 32;
+#pragma unroll 1
+    for (int c = 0; c < BLOCK_Q; c += CHUNK) {
+      float v[32];
+      if constexpr (CHUNK == 32) {
+        uint32_t r[32];
+        tmem_ld_32(taddr + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+      } else {
+        uint32_t r[16];
+        tmem_ld_16(taddr + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+#pragma unroll
+        for (int j = 16; j < 32; ++j) v[j] = 0.f;
+      }
+      if (row >= p.rows || num_kb <= 0) continue;
+      if constexpr (SWAP) {
+        // row = weight row n, columns = tokens m; partial[split][m][n]
+        float* dst = p.partial + ((size_t)blockIdx.z * p.cols) * p.rows + row;
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) {
+          const int m = col0 + c + j;
+          if (m < p.cols) dst[(size_t)m * p.rows] = v[j];
+        }
+      } else {
+        epilogue_chunk(p, row, col0 + c, v);
+      }
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc<TMEM_COLS>(tmem_base);
+  }
+}
+
+// Adds the split partials [splits][M][N] in ascending split order and applies the epilogue.
+__global__ void splitk_finish_kernel(const float* __restrict__ partial, int splits, int M, int N,
+                                     const float* __restrict__ bias, int epilogue, void* out, long long ldo) {
+  const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)M * out_cols) return;
+  const int m = (int)(idx / out_cols), c = (int)(idx % out_cols);
+  const size_t plane = (size_t)M * N;
+  if (epilogue == EPI_SWIGLU_BF16) {
+    const int g = (c >> 4) * 32 + (c & 15);
+    float gate = 0.f, up = 0.f;
+    for (int s = 0; s < splits; ++s) {
+      gate += partial[s * plane + (size_t)m * N + g];
+      up += partial[s * plane + (size_t)m * N + g + 16];
+    }
+    ((__nv_bfloat16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(silu(gate) * up);
+    return;
+  }
+  float v = 0.f;
+  for (int s = 0; s < splits; ++s) v += partial[s * plane + (size_t)m * N + c];
+  if (bias) v += bias[c];
+  if (epilogue == EPI_STORE_BF16)
+    ((__nv_bfloat16*)out)[(size_t)m * ldo + c] = __float2bfloat16_rn(v);
+  else if (epilogue == EPI_ACCUM_F32)
+    ((float*)out)[(size_t)m * ldo + c] += v;
+  else
+    ((float*)out)[(size_t)m * ldo + c] = v;
+}
+
+// ------------------------------------------------------------------ host side
+struct MapKey {
+  const void* base;
+  uint64_t rows, cols, ld;
+  uint32_t box_rows;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && rows == o.rows && cols == o.cols && ld == o.ld && box_rows == o.box_rows;
+  }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    size_t h = reinterpret_cast<size_t>(k.base);
+    h = h * 1000003u ^ k.rows;
+    h = h * 1000003u ^ k.cols;
+    h = h * 1000003u ^ k.ld;
+    return h * 1000003u ^ k.box_rows;
+  }
+};
+
+bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint64_t cols, uint64_t ld, uint32_t box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex lock;
+  const MapKey key{base, rows, cols, ld, box_rows};
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap map;
+    if (!tc_host::make_map_bf16(&map, base, rows, cols, ld, box_rows)) return false;
+    if (cache.size() > 4096) cache.clear();
+    it = cache.emplace(key, map).first;
+  }
+  *out = it->second;
+  return true;
+}
+
+int sm_count() {
+  static int count = 0;
+  if (!count) {
+    int device = 0;
+    cudaGetDevice(&device);
+    cudaDeviceGetAttribute(&count, cudaDevAttrMultiProcessorCount, device);
+    if (count <= 0) count = 148;
+  }
+  return count;
+}
+
+constexpr int SWAP_MAX_TOKENS = 256;
+
+int pick_block_q_swapped(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+struct Plan {
+  bool swap;
+  int block_q, splits, k_blocks_per_split;
+};
+
+Plan make_plan(int M, int N, int K) {
+  Plan plan;
+  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  plan.swap = M <= SWAP_MAX_TOKENS;
+  if (plan.swap) {
+    plan.block_q = pick_block_q_swapped(M);
+    const int tiles = ((N + BLOCK_P - 1) / BLOCK_P) * ((M + plan.block_q - 1) / plan.block_q);
+    int splits = sm_count() / tiles;
+    if (splits < 1) splits = 1;
+    if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;  // at least 4 k-blocks a split
+    plan.k_blocks_per_split = (k_blocks + splits - 1) / splits;
+    plan.splits = (k_blocks + plan.k_blocks_per_split - 1) / plan.k_blocks_per_split;
+  } else {
+    const int row_tiles = (M + BLOCK_P - 1) / BLOCK_P;
+    plan.block_q = row_tiles * ((N + 255) / 256) >= sm_count() ? 256 : 128;
+    plan.splits = 1;
+    plan.k_blocks_per_split = k_blocks;
+  }
+  return plan;
+}
+
+template <int BLOCK_Q, int STAGES, bool SWAP>
+int launch(const CUtensorMap& map_row, const CUtensorMap& map_col, const Params& p, dim3 grid, cudaStream_t stream) {
+  constexpr int SMEM = STAGES * (ROW_TILE_BYTES + BLOCK_Q * BLOCK_K * 2) + 1024 + 256;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q, STAGES, SWAP>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  gemm_tc_kernel<BLOCK_Q, STAGES, SWAP><<<grid, THREADS, SMEM, stream>>>(map_row, map_col, p);
+  return TL_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+extern "C" {
+
+// How a product of these sizes would run: *swap (0/1), *splits; returns the bytes of
+// float32 workspace it needs (0 for the normal orientation).
+long long tl_gemm_tc_plan(int M, int N, int K, int* swap, int* splits) {
+  const Plan plan = make_plan(M, N, K);
+  if (swap) *swap = plan.swap ? 1 : 0;
+  if (splits) *splits = plan.splits;
+  return plan.swap ? (long long)plan.splits * M * N * 4 : 0;
+}
+
+// Reads and clears the error word that a bounded wait sets when it gives up.
+int tl_gemm_tc_error() {
+  int value = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&value, g_error_word, sizeof(int)) != cudaSuccess) return -1;
+  if (value) cudaMemcpyToSymbol(g_error_word, &zero, sizeof(int));
+  return value;
+}
+
+// out (+)= x[M, K] . w[N, K]^T.  x and w bfloat16 with K contiguous, ldx/ldw elements
+// between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
+// 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
+// [M, N/2], 3 float32 out.  workspace: float32 scratch of at least tl_gemm_tc_plan bytes.
+int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
+               int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes,
+               cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || epilogue < 0 || epilogue > 3) return TL_ERR_UNSUPPORTED;
+  if (epilogue == EPI_SWIGLU_BF16 && (N % 32 || bias)) return TL_ERR_UNSUPPORTED;
+  const Plan plan = make_plan(M, N, K);
+  Params p;
+  p.k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  p.k_blocks_per_split = plan.k_blocks_per_split;
+  p.bias = bias;
+  p.out = out;
+  p.ldo = ldo;
+  p.epilogue = epilogue;
+  p.partial = (float*)workspace;
+  CUtensorMap map_row, map_col;
+  int rc;
+  if (plan.swap) {
+    if ((long long)plan.splits * M * N * 4 > workspace_bytes) return TL_ERR_UNSUPPORTED;
+    p.rows = N;
+    p.cols = M;
+    if (!cached_map(&map_row, w, N, K, ldw, BLOCK_P) || !cached_map(&map_col, x, M, K, ldx, plan.block_q))
+      return TL_ERR_UNSUPPORTED;
+    dim3 grid((N + BLOCK_P - 1) / BLOCK_P, (M + plan.block_q - 1) / plan.block_q, plan.splits);
+    switch (plan.block_q) {
+      case 16: rc = launch<16, 8, true>(map_row, map_col, p, grid, stream); break;
+      case 32: rc = launch<32, 8, true>(map_row, map_col, p, grid, stream); break;
+      case 64: rc = launch<64, 8, true>(map_row, map_col, p, grid, stream); break;
+      case 128: rc = launch<128, 6, true>(map_row, map_col, p, grid, stream); break;
+      default: rc = launch<256, 4, true>(map_row, map_col, p, grid, stream); break;
+    }
+    if (rc) return rc;
+    const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
+    const long long total = (long long)M * out_cols;
+    splitk_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p.partial, plan.splits, M, N, bias,
+                                                                             epilogue, out, ldo);
+    return TL_LAUNCH_CHECK();
+  }
+  p.rows = M;
+  p.cols = N;
+  if (!cached_map(&map_row, x, M, K, ldx, BLOCK_P) || !cached_map(&map_col, w, N, K, ldw, plan.block_q))
+    return TL_ERR_UNSUPPORTED;
+  dim3 grid((M + BLOCK_P - 1) / BLOCK_P, (N + plan.block_q - 1) / plan.block_q, 1);
+  if (plan.block_q == 256)
+    rc = launch<256, 4, false>(map_row, map_col, p, grid, stream);
+  else
+    rc = launch<128, 6, false>(map_row, map_col, p, grid, stream);
+  return rc;
+}
+
+}  // extern "C"

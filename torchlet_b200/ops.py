@@ -46,6 +46,12 @@ _SIGNATURES = {
         "tl_attention_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
                                  c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     },
+    "gemm_tc": {
+        "tl_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong,
+                       c_longlong, c_void_p, c_longlong, c_void_p],
+        "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
+        "tl_gemm_tc_error": [],
+    },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
@@ -60,7 +66,7 @@ def _fn(library: str, name: str):
         lib = load_library(library)
         fn = getattr(lib, name)
         fn.argtypes = _SIGNATURES[library][name]
-        fn.restype = c_int
+        fn.restype = c_longlong if name.endswith("_plan") else c_int
         _functions[name] = fn
     return fn
 
@@ -176,3 +182,49 @@ def sample(logits, out, temperature=None, seed=None, counter=None) -> None:
         logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _ptr(counter),
         out.data_ptr(), _stream())
     _check(code, "sample")
+
+
+# ------------------------------------------------------- tensor-core products
+EPI_STORE_BF16, EPI_ACCUM_F32, EPI_SWIGLU_BF16, EPI_STORE_F32 = 0, 1, 2, 3
+_workspaces: dict = {}
+
+
+def _workspace(device, nbytes: int) -> torch.Tensor:
+    """A float32 scratch buffer per device that only grows (split-K partial sums)."""
+    ws = _workspaces.get(device)
+    if ws is None or ws.numel() * 4 < nbytes:
+        ws = torch.empty(max(nbytes // 4 + 1, 1 << 22), dtype=torch.float32, device=device)
+        _workspaces[device] = ws
+    return ws
+
+
+def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Sizes the tcgen05 product takes: K and both row strides multiples of 8 elements,
+    16-byte aligned bases."""
+    K = x.shape[1]
+    return (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and K % 8 == 0 and x.stride(0) % 8 == 0
+            and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+            and x.stride(1) == 1 and w.stride(1) == 1)
+
+
+def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16) -> None:
+    """out (+)= x @ w.T (+ bias) on the tcgen05 tensor cores; see csrc/gemm_tc.cu."""
+    _need_cuda(x, w, out, bias)
+    M, K = x.shape
+    N = w.shape[0]
+    assert w.shape[1] == K and out.stride(1) == 1
+    want = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU_BF16) else torch.float32
+    assert out.dtype == want and out.shape == (M, N // 2 if epilogue == EPI_SWIGLU_BF16 else N)
+    assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
+    need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, None, None)
+    ws = _workspace(x.device, need) if need else None
+    code = _fn("gemm_tc", "tl_gemm_tc")(
+        x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), epilogue, M, N, K, x.stride(0),
+        w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
+    _check(code, "gemm_tc")
+
+
+def gemm_tc_error() -> int:
+    """0, or the code a bounded wait in a tensor-core kernel left when it gave up
+    (1 producer, 2 MMA issuer, 3 epilogue).  Reading clears it."""
+    return _fn("gemm_tc", "tl_gemm_tc_error")()

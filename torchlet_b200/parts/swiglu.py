@@ -18,6 +18,7 @@ class SwiGLU(FeedForward):
         self.hidden_size = int(spec.params["hidden_size"])
         self.intermediate_size = int(spec.params["intermediate_size"])
         self.gate_up_proj: Linear | None = None
+        self.gate_up_interleaved = None  # bfloat16 fused path: gate/up rows interleaved by 16
         self.down_proj: Linear | None = None
 
     @classmethod
@@ -30,8 +31,14 @@ class SwiGLU(FeedForward):
         ]
 
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
-        gate_up = torch.cat([tensors[prefix + "gate_proj.weight"], tensors[prefix + "up_proj.weight"]], dim=0)
-        self.gate_up_proj = Linear(gate_up, None, device, dtype)
+        from . import swiglu_bf16
+
+        gate, up = tensors[prefix + "gate_proj.weight"], tensors[prefix + "up_proj.weight"]
+        if dtype == torch.bfloat16 and swiglu_bf16.usable(self.hidden_size, self.intermediate_size):
+            self.gate_up_interleaved = swiglu_bf16.interleave(
+                gate.to(device=device, dtype=dtype), up.to(device=device, dtype=dtype))
+        else:
+            self.gate_up_proj = Linear(torch.cat([gate, up], dim=0), None, device, dtype)
         self.down_proj = Linear(tensors[prefix + "down_proj.weight"], None, device, dtype)
 
     def forward(self, ctx, x, acc) -> None:
