@@ -1,0 +1,356 @@
+"""Each kernel alone against a plain float32 PyTorch reference of the same operation, at
+sizes other than the engine's tiny models: widths and vocabularies that are no power of
+two, head sizes 48/64/128, odd group sizes, several page sizes.  Where random inputs
+would hide a fault (one far key among hundreds, a window's edge, a page's edge) the
+inputs are built so that it shows."""
+import math
+
+import pytest
+import torch
+
+import plain_model
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def _ops():
+    from torchlet_b200 import ops
+
+    return ops
+
+
+def randn(*shape, dtype=torch.float32, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).to(DEV)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(dtype):
+    ops = _ops()
+    table = randn(331, 100, dtype=dtype)
+    ids = torch.tensor([0, 330, 7, 7, 100], dtype=torch.int32, device=DEV)
+    acc = torch.empty(5, 100, device=DEV)
+    ops.embed(table, ids, acc)
+    assert torch.equal(acc, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("hidden", [100, 96, 3584])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rms_norm(hidden, dtype):
+    ops = _ops()
+    acc, w = randn(7, hidden, scale=3.0), randn(hidden, seed=1) * 0.1 + 1
+    out = torch.empty(7, hidden, device=DEV, dtype=dtype)
+    ops.rms_norm(acc, w, 1e-5, out)
+    want = plain_model.rms_norm(acc.cpu(), w.cpu(), 1e-5)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    assert (out.float().cpu() - want).abs().max() <= tol * want.abs().max()
+    rows = torch.tensor([5, 0, 5], dtype=torch.int32, device=DEV)
+    picked = torch.empty(3, hidden, device=DEV, dtype=dtype)
+    ops.rms_norm(acc, w, 1e-5, picked, rows)
+    assert torch.equal(picked, out[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_swiglu(dtype):
+    ops = _ops()
+    gu = randn(9, 400, dtype=dtype, scale=2.0)
+    out = torch.empty(9, 200, device=DEV, dtype=dtype)
+    ops.swiglu(gu, out)
+    g, u = gu.float()[:, :200], gu.float()[:, 200:]
+    want = torch.nn.functional.silu(g) * u
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    assert (out.float() - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("dtype, out_dtype", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                              (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("M, N, K", [(1, 70, 45), (33, 130, 77), (200, 64, 256)])
+def test_gemm_simt(dtype, out_dtype, M, N, K):
+    ops = _ops()
+    x, w, b = randn(M, K, dtype=dtype), randn(N, K, dtype=dtype, seed=1), randn(N, seed=2)
+    out = torch.empty(M, N, device=DEV, dtype=out_dtype)
+    ops.gemm_simt(x, w, out, b)
+    want = x.double() @ w.double().t() + b.double()
+    tol = 1e-5 if out_dtype == torch.float32 else 1e-2
+    assert (out.double() - want).abs().max() <= tol * want.abs().max()
+    if out_dtype == torch.float32:
+        base = randn(M, N, seed=3)
+        acc = base.clone()
+        ops.gemm_simt(x, w, acc, None, accumulate=True)
+        assert (acc.double() - (base.double() + want - b.double())).abs().max() <= 1e-5 * want.abs().max()
+        # a row's result does not depend on the other rows of the batch
+        alone = torch.empty(1, N, device=DEV)
+        ops.gemm_simt(x[M - 1:], w, alone, b)
+        assert torch.equal(alone[0], out[M - 1])
+
+
+@pytest.mark.parametrize("M, N, K, epilogue, bias", [
+    (1, 256, 128, 3, False), (8, 384, 264, 0, True), (64, 520, 1024, 1, False), (5, 448, 96, 2, False),
+    (100, 1000, 520, 3, True), (300, 512, 256, 0, True), (1000, 384, 512, 1, True), (700, 448, 96, 2, False),
+    (513, 1000, 72, 3, False), (257, 331, 200, 0, True),
+])
+def test_gemm_tc(M, N, K, epilogue, bias):
+    ops = _ops()
+    x, w = randn(M, K, dtype=torch.bfloat16, scale=0.5), randn(N, K, dtype=torch.bfloat16, scale=0.5, seed=1)
+    b = randn(N, seed=2) if bias else None
+    want = x.double() @ w.double().t() + (b.double() if bias else 0)
+    if epilogue == ops.EPI_STORE_BF16:
+        out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_tc(x, w, out, b, epilogue)
+        tol = 8e-3
+    elif epilogue == ops.EPI_ACCUM_F32:
+        base = randn(M, N, seed=3)
+        out = base.clone()
+        ops.gemm_tc(x, w, out, b, epilogue)
+        want, tol = want + base.double(), 2e-5
+    elif epilogue == ops.EPI_STORE_F32:
+        out = torch.zeros(M, N, device=DEV)
+        ops.gemm_tc(x, w, out, b, epilogue)
+        tol = 2e-5
+    else:
+        from torchlet_b200.parts.swiglu_bf16 import interleave
+
+        inter = N // 2
+        out = torch.zeros(M, inter, device=DEV, dtype=torch.bfloat16)
+        ops.gemm_tc(x, interleave(w[:inter], w[inter:]), out, None, epilogue)
+        want = torch.nn.functional.silu(want[:, :inter]) * want[:, inter:]
+        tol = 8e-3
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_error() == 0
+    assert (out.double() - want).abs().max() <= tol * want.abs().max()
+
+
+def test_gemm_tc_refuses_what_it_cannot_do():
+    ops = _ops()
+    x, w = randn(4, 100, dtype=torch.bfloat16), randn(8, 100, dtype=torch.bfloat16)
+    assert not ops.gemm_tc_supported(x, w)  # K = 100 is no multiple of 8
+    with pytest.raises(ops.KernelError):
+        ops.gemm_tc(x, w, torch.empty(4, 8, device=DEV, dtype=torch.bfloat16))
+
+
+# ----------------------------------------------------------------- attention
+def paged_inputs(lens_before, q_lens, nh, nkv, d, page, dtype, seed=0, num_pages=None, shuffle=True):
+    """Random q/k/v for requests with ``lens_before`` cached tokens and ``q_lens`` new ones;
+    returns the kernel's inputs and per-request dense (q, k, v) for the plain reference."""
+    g = torch.Generator().manual_seed(seed)
+    n = len(q_lens)
+    totals = [b + q for b, q in zip(lens_before, q_lens)]
+    width = max(-(-t // page) for t in totals)
+    need = sum(-(-t // page) for t in totals)
+    num_pages = num_pages or need + 3
+    order = torch.randperm(num_pages - 1, generator=g) + 1 if shuffle else torch.arange(1, num_pages)
+    pages = torch.randn(num_pages, 2, nkv, page, d, generator=g).to(dtype)  # garbage everywhere first
+    table = torch.zeros(n, width, dtype=torch.int32)
+    dense, cursor = [], 0
+    T = sum(q_lens)
+    qkv = torch.zeros(T, (nh + 2 * nkv) * d, dtype=dtype)
+    positions, token_req, indptr = [], [], [0]
+    t0 = 0
+    for i, (before, q_len, total) in enumerate(zip(lens_before, q_lens, totals)):
+        k = torch.randn(total, nkv, d, generator=g).to(dtype)
+        v = torch.randn(total, nkv, d, generator=g).to(dtype)
+        q = torch.randn(q_len, nh, d, generator=g).to(dtype)
+        count = -(-total // page)
+        mine = order[cursor:cursor + count]
+        cursor += count
+        table[i, :count] = mine.to(torch.int32)
+        for pos in range(total):
+            pages[mine[pos // page], 0, :, pos % page] = k[pos]
+            pages[mine[pos // page], 1, :, pos % page] = v[pos]
+        qkv[t0:t0 + q_len, : nh * d] = q.reshape(q_len, nh * d)
+        positions += list(range(before, total))
+        token_req += [i] * q_len
+        indptr.append(indptr[-1] + q_len)
+        dense.append((q, k, v))
+        t0 += q_len
+    to = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+    return dict(qkv=qkv.to(DEV), pages=pages.to(DEV), table=table.to(DEV), positions=to(positions),
+                token_req=to(token_req), indptr=to(indptr), before=to(lens_before), dense=dense, T=T)
+
+
+def plain_attention(dense, lens_before, nh, nkv, window, scale):
+    outs = []
+    for (q, k, v), before in zip(dense, lens_before):
+        total = k.shape[0]
+        full_q = torch.zeros(total, nh, q.shape[-1])
+        full_q[before:] = q.float()
+        out = plain_model.causal_gqa_attention(full_q, k.float(), v.float(), window, scale)
+        outs.append(out[before:])
+    return torch.cat(outs)
+
+
+ATTENTION_CASES = [
+    # lens_before, q_lens, nh, nkv, d, page, window
+    ([0, 37, 300], [50, 1, 9], 5, 1, 48, 32, None),
+    ([0, 5, 64], [33, 20, 1], 4, 2, 16, 16, 7),
+    ([10, 0], [1, 130], 6, 3, 64, 8, None),
+    ([700, 0, 63, 128], [1, 1, 1, 1], 14, 2, 128, 16, None),
+    ([100, 90], [70, 3], 7, 1, 128, 16, 64),
+]
+
+
+@pytest.mark.parametrize("case", ATTENTION_CASES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_generic(case, dtype):
+    ops = _ops()
+    before, q_lens, nh, nkv, d, page, window = case
+    x = paged_inputs(before, q_lens, nh, nkv, d, page, dtype)
+    out = torch.zeros(x["T"], nh * d, device=DEV, dtype=dtype)
+    scale = 0.37 / math.sqrt(d)
+    ops.attention_generic(x["qkv"], x["qkv"].stride(0), x["pages"], x["table"], x["token_req"], x["positions"], out,
+                          x["T"], nh, nkv, d, page, window, scale)
+    want = plain_attention(x["dense"], before, nh, nkv, window, scale)
+    tol = 2e-5 if dtype == torch.float32 else 1.5e-2
+    assert (out.float().cpu() - want).abs().max() <= tol * want.abs().max()
+
+
+@pytest.mark.parametrize("case", [c for c in ATTENTION_CASES if c[4] in (64, 128)] + [
+    ([0], [257], 8, 8, 64, 32, None),
+    ([5, 1000, 0, 17], [3, 1, 64, 1], 28, 4, 128, 16, None),
+])
+def test_attention_mma(case):
+    ops = _ops()
+    before, q_lens, nh, nkv, d, page, window = case
+    group = nh // nkv
+    x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=3)
+    scale = 0.37 / math.sqrt(d)
+    want = plain_attention(x["dense"], before, nh, nkv, window, scale)
+    n = len(q_lens)
+    # every request through the 64-row tiles
+    tile_req, tile_row = [], []
+    for r, q in enumerate(q_lens):
+        for start in range(0, q * group, 64):
+            tile_req.append(r)
+            tile_row.append(start)
+    to = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = torch.zeros(x["T"], nh * d, device=DEV, dtype=torch.bfloat16)
+    ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(tile_req), to(tile_row),
+                      len(tile_req), out, x["T"], nh, nkv, d, page, window, scale, rows16=False)
+    assert (out.float().cpu() - want).abs().max() <= 1.5e-2 * want.abs().max()
+    # single-token requests through the 16-row tiles, keys split over 1, 3 and 8 CTAs
+    singles = [r for r, q in enumerate(q_lens) if q == 1]
+    if singles and group <= 16:
+        rows = torch.tensor([sum(q_lens[:r]) for r in singles])
+        for splits in (1, 3, 8):
+            out2 = torch.zeros_like(out)
+            ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(singles), None,
+                              len(singles), out2, x["T"], nh, nkv, d, page, window, scale, rows16=True, splits=splits)
+            assert (out2.float().cpu()[rows] - want[rows]).abs().max() <= 1.5e-2 * want.abs().max()
+
+
+@pytest.mark.parametrize("kernel", ["generic_f32", "generic_bf16", "mma"])
+def test_attention_finds_one_far_key_and_respects_the_window_edge(kernel):
+    """One key among 900 carries a large score: the output must be its value.  With a
+    window, the key at the window's edge is seen and the one just outside is not."""
+    ops = _ops()
+    nh, nkv, d, page = 2, 1, 64, 16
+    dtype = torch.float32 if kernel == "generic_f32" else torch.bfloat16
+    total, far = 900, 3
+    for window, hot in ((None, far), (200, total - 200), (200, total - 201)):
+        k = torch.randn(total, nkv, d, generator=torch.Generator().manual_seed(1)) * 0.05
+        v = torch.randn(total, nkv, d, generator=torch.Generator().manual_seed(2))
+        q = torch.randn(1, nh, d, generator=torch.Generator().manual_seed(3)) * 0.05
+        direction = torch.zeros(d)
+        direction[5] = 1.0
+        k[hot, 0] = direction * 8.0
+        q[0, :] = direction * 8.0  # score 64 at the hot key, about 0 elsewhere
+        num_pages = total // page + 3
+        pages = torch.zeros(num_pages, 2, nkv, page, d)
+        table = torch.arange(1, total // page + 2, dtype=torch.int32).flip(0).contiguous()
+        for pos in range(total):
+            pages[table[pos // page], 0, :, pos % page] = k[pos]
+            pages[table[pos // page], 1, :, pos % page] = v[pos]
+        qkv = torch.zeros(1, (nh + 2 * nkv) * d)
+        qkv[0, : nh * d] = q.reshape(-1)
+        to = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)
+        out = torch.zeros(1, nh * d, device=DEV, dtype=dtype)
+        args = (qkv.to(dtype).to(DEV), pages.to(dtype).to(DEV), table.view(1, -1).to(DEV))
+        if kernel == "mma":
+            ops.attention_mma(args[0], args[1], args[2], to([0, 1]), to([total - 1]), None, None, 1, out, 1, nh, nkv,
+                              d, page, window, 1.0, rows16=True, splits=4)
+        else:
+            ops.attention_generic(args[0], args[0].stride(0), args[1], args[2], to([0]), to([total - 1]), out, 1, nh,
+                                  nkv, d, page, window, 1.0)
+        got = out.float().cpu().view(nh, d)
+        seen = window is None or hot > total - 1 - window
+        if seen:
+            assert (got - v[hot, 0].to(dtype).float()).abs().max() < 2e-2, (window, hot)
+        else:
+            assert (got - v[hot, 0]).abs().max() > 0.5, (window, hot)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("d, nh, nkv, page", [(48, 5, 1, 32), (128, 4, 2, 16), (16, 2, 2, 8)])
+def test_rope_and_cache_write(dtype, d, nh, nkv, page):
+    ops = _ops()
+    theta = 50000.0
+    T = 23
+    g = torch.Generator().manual_seed(0)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, generator=g).to(dtype)
+    positions = torch.tensor([0, 1, 2, 31, 32, 33, 400, 401] + list(range(95, 110)), dtype=torch.int32)
+    token_req = torch.tensor([0] * 8 + [1] * 15, dtype=torch.int32)
+    width = 402 // page + 1
+    table = torch.zeros(2, width, dtype=torch.int32)
+    table[0] = torch.arange(1, width + 1)
+    table[1] = torch.arange(width + 1, 2 * width + 1).flip(0)
+    pages = torch.zeros(2 * width + 2, 2, nkv, page, d, dtype=dtype, device=DEV)
+    inv_freq = (1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    dev_qkv = qkv.to(DEV).clone()
+    ops.rope_kv(dev_qkv, positions.to(DEV), token_req.to(DEV), table.to(DEV), pages, inv_freq, nh, nkv, d, page)
+    x = qkv.float()
+    q = plain_model.rope_split_half(x[:, : nh * d].view(T, nh, d), positions, theta)
+    k = plain_model.rope_split_half(x[:, nh * d:(nh + nkv) * d].view(T, nkv, d), positions, theta)
+    v = x[:, (nh + nkv) * d:].view(T, nkv, d)
+    tol = 1e-5 if dtype == torch.float32 else 1e-2
+    got_q = dev_qkv.float().cpu()[:, : nh * d].view(T, nh, d)
+    assert (got_q - q).abs().max() <= tol * q.abs().max()
+    host_pages = pages.float().cpu()
+    for t in range(T):
+        pos, req = int(positions[t]), int(token_req[t])
+        page_id = int(table[req, pos // page])
+        assert (host_pages[page_id, 0, :, pos % page] - k[t]).abs().max() <= tol * k.abs().max()
+        assert torch.equal(host_pages[page_id, 1, :, pos % page], v[t])
+    assert host_pages[0].abs().max() == 0  # page 0 is untouched: every token had a real page
+
+
+def test_sampling_greedy_and_temperature():
+    ops = _ops()
+    vocab = 1531
+    logits = randn(6, vocab, scale=3.0)
+    logits[0, 100] = logits[0, 900] = 50.0  # a tie: the lowest index wins
+    logits[1, vocab - 1] = 60.0
+    out = torch.zeros(6, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out)
+    assert out.tolist() == logits.cpu().argmax(-1).tolist() and out[0] == 100 and out[1] == vocab - 1
+    temperature = torch.tensor([0.0, 0.7, 1.3, 1.3, 1.3, 2.0], device=DEV)
+    seed = torch.tensor([1, 2, 3, 2, 99, 2 ** 40 + 5], dtype=torch.int64, device=DEV)
+    counter = torch.tensor([0, 5, 5, 6, 5, 1], dtype=torch.int32, device=DEV)
+    logits[3] = logits[2]
+    logits[4] = logits[2]
+    ops.sample(logits, out, temperature, seed, counter)
+    host = logits.cpu()
+    for r in range(6):
+        if temperature[r] == 0:
+            assert out[r] == host[r].argmax()
+            continue
+        scores = plain_model.temperature_scores(host[r], float(temperature[r]), int(seed[r]), int(counter[r]))
+        best = max(scores)
+        assert scores[int(out[r])] >= best - 1e-3  # the kernel's pick is the plain rule's (up to rounding)
+    # same logits, same seed: the counter and the seed change the draw
+    assert len({int(out[2]), int(out[3]), int(out[4])}) > 1
+    again = torch.zeros_like(out)
+    ops.sample(logits, again, temperature, seed, counter)
+    assert torch.equal(out, again)
+
+
+def test_temperature_sampling_follows_the_distribution():
+    ops = _ops()
+    probs = torch.tensor([0.5, 0.25, 0.125, 0.0625, 0.0625])
+    rows = 4000
+    logits = probs.log().repeat(rows, 1).to(DEV).contiguous()
+    out = torch.zeros(rows, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, torch.ones(rows, device=DEV), torch.full((rows,), 7, dtype=torch.int64, device=DEV),
+               torch.arange(rows, dtype=torch.int32, device=DEV))
+    freq = torch.bincount(out.long().cpu(), minlength=5).float() / rows
+    assert (freq - probs).abs().max() < 0.03

@@ -1,0 +1,475 @@
+// Paged causal grouped-query attention on tensor cores for bfloat16, head_dim 64 or 128.
+//
+// Work is cut into tiles of PACKED ROWS: for one (request, KV head) the rows are the
+// pairs (token of the step, query head of the KV head's group), token-major, so that all
+// query heads of a group share every K/V tile that is loaded.  A CTA of 4 warps walks
+// over the keys in tiles of 64 absolute positions (pages gathered through the block
+// table with cp.async into swizzled shared memory, double-buffered), computes
+// S = Q K^T with mma.sync.m16n8k16 (bf16 in, float32 out), keeps the online-softmax
+// state (max, sum, accumulator) in float32 registers, and accumulates P V with P
+// rounded to bfloat16 as the tensor-core operand.
+//
+// Two shapes of CTA:
+//   ROWS64  (prompt portions): the tile has 64 packed rows, each warp owns 16 of them
+//           and sees every key of the tile.
+//   ROWS16  (decode, few rows a request): the tile has 16 packed rows that all four
+//           warps share; each warp takes 16 of the tile's 64 keys, and the warps' partial
+//           states are merged at the end.  The keys of a request can also be split over
+//           blockIdx.z; each split then writes its (max, sum, accumulator) to a workspace
+//           and a second kernel merges the splits.
+//
+// Reference counterparts: forward_ragged_attention_kernel and
+// forward_slot_attention_decode_kernel (v10_triton_paged_gqa/kernel/gqa.py:5-228), which
+// use the same numerics: float32 scores scaled by head_dim^-0.5, float32 max/sum/acc, the
+// weights cast to the value dtype before P.V, acc / sum at the end.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace {
+
+constexpr int WARPS = 4;
+constexpr int THREADS = WARPS * 32;
+constexpr int BLOCK_N = 64;  // keys per tile
+
+struct Params {
+  const __nv_bfloat16* q;  // packed qkv rows; query head h of token t at q + t*q_stride + h*D
+  long long q_stride;
+  const __nv_bfloat16* pages;  // [page][2][nkv][page_size][D]
+  const int* block_table;      // [requests][table_width]
+  int table_width;
+  const int* req_indptr;  // [requests + 1] first token of each request in the step
+  const int* kv_before;   // [requests] cached tokens before the step
+  const int* tile_req;    // [tiles] request of each row tile, or null: tile i = request i
+  const int* tile_row;    // [tiles] first packed row of the tile (null: 0)
+  __nv_bfloat16* out;     // [tokens][nh*D]
+  long long out_stride;
+  float* part_acc;  // [tokens*nh][splits][D]   (splits > 1)
+  float* part_ml;   // [tokens*nh][splits][2]
+  int nh, nkv, page_size, window, splits;
+  float scale_log2;  // scale * log2(e)
+};
+
+__device__ __forceinline__ void cp_async_16(void* smem, const void* gmem, bool valid) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  const int bytes = valid ? 16 : 0;  // 0: the 16 bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(s), "l"(gmem), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* smem) {
+  const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(s));
+}
+__device__ __forceinline__ void mma_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&h);
+}
+
+// Element (row, 8-element chunk) of a [rows][D] bf16 tile with the chunk index xor-ed by
+// the row, so that the 8 rows of an ldmatrix fall into different banks.
+template <int D> __device__ __forceinline__ __nv_bfloat16* tile_at(__nv_bfloat16* tile, int row, int chunk) {
+  return tile + row * D + ((chunk ^ (row & 7)) << 3);
+}
+
+// Gathers the K and V rows of keys [key0, key0 + 64) of one KV head into shared memory.
+// Rows outside [lo_key, hi_key] are zero-filled instead of read.
+template <int D>
+__device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, int kvh, int key0, int lo_key,
+                                             int hi_key, __nv_bfloat16* ks, __nv_bfloat16* vs) {
+  constexpr int CHUNKS = D / 8;
+  const size_t page_elems = (size_t)2 * p.nkv * p.page_size * D;
+  const size_t v_off = (size_t)p.nkv * p.page_size * D;
+  for (int i = threadIdx.x; i < BLOCK_N * CHUNKS; i += THREADS) {
+    const int r = i / CHUNKS, c = i % CHUNKS;
+    const int key = key0 + r;
+    const bool valid = key >= lo_key && key <= hi_key;
+    const __nv_bfloat16* src = p.pages;
+    if (valid) {
+      const int page = table[key / p.page_size];
+      src = p.pages + (size_t)page * page_elems + ((size_t)kvh * p.page_size + key % p.page_size) * D + c * 8;
+    }
+    cp_async_16(tile_at<D>(ks, r, c), src, valid);
+    cp_async_16(tile_at<D>(vs, r, c), valid ? src + v_off : src, valid);
+  }
+}
+
+template <int D, bool ROWS16>
+__global__ void __launch_bounds__(THREADS)
+attention_mma_kernel(const Params p) {
+  constexpr int BLOCK_M = ROWS16 ? 16 : 64;
+  constexpr int KSTEPS = D / 16;   // k-steps of Q K^T
+  constexpr int DTILES = D / 8;    // n-tiles of the output
+  // key sub-range of a 64-key tile this warp multiplies: all of it, or its own 16 keys
+  constexpr int WARP_KEYS = ROWS16 ? 16 : 64;
+  constexpr int NTILES = WARP_KEYS / 8;
+
+  extern __shared__ __align__(128) uint8_t smem_raw[];
+  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BLOCK_M][D]
+  __nv_bfloat16* kv = qs + BLOCK_M * D;                             // 2 stages x (K, V) x [64][D]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int req = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.x;
+  const int row_start = p.tile_row ? p.tile_row[blockIdx.x] : 0;
+  const int kvh = blockIdx.y;
+  const int split = blockIdx.z;
+  const int g = p.nh / p.nkv;
+  const int tok0 = p.req_indptr[req];
+  const int q_len = p.req_indptr[req + 1] - tok0;
+  const int before = p.kv_before[req];
+  const int total_rows = q_len * g;
+  const int* table = p.block_table + (size_t)req * p.table_width;
+
+  // rows of this tile: [row_start, row_end)
+  const int row_end = min(total_rows, row_start + BLOCK_M);
+  if (row_start >= row_end) return;
+  const int first_tok = row_start / g, last_tok = (row_end - 1) / g;
+  const int hi_key = before + last_tok;  // last key any row of the tile may see
+  int lo_key = 0;
+  if (p.window > 0) lo_key = max(0, before + first_tok - p.window + 1);
+
+  // key tiles of this CTA
+  int tile_begin = lo_key / BLOCK_N, tile_end = hi_key / BLOCK_N + 1;
+  if (p.splits > 1) {
+    const int per = (tile_end - tile_begin + p.splits - 1) / p.splits;
+    tile_begin = tile_begin + split * per;
+    tile_end = min(tile_end, tile_begin + per);
+  }
+
+  // ---- Q rows into shared memory (zero for rows past the tile's end)
+  for (int i = threadIdx.x; i < BLOCK_M * (D / 8); i += THREADS) {
+    const int r = i / (D / 8), c = i % (D / 8);
+    const int row = row_start + r;
+    const bool valid = row < row_end;
+    const __nv_bfloat16* src = p.q;
+    if (valid) src = p.q + (size_t)(tok0 + row / g) * p.q_stride + (size_t)(kvh * g + row % g) * D + c * 8;
+    cp_async_16(tile_at<D>(qs, r, c), src, valid);
+  }
+  cp_async_commit();
+
+  const int my_rows = ROWS16 ? 0 : warp * 16;  // first tile row of this warp
+  // the two rows this thread holds in accumulator fragments
+  int row_pos[2], row_lo[2];
+#pragma unroll
+  for (int h = 0; h < 2; ++h) {
+    const int row = row_start + my_rows + (lane >> 2) + 8 * h;
+    if (row < row_end) {
+      row_pos[h] = before + row / g;
+      row_lo[h] = p.window > 0 ? max(0, row_pos[h] - p.window + 1) : 0;
+    } else {
+      row_pos[h] = -1;  // sees no key
+      row_lo[h] = 0;
+    }
+  }
+
+  float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+  float o_acc[DTILES][4];
+#pragma unroll
+  for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
+
+  constexpr int STAGE_ELEMS = 2 * BLOCK_N * D;
+  if (tile_begin < tile_end) {
+    load_kv_tile<D>(p, table, kvh, tile_begin * BLOCK_N, lo_key, hi_key, kv, kv + BLOCK_N * D);
+  }
+  cp_async_commit();
+  cp_async_wait<1>();  // Q has landed
+  __syncthreads();
+
+  unsigned q_frag[KSTEPS][4];
+#pragma unroll
+  for (int ks = 0; ks < KSTEPS; ++ks) {
+    const int r = my_rows + (lane & 7) + ((lane >> 3) & 1) * 8;
+    const int c = 2 * ks + (lane >> 4);
+    ldmatrix_x4(q_frag[ks], tile_at<D>(qs, r, c));
+  }
+
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    const int stage = (tile - tile_begin) & 1;
+    __nv_bfloat16* ks_tile = kv + stage * STAGE_ELEMS;
+    __nv_bfloat16* vs_tile = ks_tile + BLOCK_N * D;
+    if (tile + 1 < tile_end) {
+      __nv_bfloat16* next = kv + (stage ^ 1) * STAGE_ELEMS;
+      load_kv_tile<D>(p, table, kvh, (tile + 1) * BLOCK_N, lo_key, hi_key, next, next + BLOCK_N * D);
+    }
+    cp_async_commit();
+    cp_async_wait<1>();  // this tile has landed
+    __syncthreads();
+
+    const int key_base = tile * BLOCK_N + (ROWS16 ? warp * 16 : 0);  // first key this warp multiplies
+    const int key_row0 = ROWS16 ? warp * 16 : 0;                      // its row inside the tile
+
+    // ---- S = Q K^T over this warp's keys
+    float s[NTILES][4];
+#pragma unroll
+    for (int i = 0; i < NTILES; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+#pragma unroll
+      for (int nb = 0; nb < NTILES / 2; ++nb) {
+        unsigned b[4];
+        const int r = key_row0 + nb * 16 + (lane & 7) + (lane >> 4) * 8;
+        const int c = 2 * ks + ((lane >> 3) & 1);
+        ldmatrix_x4(b, tile_at<D>(ks_tile, r, c));
+        mma_16816(s[2 * nb], q_frag[ks], b[0], b[1]);
+        mma_16816(s[2 * nb + 1], q_frag[ks], b[2], b[3]);
+      }
+    }
+
+    // ---- mask, online softmax (float32)
+    float tile_max[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+    for (int i = 0; i < NTILES; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h = e >> 1;
+        const int key = key_base + i * 8 + (lane & 3) * 2 + (e & 1);
+        const bool ok = key <= row_pos[h] && key >= row_lo[h];
+        s[i][e] = ok ? s[i][e] * p.scale_log2 : -INFINITY;
+        tile_max[h] = fmaxf(tile_max[h], s[i][e]);
+      }
+    }
+    float corr[2], m_use[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 1));
+      tile_max[h] = fmaxf(tile_max[h], __shfl_xor_sync(0xffffffffu, tile_max[h], 2));
+      const float m_new = fmaxf(m_run[h], tile_max[h]);
+      m_use[h] = m_new == -INFINITY ? 0.f : m_new;  // a row that has seen no key yet
+      corr[h] = exp2f(m_run[h] - m_use[h]);         // exp2(-inf) = 0 on the first tile
+      m_run[h] = m_new;
+    }
+    float row_sum[2] = {0.f, 0.f};
+    unsigned p_frag[NTILES / 2][4];
+#pragma unroll
+    for (int i = 0; i < NTILES; ++i) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float pv = exp2f(s[i][e] - m_use[e >> 1]);
+        s[i][e] = pv;
+        row_sum[e >> 1] += pv;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < NTILES / 2; ++j) {
+      p_frag[j][0] = pack_bf16(s[2 * j][0], s[2 * j][1]);
+      p_frag[j][1] = pack_bf16(s[2 * j][2], s[2 * j][3]);
+      p_frag[j][2] = pack_bf16(s[2 * j + 1][0], s[2 * j + 1][1]);
+      p_frag[j][3] = pack_bf16(s[2 * j + 1][2], s[2 * j + 1][3]);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 1);
+      row_sum[h] += __shfl_xor_sync(0xffffffffu, row_sum[h], 2);
+      l_run[h] = l_run[h] * corr[h] + row_sum[h];
+    }
+#pragma unroll
+    for (int i = 0; i < DTILES; ++i) {
+      o_acc[i][0] *= corr[0];
+      o_acc[i][1] *= corr[0];
+      o_acc[i][2] *= corr[1];
+      o_acc[i][3] *= corr[1];
+    }
+
+    // ---- O += P V over this warp's keys
+#pragma unroll
+    for (int kk = 0; kk < NTILES / 2; ++kk) {
+#pragma unroll
+      for (int nb = 0; nb < DTILES / 2; ++nb) {
+        unsigned b[4];
+        const int r = key_row0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
+        const int c = 2 * nb + (lane >> 4);
+        ldmatrix_x4_trans(b, tile_at<D>(vs_tile, r, c));
+        mma_16816(o_acc[2 * nb], p_frag[kk], b[0], b[1]);
+        mma_16816(o_acc[2 * nb + 1], p_frag[kk], b[2], b[3]);
+      }
+    }
+    __syncthreads();  // the stage may be overwritten by the load after next
+  }
+  cp_async_wait<0>();
+
+  // ---- finish: merge the warps (ROWS16), then write output or split partials
+  float* merge = reinterpret_cast<float*>(kv);  // reuse the K/V stages
+  if constexpr (ROWS16) {
+    __syncthreads();
+    // merge[w][row][D + 2]: acc, then max and sum
+    constexpr int STRIDE = D + 2;
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int r = (lane >> 2) + 8 * h;
+      float* dst = merge + ((size_t)warp * 16 + r) * STRIDE;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) {
+        dst[i * 8 + (lane & 3) * 2] = o_acc[i][2 * h];
+        dst[i * 8 + (lane & 3) * 2 + 1] = o_acc[i][2 * h + 1];
+      }
+      if ((lane & 3) == 0) {
+        dst[D] = m_run[h];
+        dst[D + 1] = l_run[h];
+      }
+    }
+    __syncthreads();
+    const int rows_here = row_end - row_start;
+    for (int i = threadIdx.x; i < rows_here * D; i += THREADS) {
+      const int r = i / D, c = i % D;
+      float m_all = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) m_all = fmaxf(m_all, merge[((size_t)w * 16 + r) * STRIDE + D]);
+      const float m_ref = m_all == -INFINITY ? 0.f : m_all;
+      float acc = 0.f, l = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) {
+        const float* src = merge + ((size_t)w * 16 + r) * STRIDE;
+        const float f = exp2f(src[D] - m_ref);
+        acc += src[c] * f;
+        l += src[D + 1] * f;
+      }
+      const int row = row_start + r;
+      const int token = tok0 + row / g, head = kvh * g + row % g;
+      if (p.splits > 1) {
+        const size_t item = ((size_t)token * p.nh + head) * p.splits + split;
+        p.part_acc[item * D + c] = acc;
+        if (c == 0) {
+          p.part_ml[item * 2] = m_all;
+          p.part_ml[item * 2 + 1] = l;
+        }
+      } else {
+        p.out[(size_t)token * p.out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / l);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int row = row_start + my_rows + (lane >> 2) + 8 * h;
+      if (row >= row_end) continue;
+      const int token = tok0 + row / g, head = kvh * g + row % g;
+      const float inv = 1.f / l_run[h];
+      __nv_bfloat16* dst = p.out + (size_t)token * p.out_stride + (size_t)head * D + (lane & 3) * 2;
+#pragma unroll
+      for (int i = 0; i < DTILES; ++i) {
+        *reinterpret_cast<unsigned*>(dst + i * 8) = pack_bf16(o_acc[i][2 * h] * inv, o_acc[i][2 * h + 1] * inv);
+      }
+    }
+  }
+}
+
+// Merges the key splits of every (token, head): one warp each.
+template <int D>
+__global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                                         __nv_bfloat16* __restrict__ out, long long out_stride, int items, int nh,
+                                         int splits) {
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  float m_all = -INFINITY;
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, part_ml[((size_t)item * splits + s) * 2]);
+  const float m_ref = m_all == -INFINITY ? 0.f : m_all;
+  float l = 0.f;
+  float acc[D / 32];
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c) acc[c] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const size_t base = (size_t)item * splits + s;
+    const float f = exp2f(part_ml[base * 2] - m_ref);
+    l += part_ml[base * 2 + 1] * f;
+#pragma unroll
+    for (int c = 0; c < D / 32; ++c) acc[c] += part_acc[base * D + lane + 32 * c] * f;
+  }
+  const int token = item / nh, head = item % nh;
+  const float inv = 1.f / l;
+#pragma unroll
+  for (int c = 0; c < D / 32; ++c)
+    out[(size_t)token * out_stride + (size_t)head * D + lane + 32 * c] = __float2bfloat16_rn(acc[c] * inv);
+}
+
+template <int D, bool ROWS16>
+int launch(const Params& p, int tiles, cudaStream_t stream) {
+  constexpr int BLOCK_M = ROWS16 ? 16 : 64;
+  constexpr int SMEM = (BLOCK_M * D + 2 * 2 * BLOCK_N * D) * 2;
+  static_assert(!ROWS16 || WARPS * 16 * (D + 2) * 4 <= 2 * 2 * BLOCK_N * D * 2, "merge buffer fits the stages");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_mma_kernel<D, ROWS16>,
+                                           cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  dim3 grid(tiles, p.nkv, p.splits);
+  attention_mma_kernel<D, ROWS16><<<grid, THREADS, SMEM, stream>>>(p);
+  return TL_LAUNCH_CHECK();
+}
+
+}  // namespace
+
+extern "C" {
+
+// Bytes of float32 workspace for ``splits`` key splits over ``tokens`` tokens.
+long long tl_attention_mma_workspace(int tokens, int nh, int d, int splits) {
+  return splits > 1 ? (long long)tokens * nh * splits * (d + 2) * 4 : 0;
+}
+
+// rows16 != 0: tiles of 16 packed rows with the keys split over the warps and over
+// ``splits`` CTAs (decode); else tiles of 64 packed rows (prompt portions), splits = 1.
+int tl_attention_mma(const void* q, long long q_stride, const void* pages, const int* block_table, int table_width,
+                     const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
+                     int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
+                     int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
+                     cudaStream_t stream) {
+  if (tiles <= 0 || tokens <= 0) return 0;
+  if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 2)
+    return TL_ERR_UNSUPPORTED;
+  if (splits < 1 || (!rows16 && splits != 1) || nkv > 65535 || splits > 65535) return TL_ERR_UNSUPPORTED;
+  if (tl_attention_mma_workspace(tokens, nh, d, splits) > workspace_bytes) return TL_ERR_UNSUPPORTED;
+  Params p;
+  p.q = (const __nv_bfloat16*)q;
+  p.q_stride = q_stride;
+  p.pages = (const __nv_bfloat16*)pages;
+  p.block_table = block_table;
+  p.table_width = table_width;
+  p.req_indptr = req_indptr;
+  p.kv_before = kv_before;
+  p.tile_req = tile_req;
+  p.tile_row = tile_row;
+  p.out = (__nv_bfloat16*)out;
+  p.out_stride = out_stride;
+  p.part_acc = (float*)workspace;
+  p.part_ml = p.part_acc + (size_t)tokens * nh * splits * d;
+  p.nh = nh;
+  p.nkv = nkv;
+  p.page_size = page_size;
+  p.window = window;
+  p.splits = splits;
+  p.scale_log2 = scale * 1.4426950408889634f;
+  int rc;
+  if (d == 128)
+    rc = rows16 ? launch<128, true>(p, tiles, stream) : launch<128, false>(p, tiles, stream);
+  else
+    rc = rows16 ? launch<64, true>(p, tiles, stream) : launch<64, false>(p, tiles, stream);
+  if (rc || splits == 1) return rc;
+  const int items = tokens * nh;
+  if (d == 128)
+    attention_combine_kernel<128><<<(items + 3) / 4, 128, 0, stream>>>(p.part_acc, p.part_ml, p.out, out_stride,
+                                                                        items, nh, splits);
+  else
+    attention_combine_kernel<64><<<(items + 3) / 4, 128, 0, stream>>>(p.part_acc, p.part_ml, p.out, out_stride, items,
+                                                                       nh, splits);
+  return TL_LAUNCH_CHECK();
+}
+
+}  // extern "C"

@@ -65,12 +65,18 @@ class StepContext:
         self.req_indptr = self.kv_before = self.slots = self.logit_rows = None
         # host copies (numpy int32) for parts that plan on the host
         self.req_indptr_host = self.kv_before_host = self.slots_host = None
+        self.plans: dict = {}  # per-step plans parts share across layers
         # sampling rows of the step (device), None when every sampled row is greedy
         self.num_sampled = 0
         self.sample_temperature = self.sample_seed = self.sample_counter = None
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         return self._runner.buffer(name, shape, dtype)
+
+    def upload(self, values) -> torch.Tensor:
+        """Copy a small int32 array a part planned on the host to the device (valid for
+        this step only)."""
+        return self._runner.upload_aux(values)
 
 
 class ModelRunner:
@@ -133,6 +139,19 @@ class ModelRunner:
         if self._meta_event[turn] is None:
             self._meta_event[turn] = torch.cuda.Event()
         self._meta_event[turn].record()
+
+    def upload_aux(self, values) -> torch.Tensor:
+        """Room after the step's metadata, in the same pinned and device blocks."""
+        values = np.asarray(values, dtype=np.int32).reshape(-1)
+        turn = self._meta_turn
+        start, count = self._aux_offset, values.size
+        if start + count > self._meta_host[turn].numel():
+            raise ValueError("the step's host-planned data does not fit the metadata block")
+        self._meta_np[turn][start:start + count] = values
+        self._meta_dev[start:start + count].copy_(self._meta_host[turn][start:start + count], non_blocking=True)
+        self._meta_event[turn].record()
+        self._aux_offset += count
+        return self._meta_dev[start:start + count]
 
     # -------------------------------------------------------------- requests
     def admit(self, request_id: Hashable) -> int:
@@ -218,7 +237,8 @@ class ModelRunner:
         width = max(1, max(-(-(b + q) // cache.page_size) for b, q in zip(kv_before, lens)))
         G = self.num_groups
         words = 3 * T + (n + 1) + 2 * n + m + G * n * width + (4 * k + 2 if hot else 0)
-        host, dev = self._meta(words)
+        host, dev = self._meta(words + T + 4 * n + 1024)  # room for what parts plan on the host
+        self._aux_offset = words
         o = 0
 
         def take(count):

@@ -52,6 +52,11 @@ _SIGNATURES = {
         "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_error": [],
     },
+    "attention_mma": {
+        "tl_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                             c_int, c_void_p, c_longlong, c_void_p],
+    },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
     },
@@ -193,7 +198,8 @@ def _workspace(device, nbytes: int) -> torch.Tensor:
     """A float32 scratch buffer per device that only grows (split-K partial sums)."""
     ws = _workspaces.get(device)
     if ws is None or ws.numel() * 4 < nbytes:
-        ws = torch.empty(max(nbytes // 4 + 1, 1 << 22), dtype=torch.float32, device=device)
+        where = device[1] if isinstance(device, tuple) else device
+        ws = torch.empty(max(nbytes // 4 + 1, 1 << 22), dtype=torch.float32, device=where)
         _workspaces[device] = ws
     return ws
 
@@ -228,3 +234,19 @@ def gemm_tc_error() -> int:
     """0, or the code a bounded wait in a tensor-core kernel left when it gave up
     (1 producer, 2 MMA issuer, 3 epilogue).  Reading clears it."""
     return _fn("gemm_tc", "tl_gemm_tc_error")()
+
+
+def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, tokens, nh, nkv,
+                  d, page_size, window, scale, rows16: bool, splits: int = 1) -> None:
+    """Tensor-core paged attention (csrc/attention_mma.cu).  ``tile_req``/``tile_row`` None:
+    tile i is request i from its first packed row."""
+    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
+    assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16
+    need = tokens * nh * splits * (d + 2) * 4 if splits > 1 else 0
+    ws = _workspace(("attention", qkv.device), need) if need else None
+    code = _fn("attention_mma", "tl_attention_mma")(
+        qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), block_table.data_ptr(), block_table.shape[1],
+        req_indptr.data_ptr(), kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles, out.data_ptr(),
+        out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale), 1 if rows16 else 0, splits,
+        _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
+    _check(code, "attention_mma")

@@ -1,7 +1,75 @@
-"""Choice of the bfloat16 tensor-core attention kernels.  Returns False when none
-takes the sizes; the caller then uses the any-size kernel."""
+"""Choice and planning of the bfloat16 tensor-core attention kernel
+(csrc/attention_mma.cu).  Returns False when it does not take the sizes (head_dim other
+than 64 or 128, more than 16 query heads per KV head); the caller then uses the any-size
+kernel.
+
+Requests that bring a single token (decode) run in tiles of 16 packed rows with their
+keys split over several CTAs, so that a few long requests still fill the GPU; requests
+that bring a portion of a prompt run in tiles of 64 packed rows planned here on the host,
+as the reference plans its prefill tiles (v10_triton_paged_gqa/layer/gqa.py:163-216).
+"""
 from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+
+ROWS = 64
+SM_COUNT = 148
+
+
+def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
+    """Key splits so that about two CTAs per SM are busy; never more than one per 256 keys."""
+    want = -(-2 * SM_COUNT // max(1, num_requests * num_kv_heads))
+    return max(1, min(want, -(-max_kv_len // 256), 64))
+
+
+def _plan(ctx, group_size: int):
+    """Which requests decode, and the 64-row tiles of the others (uploaded once a step)."""
+    key = ("attention_mma", group_size)
+    plan = ctx.plans.get(key)
+    if plan is not None:
+        return plan
+    indptr = ctx.req_indptr_host
+    q_lens = np.diff(indptr)
+    if ctx.decode_only:
+        plan = {"decode": (None, ctx.num_requests), "prefill": None}
+    else:
+        decode = np.nonzero(q_lens == 1)[0].astype(np.int32)
+        others = np.nonzero(q_lens > 1)[0]
+        tile_req, tile_row = [], []
+        for r in others:
+            rows = int(q_lens[r]) * group_size
+            starts = np.arange(0, rows, ROWS, dtype=np.int32)
+            tile_req.append(np.full(starts.size, r, dtype=np.int32))
+            tile_row.append(starts)
+        plan = {"decode": None, "prefill": None}
+        if decode.size:
+            plan["decode"] = (ctx.upload(decode), int(decode.size))
+        if others.size:
+            req, row = np.concatenate(tile_req), np.concatenate(tile_row)
+            both = ctx.upload(np.concatenate([req, row]))
+            plan["prefill"] = (both[:req.size], both[req.size:], int(req.size))
+    ctx.plans[key] = plan
+    return plan
 
 
 def forward(mixer, ctx, qkv, cache, out) -> bool:
-    return False
+    d, nh, nkv = mixer.head_dim, mixer.num_heads, mixer.num_kv_heads
+    group = nh // nkv
+    if d not in (64, 128) or group > 16 or qkv.stride(0) % 8:
+        return False
+    plan = _plan(ctx, group)
+    common = dict(out=out, tokens=ctx.num_tokens, nh=nh, nkv=nkv, d=d, page_size=cache.page_size,
+                  window=mixer.window, scale=mixer.scale)
+    if plan["decode"] is not None:
+        tile_req, count = plan["decode"]
+        splits = decode_splits(count, nkv, ctx.max_kv_len)
+        ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, None,
+                          count, rows16=True, splits=splits, **common)
+    if plan["prefill"] is not None:
+        tile_req, tile_row, count = plan["prefill"]
+        ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row,
+                          count, rows16=False, splits=1, **common)
+    return True
