@@ -1,0 +1,137 @@
+"""Generation through the Python entry point and the engine: greedy tokens equal the plain
+implementation's; sampling does not depend on the batch; the CUDA-graph decode path equals
+the eager one; a pool too small for everyone preempts and still gives the same tokens."""
+import pytest
+import torch
+
+import harness
+import plain_model
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+
+
+def model_dir(tmp_path, name):
+    cfg, w = harness.weights_for(name)
+    return tiny_configs.write_model_dir(tmp_path / name, cfg, {k: v.to(torch.bfloat16) for k, v in w.items()})
+
+
+def prompts_for(name):
+    cfg = tiny_configs.ALL[name][0]
+    lengths = (5, 17, 33) if name == "A" else (1, 9, 24, 40)
+    return [tiny_configs.make_ids(cfg, n, seed=50 + i) for i, n in enumerate(lengths)]
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_entry_point(tmp_path, name, dtype):
+    from torchlet_b200 import LLM
+
+    folder = model_dir(tmp_path, name)
+    page = tiny_configs.ALL[name][1]["page_size"]
+    llm = LLM(folder, max_decode_slots=4, kv_block_size=page, dtype=dtype, max_seq_len=128)
+    prompts = prompts_for(name)
+    new = 8 if name == "A" else 12
+    outputs = llm.generate(prompts, max_new_tokens=new)
+    assert llm.engine.runner.graph_steps > 0  # decode went through the captured graph
+    cfg, w = harness.weights_for(name)
+    for prompt, got in zip(prompts, outputs):
+        assert len(got) == new
+        if dtype == "float32":
+            assert got == plain_model.greedy_generate(cfg, w, prompt, new)
+        else:
+            # bfloat16 may flip a near-tie: every token must be within rounding of the best
+            ids = list(prompt)
+            for token in got:
+                logits = plain_model.forward_logits(cfg, w, ids)[-1]
+                assert logits[token] >= logits.max() - 2.5e-2 * logits.abs().max()
+                ids.append(token)
+    llm.engine.runner.cache.check()
+    assert llm.engine.runner.cache.live_requests() == []
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_decode_equals_eager_decode(tmp_path, dtype):
+    from torchlet_b200 import LLM, SamplingParams
+
+    folder = model_dir(tmp_path, "B")
+    prompts = prompts_for("B")
+    params = [SamplingParams(max_new_tokens=20, temperature=t, seed=11 + i) for i, t in enumerate((0.0, 0.8, 0.0, 1.1))]
+    outs = []
+    for graph in (True, False):
+        llm = LLM(folder, max_decode_slots=4, kv_block_size=8, dtype=dtype, max_seq_len=128, cuda_graph=graph)
+        outs.append(llm.generate(prompts, sampling_params=params))
+        assert (llm.engine.runner.graph_steps > 0) == graph
+    if dtype == "float32":
+        assert outs[0] == outs[1]
+    else:
+        same = sum(a == b for x, y in zip(*outs) for a, b in zip(x, y))
+        assert same >= 0.8 * sum(len(x) for x in outs[0])
+
+
+def test_sampling_does_not_depend_on_the_batch(tmp_path):
+    from torchlet_b200 import LLM, SamplingParams
+
+    folder = model_dir(tmp_path, "B")
+    prompts = prompts_for("B")
+    params = [SamplingParams(max_new_tokens=12, temperature=0.8, seed=100 + i) for i in range(len(prompts))]
+    llm = LLM(folder, max_decode_slots=4, kv_block_size=8, dtype="float32", max_seq_len=128)
+    together = llm.generate(prompts, sampling_params=params)
+    alone = [llm.generate([p], sampling_params=[sp])[0] for p, sp in zip(prompts, params)]
+    assert together == alone
+    other_seed = llm.generate([prompts[3]], sampling_params=[SamplingParams(max_new_tokens=12, temperature=0.8, seed=5)])[0]
+    assert other_seed != alone[3]
+    # the first draw follows the plain rule
+    cfg, w = harness.weights_for("B")
+    logits = plain_model.forward_logits(cfg, w, prompts[2])[-1]
+    scores = plain_model.temperature_scores(logits, 0.8, 102, 0)
+    assert scores[alone[2][0]] >= max(scores) - 1e-3
+
+
+def test_small_pool_preempts_and_gives_the_same_tokens(tmp_path):
+    from torchlet_b200 import LLM
+
+    folder = model_dir(tmp_path, "A")
+    cfg = tiny_configs.ALL["A"][0]
+    prompts = [tiny_configs.make_ids(cfg, n, seed=70 + i) for i, n in enumerate((40, 37, 45, 30, 22))]
+    roomy = LLM(folder, max_decode_slots=4, kv_block_size=16, dtype="float32", max_seq_len=128)
+    want = roomy.generate(prompts, max_new_tokens=30)
+    # 9 usable pages of 16 tokens: not enough for four requests of ~70 tokens
+    tight = LLM(folder, max_decode_slots=4, kv_block_size=16, max_num_blocks=10, dtype="float32", max_seq_len=128,
+                max_num_batched_tokens=48)
+    got = tight.generate(prompts, max_new_tokens=30)
+    assert got == want
+    assert tight.engine.scheduler.stats.preemptions > 0
+    tight.engine.runner.cache.check()
+    assert tight.engine.runner.cache.pools[0].num_free == 9
+
+
+def test_a_request_too_large_for_the_pool_fails_alone(tmp_path):
+    from torchlet_b200.engine.scheduler import Request
+    from torchlet_b200 import LLM, SamplingParams
+
+    folder = model_dir(tmp_path, "A")
+    cfg = tiny_configs.ALL["A"][0]
+    llm = LLM(folder, max_decode_slots=2, kv_block_size=16, max_num_blocks=4, dtype="float32", max_seq_len=128)
+    small = Request(tiny_configs.make_ids(cfg, 10, 1), SamplingParams(max_new_tokens=4))
+    big = Request(tiny_configs.make_ids(cfg, 90, 2), SamplingParams(max_new_tokens=4))
+    llm.engine.generate([small, big])
+    assert small.error is None and len(small.output_tokens) == 4
+    assert big.error is not None and "too small" in str(big.error)
+    with pytest.raises(ValueError, match="cache positions"):
+        llm.generate([tiny_configs.make_ids(cfg, 120, 3)], max_new_tokens=20)
+
+
+def test_command_line(tmp_path):
+    import subprocess
+    import sys
+
+    folder = model_dir(tmp_path, "A")
+    cmd = [sys.executable, "-m", "torchlet_b200.llm", "--model", str(folder), "--prompt-ids", "1,2,3", "--prompt-ids",
+           "9,8", "--max-new-tokens", "5", "--dtype", "float32", "--max-seq-len", "64"]
+    out = subprocess.run(cmd, capture_output=True, text=True, cwd=str(harness.tiny_configs.__file__).rsplit("/tests", 1)[0])
+    assert out.returncode == 0, out.stderr
+    lines = [line for line in out.stdout.splitlines() if line.startswith("[")]
+    assert len(lines) == 2 and all(len(eval(line)) == 5 for line in lines)
+    cfg, w = harness.weights_for("A")
+    assert eval(lines[0]) == plain_model.greedy_generate(cfg, w, [1, 2, 3], 5)

@@ -19,6 +19,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Hashable, Optional
 
+import numpy as np
+
 NULL_PAGE = 0
 
 
@@ -89,6 +91,9 @@ class CacheManager:
         self.max_seq_len = max_seq_len
         self.max_pages_per_request = -(-max_seq_len // page_size)
         self.pools = [PagePool(g.num_pages) for g in self.groups]
+        # per group: the block tables of all slots as one int32 array [max_slots, pages per
+        # request], kept equal to the per-request lists so that a step gathers rows at once
+        self.table_arrays = [np.zeros((max_slots, self.max_pages_per_request), dtype=np.int32) for _ in self.groups]
         self._free_slots = list(range(max_slots - 1, -1, -1))
         self._requests: dict[Hashable, _RequestPages] = {}
 
@@ -141,8 +146,11 @@ class CacheManager:
         need = self._pages_needed(record, new_len)
         if any(n > pool.num_free for n, pool in zip(need, self.pools)):
             return False
-        for table, n, pool in zip(record.tables, need, self.pools):
-            table.extend(pool.take(n))
+        for g, (table, n, pool) in enumerate(zip(record.tables, need, self.pools)):
+            if n:
+                start = len(table)
+                table.extend(pool.take(n))
+                self.table_arrays[g][record.slot, start:start + n] = table[start:]
         return True
 
     def advance(self, request_id: Hashable, new_len: int) -> int:
@@ -166,6 +174,7 @@ class CacheManager:
             for logical in range(record.first_live[g], first_needed_page):
                 pool.give_back([table[logical]])
                 table[logical] = NULL_PAGE
+                self.table_arrays[g][record.slot, logical] = NULL_PAGE
                 given += 1
             record.first_live[g] = max(record.first_live[g], first_needed_page)
         return given
@@ -176,8 +185,9 @@ class CacheManager:
     def finish(self, request_id: Hashable) -> int:
         """Give back everything the request holds; returns its slot (now free)."""
         record = self._requests.pop(request_id)
-        for table, pool in zip(record.tables, self.pools):
+        for g, (table, pool) in enumerate(zip(record.tables, self.pools)):
             pool.give_back(table)
+            self.table_arrays[g][record.slot, :len(table)] = NULL_PAGE
         self._free_slots.append(record.slot)
         return record.slot
 
@@ -203,6 +213,10 @@ class CacheManager:
                 raise CacheError(f"group {g}: {pool.num_pages - 1 - len(free) - len(held)} pages lost")
             if NULL_PAGE in free:
                 raise CacheError(f"group {g}: page 0 is in the free list")
+            for record in self._requests.values():
+                row = self.table_arrays[g][record.slot]
+                if row[:len(record.tables[g])].tolist() != record.tables[g] or row[len(record.tables[g]):].any():
+                    raise CacheError(f"group {g}: the table array differs from the table of slot {record.slot}")
         slots = [r.slot for r in self._requests.values()]
         if len(slots) != len(set(slots)) or set(slots) & set(self._free_slots):
             raise CacheError("a slot is held twice")

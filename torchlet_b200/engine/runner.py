@@ -104,7 +104,11 @@ class ModelRunner:
         self._meta_event = [None, None]
         self._meta_dev: Optional[torch.Tensor] = None
         self._meta_turn = 0
+        self._aux_offset = 0
+        self._graphs: dict = {}
+        self._graph_safe = all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
         self.steps_run = 0
+        self.graph_steps = 0
 
     # ------------------------------------------------------------- workspace
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype, exact: bool = False) -> torch.Tensor:
@@ -181,6 +185,8 @@ class ModelRunner:
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepResult(None, None)
+        if self._graphable(entries):
+            return self._run_decode_graph(entries)
         ctx, caches = self._build(entries)
         with torch.no_grad():
             acc = self.model.forward(ctx, caches)
@@ -200,6 +206,131 @@ class ModelRunner:
             self.cache.advance(e.request_id, self.cache.num_tokens(e.request_id) + len(e.tokens))
         self.steps_run += 1
         return StepResult(logits, tokens)
+
+    # ------------------------------------------------------ decode by CUDA graph
+    # A step in which every entry brings one token and samples is replayed from a CUDA
+    # graph captured once per batch-size bucket over static buffers, as the reference
+    # captures its decode forward (v10_triton_paged_gqa/engine.py:137-185).  Lanes beyond
+    # the live requests are padding: token 0 at position 0 of the reserved page 0.
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+    def _graphable(self, entries) -> bool:
+        if not self.config.cuda_graph or not self._graph_safe:
+            return False
+        if len(entries) > min(self.config.max_decode_slots, self.GRAPH_BUCKETS[-1]):
+            return False
+        return all(len(e.tokens) == 1 and e.sample is not None and not e.want for e in entries)
+
+    def _bucket(self, n: int) -> int:
+        for b in self.GRAPH_BUCKETS:
+            if b >= n:
+                return b
+        raise ValueError(n)
+
+    def _graph_layout(self, b: int):
+        """Offsets (in int32 words) of the static metadata block of bucket ``b``."""
+        W, G = self.cache.max_pages_per_request, self.num_groups
+        names = (("tok", b), ("pos", b), ("req", b), ("ind", b + 1), ("kvb", b), ("slot", b), ("row", b),
+                 ("pad", (4 * b + 1 + 3 * b) & 1), ("seed", 2 * b), ("temp", b), ("count", b))
+        layout, o = {}, 0
+        for name, size in names:
+            layout[name] = (o, size)
+            o += size
+        layout["tables"] = [(o + g * b * W, b * W) for g in range(G)]
+        return layout, o + G * b * W
+
+    def _capture_decode_graph(self, b: int):
+        layout, words = self._graph_layout(b)
+        W = self.cache.max_pages_per_request
+        dev = torch.zeros(words, dtype=torch.int32, device=self.device)
+        view = lambda name: dev[layout[name][0]:layout[name][0] + layout[name][1]]
+        ctx = StepContext(self)
+        ctx.num_tokens = ctx.num_requests = b
+        ctx.max_q_len, ctx.decode_only = 1, True
+        ctx.max_kv_len = self.config.max_seq_len
+        ctx.tokens, ctx.positions, ctx.token_req = view("tok"), view("pos"), view("req")
+        ctx.req_indptr, ctx.kv_before, ctx.slots = view("ind"), view("kvb"), view("slot")
+        ctx.logit_rows = view("row")
+        ctx.num_sampled = b
+        ctx.sample_seed = view("seed").view(torch.int64)
+        ctx.sample_temperature = view("temp").view(torch.float32)
+        ctx.sample_counter = view("count")
+        ctx.req_indptr_host = np.arange(b + 1, dtype=np.int32)
+        ctx.kv_before_host = np.zeros(b, dtype=np.int32)
+        ctx.slots_host = np.zeros(b, dtype=np.int32)
+        tables = [dev[o:o + size].view(b, W) for o, size in layout["tables"]]
+        caches = self.storage.layer_caches(tables)
+        # padding everywhere for the warm-up and the capture
+        host = np.zeros(words, dtype=np.int32)
+        host[layout["req"][0]:layout["req"][0] + b] = np.arange(b)
+        host[layout["ind"][0]:layout["ind"][0] + b + 1] = np.arange(b + 1)
+        host[layout["row"][0]:layout["row"][0] + b] = np.arange(b)
+        dev.copy_(torch.from_numpy(host))
+        logits = torch.empty((b, self.vocab_size), dtype=torch.float32, device=self.device)
+        tokens = torch.empty(b, dtype=torch.int32, device=self.device)
+
+        def body():
+            acc = self.model.forward(ctx, caches)
+            self.model.logits(ctx, acc, ctx.logit_rows, logits)
+            ops.sample(logits, tokens, ctx.sample_temperature, ctx.sample_seed, ctx.sample_counter)
+
+        with torch.no_grad():
+            side = torch.cuda.Stream(device=self.device)
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                body()  # warm-up: builds kernels, sizes every scratch buffer
+            torch.cuda.current_stream().wait_stream(side)
+            torch.cuda.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                body()
+        state = {"layout": layout, "words": words, "dev": dev, "graph": graph, "logits": logits, "tokens": tokens,
+                 "template": host}
+        self._graphs[b] = state
+        return state
+
+    def _run_decode_graph(self, entries) -> StepResult:
+        cache = self.cache
+        n = len(entries)
+        b = self._bucket(n)
+        state = self._graphs.get(b) or self._capture_decode_graph(b)
+        layout, words = state["layout"], state["words"]
+        W = cache.max_pages_per_request
+        before = np.fromiter((cache.num_tokens(e.request_id) for e in entries), dtype=np.int32, count=n)
+        slots = np.fromiter((cache.slot_of(e.request_id) for e in entries), dtype=np.int32, count=n)
+        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
+        if n and (toks.min() < 0 or toks.max() >= self.vocab_size):
+            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
+        if len(set(slots.tolist())) != n:
+            raise ValueError("a request appears twice in one step")
+        for e, length in zip(entries, before):
+            if not cache.extend(e.request_id, int(length) + 1):
+                raise OutOfPages(f"no pages left for request {e.request_id!r}")
+        host, _ = self._meta(words)
+        host[:words] = state["template"]
+        put = lambda name, values: host.__setitem__(slice(layout[name][0], layout[name][0] + n), values)
+        put("tok", toks)
+        put("pos", before)
+        put("kvb", before)
+        put("slot", slots)
+        o = layout["seed"][0]
+        host[o:o + 2 * n].view(np.int64)[:] = [e.sample.seed & 0x7FFFFFFFFFFFFFFF for e in entries]
+        o = layout["temp"][0]
+        host[o:o + n].view(np.float32)[:] = [e.sample.temperature for e in entries]
+        put("count", [e.sample.counter for e in entries])
+        for g, (o, size) in enumerate(layout["tables"]):
+            np.take(cache.table_arrays[g], slots, axis=0, out=host[o:o + n * W].reshape(n, W))
+        turn = self._meta_turn
+        state["dev"].copy_(self._meta_host[turn][:words], non_blocking=True)
+        if self._meta_event[turn] is None:
+            self._meta_event[turn] = torch.cuda.Event()
+        self._meta_event[turn].record()
+        state["graph"].replay()
+        for e, length in zip(entries, before):
+            cache.advance(e.request_id, int(length) + 1)
+        self.steps_run += 1
+        self.graph_steps += 1
+        return StepResult(state["logits"][:n], state["tokens"][:n])
 
     def _build(self, entries):
         cache = self.cache
@@ -266,12 +397,10 @@ class ModelRunner:
             pos_h[start:start + q] = np.arange(before, before + q, dtype=np.int32)
             req_h[start:start + q] = i
             slot_h[i] = cache.slot_of(e.request_id)
-            for g in range(G):
-                table = cache.table(e.request_id, g)
-                row = tables[g][0][i * width:(i + 1) * width]
-                row[:len(table)] = table[:width]
-                row[len(table):] = 0
             start += q
+        slot_index = slot_h[:n]
+        for g in range(G):
+            np.take(cache.table_arrays[g][:, :width], slot_index, axis=0, out=tables[g][0].reshape(n, width))
         if T and (tok_h[:T].min() < 0 or tok_h[:T].max() >= vocab):
             raise ValueError(f"token ids must lie in [0, {vocab})")
         row_h[:] = want_rows

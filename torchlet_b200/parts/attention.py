@@ -25,6 +25,8 @@ from .linear import Linear
 
 @MIXERS.register("attention")
 class AttentionMixer(Mixer):
+    graph_safe = True  # nothing is planned on the host for single-token steps
+
     def __init__(self, spec: PartSpec):
         super().__init__(spec)
         p = spec.params
