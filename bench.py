@@ -1,0 +1,371 @@
+#!/usr/bin/env python3
+"""Benchmark of the engine on one B200: decode tokens a second at Qwen2.5-7B layer sizes
+with random bfloat16 weights (batch 8, context 4096 by default), with the prefill of a
+2,048-token prompt, decode at batch 1 and 64, the roofline fractions and the clocks seen.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+Prints ONE JSON line.  A "step" is one decode step of the whole batch.  ``value`` times
+the step function on the device with CUDA events (host -> device copy of the step's
+metadata included); ``e2e`` times the same decode steps through the Python entry point
+(``LLM`` -> engine -> scheduler), host tokens in and out, by the wall clock.  Inputs are
+seeded synthetic token ids; the cached context of the decode runs is seeded random keys
+and values.  Every step reads all weights (15 GB), far more than the 126 MB L2, so no
+L2 flush is needed between steps.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+QWEN25_7B = {
+    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 152064, "hidden_size": 3584, "intermediate_size": 18944,
+    "num_hidden_layers": 28, "num_attention_heads": 28, "num_key_value_heads": 4, "max_position_embeddings": 32768,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
+}
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    peaks, source = dict(FALLBACK_PEAKS), "fallback"
+    try:
+        with open(path) as handle:
+            raw = json.load(handle)
+        for key in ("hbm_gbs", "bf16_tflops", "bf16_tflops_sustained"):
+            if isinstance(raw.get(key), (int, float)) and raw[key] > 0:
+                peaks[key] = float(raw[key])
+                source = "measured"
+    except (OSError, ValueError):
+        pass
+    return peaks, source
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            out, _ = self.proc.communicate()
+        clocks, max_clock, reasons = [], None, set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                clocks.append(float(parts[0]))
+                max_clock = float(parts[1])
+            except ValueError:
+                continue
+            for name, value in zip(names, parts[2:6]):
+                if value.lower().startswith("active"):
+                    reasons.add(name)
+        clocks.sort()
+        median = clocks[len(clocks) // 2] if clocks else None
+        return {"sm_mhz": median, "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
+
+
+def model_numbers(cfg: dict, layers: int):
+    """Parameters a decode step reads, KV bytes per token, and flops of a prefill."""
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv = cfg["num_attention_heads"], cfg["num_key_value_heads"]
+    d = H // nh
+    per_layer = (nh + 2 * nkv) * d * H + (nh + 2 * nkv) * d + H * nh * d + 3 * I * H + 2 * H
+    read_params = layers * per_layer + V * H + H  # layers + LM head + final norm
+    kv_bytes_per_token = 2 * layers * nkv * d * 2
+
+    def prefill_flops(tokens: int) -> float:
+        gemm = 2.0 * tokens * layers * ((nh + 2 * nkv) * d * H + H * nh * d + 3 * I * H)
+        attention = layers * 4.0 * nh * d * tokens * (tokens + 1) / 2  # causal q.k and p.v
+        head = 2.0 * V * H  # one row of logits
+        return gemm + attention + head
+
+    return read_params, kv_bytes_per_token, prefill_flops
+
+
+def build_model(cfg: dict, layers: int, seed: int):
+    import torch
+
+    from torchlet_b200.config import Qwen2Config
+    from torchlet_b200.engine.loading import build_model as build
+    from torchlet_b200.weights import random_tensors
+
+    config = Qwen2Config.from_dict(dict(cfg, num_hidden_layers=layers))
+    tensors = random_tensors(config, seed, std=0.02, norm_std=0.0, dtype="bfloat16", device="cuda:0")
+    model = build(config, tensors, "bfloat16")
+    del tensors
+    torch.cuda.empty_cache()
+    return model
+
+
+def fill_context(runner, ids, context: int, seed: int):
+    """Give each request ``context`` cached tokens of seeded random keys and values."""
+    import torch
+
+    generator = torch.Generator(device="cuda:0").manual_seed(seed)
+    for pages in runner.storage.pages:
+        _randn_chunks(pages, generator)
+    for rid in ids:
+        runner.admit(rid)
+        if not runner.cache.extend(rid, context):
+            raise RuntimeError("the page pool is too small for the benchmark's context")
+        runner.cache.advance(rid, context)
+
+
+def _randn_chunks(pages, generator):
+    import torch
+
+    flat = pages.view(-1)
+    step = 1 << 27
+    for start in range(0, flat.numel(), step):
+        chunk = flat[start:start + step]
+        chunk.copy_(torch.randn(chunk.shape, generator=generator, device=pages.device, dtype=torch.float32).mul_(0.5))
+    return pages
+
+
+def time_decode(model, batch: int, context: int, steps: int, warmup: int, clock=None):
+    """Device time of ``steps`` decode steps of ``batch`` requests ending at ``context``."""
+    import torch
+
+    from torchlet_b200 import ops
+    from torchlet_b200.config import EngineConfig
+    from torchlet_b200.engine import ModelRunner, StepEntry
+    from torchlet_b200.sampling import SampleSpec
+
+    page = 16
+    start_len = context - steps - warmup
+    config = EngineConfig(dtype="bfloat16", max_decode_slots=batch, kv_block_size=page, max_seq_len=context,
+                          max_num_blocks=batch * (-(-context // page)) + 1, max_num_batched_tokens=2048)
+    runner = ModelRunner(model, config)
+    ids = [f"d{i}" for i in range(batch)]
+    fill_context(runner, ids, start_len, seed=17)
+    vocab = model.spec.vocab_size
+    generator = torch.Generator().manual_seed(batch)
+    tokens = torch.randint(0, vocab, (steps + warmup, batch), generator=generator).tolist()
+
+    def step(k):
+        entries = [StepEntry(rid, [tokens[k][i]], sample=SampleSpec(0.0, i, k)) for i, rid in enumerate(ids)]
+        return runner.run(entries)
+
+    for k in range(warmup):
+        step(k)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches = ops.launch_count
+    if clock:
+        clock.start()
+    begin.record()
+    for k in range(warmup, warmup + steps):
+        step(k)
+    end.record()
+    torch.cuda.synchronize()
+    stats = clock.stop() if clock else None
+    ms = begin.elapsed_time(end)
+    launches = ops.launch_count - launches
+    meta_words = runner._graphs[runner._bucket(batch)]["words"] if runner._graphs else 0
+    mean_context = start_len + warmup + steps / 2
+    for rid in ids:
+        runner.finish(rid)
+    del runner
+    torch.cuda.empty_cache()
+    return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
+            "h2d_bytes": meta_words * 4, "mean_context": mean_context, "clocks": stats}
+
+
+def time_prefill(model, tokens: int, repeats: int):
+    import torch
+
+    from torchlet_b200.config import EngineConfig
+    from torchlet_b200.engine import ModelRunner, StepEntry
+    from torchlet_b200.sampling import SampleSpec
+
+    config = EngineConfig(dtype="bfloat16", max_decode_slots=2, kv_block_size=16, max_seq_len=tokens + 16,
+                          max_num_batched_tokens=tokens)
+    runner = ModelRunner(model, config)
+    generator = torch.Generator().manual_seed(3)
+    best = None
+    for r in range(repeats + 2):
+        prompt = torch.randint(0, model.spec.vocab_size, (tokens,), generator=generator).tolist()
+        runner.admit("p")
+        torch.cuda.synchronize()
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record()
+        result = runner.run([StepEntry("p", prompt, sample=SampleSpec())])
+        end.record()
+        torch.cuda.synchronize()
+        result.tokens.tolist()
+        runner.finish("p")
+        ms = begin.elapsed_time(end)
+        if r >= 2:
+            best = ms if best is None else min(best, ms)
+    del runner
+    torch.cuda.empty_cache()
+    return best
+
+
+def time_e2e(model, batch: int, context: int, steps: int, warmup: int):
+    """The same decode steps through the Python entry point: ``LLM`` -> engine -> scheduler
+    -> step function, host token ids in, host token ids out, by the wall clock."""
+    import torch
+
+    from torchlet_b200 import LLM, SamplingParams
+    from torchlet_b200.engine.scheduler import Request
+
+    page = 16
+    llm = LLM.from_model(model, max_decode_slots=batch, kv_block_size=page, max_seq_len=context,
+                         max_num_blocks=batch * (-(-context // page)) + 1, max_num_batched_tokens=2048)
+    engine = llm.engine
+    prompt_len = context - steps - warmup - 1
+    generator = torch.Generator().manual_seed(5)
+    params = SamplingParams(max_new_tokens=steps + warmup + 1, ignore_eos=True)
+    requests = [Request(torch.randint(0, model.spec.vocab_size, (prompt_len,), generator=generator).tolist(),
+                        SamplingParams(**vars(params))) for _ in range(batch)]
+    engine.add_requests(requests)
+    while any(r.num_computed < prompt_len for r in requests):  # prompts, in portions (untimed)
+        engine.step()
+    for _ in range(warmup):
+        engine.step()
+    torch.cuda.synchronize()
+    graph_before = engine.runner.graph_steps
+    produced = sum(len(r.output_tokens) for r in requests)
+    start = time.perf_counter()
+    for _ in range(steps):
+        engine.step()
+    torch.cuda.synchronize()
+    seconds = time.perf_counter() - start
+    produced = sum(len(r.output_tokens) for r in requests) - produced
+    graph_steps = engine.runner.graph_steps - graph_before
+    words = engine.runner._graphs[engine.runner._bucket(batch)]["words"] if engine.runner._graphs else 0
+    engine.scheduler.fail_all(RuntimeError("benchmark over"))
+    del llm, engine
+    torch.cuda.empty_cache()
+    return {"tok_s": produced / seconds, "ms_per_step": seconds * 1e3 / steps, "h2d_bytes": words * 4,
+            "d2h_bytes": batch * 4, "graph_steps": graph_steps}
+
+
+def reference_arm(args) -> int:
+    """The unmodified reference through its own public API.  Its ``LLM(model_id)`` downloads
+    the model with ``modelscope.snapshot_download`` (v10_triton_paged_gqa/llm.py:9, 34), which
+    is not installed here and needs the network, so the arm reports itself unavailable."""
+    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    try:
+        from torchlet.v10_triton_paged_gqa.llm import LLM  # noqa: F401
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"impl": "reference",
+                          "unavailable": f"the reference's LLM cannot be imported: {type(exc).__name__}: {exc}"}))
+        return 0
+    print(json.dumps({"impl": "reference", "unavailable": "the reference's LLM(model_id) downloads the model with "
+                      "modelscope from the network; there is no network and no local model of it here"}))
+    return 0
+
+
+def main() -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--gpus", type=int, default=1)
+    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--warmup", type=int, default=8)
+    parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=4096)
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
+    parser.add_argument("--skip-points", action="store_true", help="leave out prefill, batch 1/64 and e2e")
+    args = parser.parse_args()
+    if args.gpus != 1:
+        print("bench.py: this engine runs on one GPU only; --gpus must be 1")
+        return 2
+    if args.impl == "reference":
+        return reference_arm(args)
+    if args.warmup < 3:
+        args.warmup = 3
+
+    import torch
+
+    from torchlet_b200 import ops
+
+    cfg = QWEN25_7B
+    layers = args.layers or cfg["num_hidden_layers"]
+    peaks, peak_source = load_peaks()
+    read_params, kv_per_token, prefill_flops = model_numbers(cfg, layers)
+    model = build_model(cfg, layers, seed=4)
+
+    clock = ClockSampler()
+    main_run = time_decode(model, args.batch, args.context, args.steps, args.warmup, clock)
+    wait_error = ops.gemm_tc_error()
+    weight_bytes = read_params * 2
+    step_bytes = weight_bytes + kv_per_token * main_run["mean_context"] * args.batch
+    achieved = step_bytes / (main_run["ms_per_step"] / 1e3) / 1e9
+    record = {
+        "metric": "decode tok/s @ batch 8 (Qwen2.5-7B layer sizes, bf16)" if args.batch == 8
+        else f"decode tok/s @ batch {args.batch} (Qwen2.5-7B layer sizes, bf16)",
+        "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
+        "config": {
+            "model": "Qwen2.5-7B layer sizes, random weights seed 4", "global_batch": args.batch,
+            "seq_len": args.context, "parallelism": "single GPU", "layers": layers,
+            "layers_of_configuration": cfg["num_hidden_layers"], "hidden_size": cfg["hidden_size"],
+            "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
+            "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": 128, "vocab_size": cfg["vocab_size"],
+            "kv_page_size": 16, "prefill_tokens": 2048, "cuda_graph": True,
+            "l2": "each step reads 15 GB of weights, larger than L2; no flush",
+            "context": "cached keys/values are seeded random numbers",
+        },
+        "gpu_launches": main_run["launches"],
+        "clocks": main_run["clocks"],
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peak_source,
+                     "bytes_per_step": int(step_bytes)},
+    }
+    if wait_error:
+        record["kernel_wait_error"] = wait_error
+    if not args.skip_points:
+        prefill_ms = time_prefill(model, 2048, repeats=3)
+        flops = prefill_flops(2048)
+        record["prefill"] = {"value": round(2048 / (prefill_ms / 1e3), 1), "tokens": 2048, "ms": round(prefill_ms, 3),
+                             "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
+                             "tflops": round(flops / (prefill_ms / 1e3) / 1e12, 1), "peak_tflops": peaks["bf16_tflops"]}
+        points = {}
+        for batch in (1, 64):
+            run = time_decode(model, batch, args.context, min(args.steps, 64), args.warmup)
+            points[f"decode_b{batch}"] = round(run["tok_s"], 1)
+            bytes_b = weight_bytes + kv_per_token * run["mean_context"] * batch
+            points[f"decode_b{batch}_hbm_frac"] = round(bytes_b / (run["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+        record["points"] = points
+        e2e = time_e2e(model, args.batch, args.context, args.steps, args.warmup)
+        record["e2e"] = {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d_bytes"],
+                         "d2h_bytes_per_step": e2e["d2h_bytes"], "ms_per_step": round(e2e["ms_per_step"], 4),
+                         "graph_steps": e2e["graph_steps"]}
+    print(json.dumps(record))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -282,9 +282,11 @@ class ModelRunner:
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            launched = ops.launch_count
             with torch.cuda.graph(graph):
                 body()
-        state = {"layout": layout, "words": words, "dev": dev, "graph": graph, "logits": logits, "tokens": tokens,
+            launched = ops.launch_count - launched
+        state = {"kernels": launched, "layout": layout, "words": words, "dev": dev, "graph": graph, "logits": logits, "tokens": tokens,
                  "template": host}
         self._graphs[b] = state
         return state
@@ -326,6 +328,7 @@ class ModelRunner:
             self._meta_event[turn] = torch.cuda.Event()
         self._meta_event[turn].record()
         state["graph"].replay()
+        ops.launch_count += state["kernels"]
         for e, length in zip(entries, before):
             cache.advance(e.request_id, int(length) + 1)
         self.steps_run += 1

@@ -64,6 +64,24 @@ class LLM:
         self.engine = Engine(self.model, self.engine_config)
         logger.info("engine ready: %s", self.engine_config)
 
+    @classmethod
+    def from_model(cls, model, max_decode_slots: int = 4, kv_block_size: int = 16,
+                   max_num_blocks: Optional[int] = None, max_seq_len: Optional[int] = None,
+                   max_num_batched_tokens: int = 2048, cuda_graph: bool = True, device: str = "cuda:0") -> "LLM":
+        """An ``LLM`` around a model that is already on the device (no folder, no tokenizer)."""
+        from .engine.engine import Engine
+
+        self = cls.__new__(cls)
+        dtype = "bfloat16" if str(model.dtype).endswith("bfloat16") else "float32"
+        self.model_dir, self.model, self.config = None, model, getattr(model, "config", None)
+        self.engine_config = EngineConfig(
+            dtype=dtype, max_decode_slots=max_decode_slots, kv_block_size=kv_block_size,
+            max_num_blocks=max_num_blocks, max_seq_len=max_seq_len,
+            max_num_batched_tokens=max_num_batched_tokens, cuda_graph=cuda_graph, device=device)
+        self.tokenizer, self.stop_ids = None, set()
+        self.engine = Engine(self.model, self.engine_config)
+        return self
+
     def _encode(self, prompts: Sequence[str]) -> list:
         if self.tokenizer is None:
             raise ValueError("text prompts need tokenizer files in the model folder; pass token ids instead")

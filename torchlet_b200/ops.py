@@ -76,8 +76,13 @@ def _fn(library: str, name: str):
     return fn
 
 
-def _check(code: int, what: str) -> None:
+launch_count = 0  # kernels launched through this module (graph replays are counted by the runner)
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
+    global launch_count
     if code == 0:
+        launch_count += kernels
         return
     if code == _UNSUPPORTED:
         raise KernelError(f"{what}: sizes or types not supported by this kernel")
@@ -224,10 +229,11 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16) -> None:
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
     need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, None, None)
     ws = _workspace(x.device, need) if need else None
+    kernels = 2 if need else 1  # swapped orientation: product + split-K finish
     code = _fn("gemm_tc", "tl_gemm_tc")(
         x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), epilogue, M, N, K, x.stride(0),
         w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
-    _check(code, "gemm_tc")
+    _check(code, "gemm_tc", kernels)
 
 
 def gemm_tc_error() -> int:
@@ -249,4 +255,4 @@ def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile
         req_indptr.data_ptr(), kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles, out.data_ptr(),
         out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale), 1 if rows16 else 0, splits,
         _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
-    _check(code, "attention_mma")
+    _check(code, "attention_mma", 2 if splits > 1 else 1)

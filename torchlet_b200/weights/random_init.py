@@ -17,20 +17,23 @@ from ..parts import expected_tensors
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
 
 
-def random_tensors(config, seed: int, std: float = 0.02, norm_std: float = 0.0, dtype="bfloat16") -> dict:
+def random_tensors(config, seed: int, std: float = 0.02, norm_std: float = 0.0, dtype="bfloat16",
+                   device="cpu") -> dict:
+    """Tensors by name.  ``device``: where they are drawn and left (a CUDA device draws
+    other numbers than the CPU for the same seed; large models are drawn there)."""
     torch_dtype = _DTYPES[dtype] if isinstance(dtype, str) else dtype
     spec = config.model_spec()
-    generator = torch.Generator(device="cpu").manual_seed(int(seed))
+    generator = torch.Generator(device=device).manual_seed(int(seed))
     tensors = {}
     for want in expected_tensors(spec):
         if want.optional:  # tied LM head: not stored
             continue
         if want.init == "ones":
-            value = torch.ones(want.shape, dtype=torch.float32)
+            value = torch.ones(want.shape, dtype=torch.float32, device=device)
             if norm_std:
-                value += torch.randn(want.shape, generator=generator, dtype=torch.float32) * norm_std
+                value += torch.randn(want.shape, generator=generator, dtype=torch.float32, device=device) * norm_std
         else:
-            value = torch.randn(want.shape, generator=generator, dtype=torch.float32) * std
+            value = torch.randn(want.shape, generator=generator, dtype=torch.float32, device=device) * std
         tensors[want.name] = value.to(torch_dtype)
     return tensors
 
