@@ -354,3 +354,59 @@ def test_temperature_sampling_follows_the_distribution():
                torch.arange(rows, dtype=torch.int32, device=DEV))
     freq = torch.bincount(out.long().cpu(), minlength=5).float() / rows
     assert (freq - probs).abs().max() < 0.03
+
+
+def test_fused_finishing_kernels_equal_the_separate_ones():
+    """finish_qkv_rope and finish_accum_norm against split finish + rope_kv / rms_norm."""
+    ops = _ops()
+    nh, nkv, d, page, T, H = 6, 2, 64, 16, 5, 6 * 64
+    x = randn(T, H, dtype=torch.bfloat16)
+    w = randn((nh + 2 * nkv) * d, H, dtype=torch.bfloat16, scale=0.1, seed=1)
+    bias = randn((nh + 2 * nkv) * d, seed=2)
+    positions = torch.tensor([0, 17, 300, 5, 64], dtype=torch.int32, device=DEV)
+    token_req = torch.tensor([0, 0, 1, 2, 2], dtype=torch.int32, device=DEV)
+    table = (torch.arange(3 * 20, dtype=torch.int32).view(3, 20) + 1).to(DEV)
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).to(DEV)
+    pages_a = torch.zeros(62, 2, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    pages_b = torch.zeros_like(pages_a)
+    qkv_a = torch.zeros(T, (nh + 2 * nkv) * d, dtype=torch.bfloat16, device=DEV)
+    ops.gemm_tc(x, w, qkv_a, bias, ops.EPI_STORE_BF16)
+    ops.rope_kv(qkv_a, positions, token_req, table, pages_a, inv_freq, nh, nkv, d, page)
+    partials, splits = ops.gemm_tc_deferred(x, w)
+    qkv_b = torch.zeros_like(qkv_a)
+    ops.finish_qkv_rope(partials, splits, bias, qkv_b, positions, token_req, table, pages_b, inv_freq, nh, nkv, d, page)
+    assert torch.equal(qkv_a[:, : nh * d], qkv_b[:, : nh * d]) and torch.equal(pages_a, pages_b)
+
+    wo = randn(H, H, dtype=torch.bfloat16, scale=0.1, seed=3)
+    norm_w = randn(H, seed=4) * 0.1 + 1
+    acc_a = randn(T, H, seed=5)
+    acc_b = acc_a.clone()
+    ops.gemm_tc(x, wo, acc_a, None, ops.EPI_ACCUM_F32)
+    out_a = torch.zeros(T, H, dtype=torch.bfloat16, device=DEV)
+    ops.rms_norm(acc_a, norm_w, 1e-6, out_a)
+    partials, splits = ops.gemm_tc_deferred(x, wo)
+    out_b = torch.zeros_like(out_a)
+    ops.finish_accum_norm(partials, splits, None, acc_b, norm_w, 1e-6, out_b)
+    assert (acc_a - acc_b).abs().max() <= 1e-5 * acc_a.abs().max()
+    assert (out_a.float() - out_b.float()).abs().max() <= 1e-2 * out_a.float().abs().max()
+    assert ops.gemm_tc_error() == 0
+
+
+def test_sampling_over_a_vocabulary_scanned_by_several_blocks():
+    ops = _ops()
+    vocab = 20011  # three chunks of 8192, the last one short
+    logits = randn(5, vocab, scale=2.0, seed=9)
+    logits[0, 8191] = logits[0, 8192] = 40.0  # a tie across a chunk edge: the lower index wins
+    logits[1, vocab - 1] = 41.0
+    out = torch.zeros(5, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out)
+    assert out.tolist() == logits.cpu().argmax(-1).tolist() and out[0] == 8191 and out[1] == vocab - 1
+    temperature = torch.tensor([0.9, 0.0, 1.5, 0.6, 1.0], device=DEV)
+    seed = torch.tensor([3, 4, 5, 6, 7], dtype=torch.int64, device=DEV)
+    counter = torch.tensor([0, 1, 2, 3, 4], dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, temperature, seed, counter)
+    host = logits.cpu()
+    for r in (2, 3, 4):
+        scores = plain_model.temperature_scores(host[r], float(temperature[r]), int(seed[r]), int(counter[r]))
+        assert scores[int(out[r])] >= max(scores) - 1e-3
+    assert out[1] == vocab - 1

@@ -47,6 +47,7 @@ struct Params {
   float* part_acc;  // [tokens*nh][splits][D]   (splits > 1)
   float* part_ml;   // [tokens*nh][splits][2]
   int nh, nkv, page_size, window, splits;
+  int page_shift;  // log2(page_size) when it is a power of two, else -1
   float scale_log2;  // scale * log2(e)
 };
 
@@ -94,18 +95,35 @@ template <int D> __device__ __forceinline__ __nv_bfloat16* tile_at(__nv_bfloat16
 template <int D>
 __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, int kvh, int key0, int lo_key,
                                              int hi_key, __nv_bfloat16* ks, __nv_bfloat16* vs) {
-  constexpr int CHUNKS = D / 8;
+  constexpr int CHUNKS = D / 8;                   // 16-byte chunks in a row
+  constexpr int ROWS_PER_PASS = THREADS / CHUNKS;  // each thread keeps its chunk column
+  constexpr int PASSES = BLOCK_N / ROWS_PER_PASS;
   const size_t page_elems = (size_t)2 * p.nkv * p.page_size * D;
   const size_t v_off = (size_t)p.nkv * p.page_size * D;
-  for (int i = threadIdx.x; i < BLOCK_N * CHUNKS; i += THREADS) {
-    const int r = i / CHUNKS, c = i % CHUNKS;
-    const int key = key0 + r;
+  const int c = threadIdx.x % CHUNKS, r0 = threadIdx.x / CHUNKS;
+  // first the page of every row (independent loads), then the copies
+  int page[PASSES], slot[PASSES];
+#pragma unroll
+  for (int k = 0; k < PASSES; ++k) {
+    const int key = key0 + r0 + k * ROWS_PER_PASS;
     const bool valid = key >= lo_key && key <= hi_key;
-    const __nv_bfloat16* src = p.pages;
-    if (valid) {
-      const int page = table[key / p.page_size];
-      src = p.pages + (size_t)page * page_elems + ((size_t)kvh * p.page_size + key % p.page_size) * D + c * 8;
+    int index, within;
+    if (p.page_shift >= 0) {
+      index = key >> p.page_shift;
+      within = key & (p.page_size - 1);
+    } else {
+      index = key / p.page_size;
+      within = key - index * p.page_size;
     }
+    page[k] = valid ? table[index] : -1;
+    slot[k] = within;
+  }
+#pragma unroll
+  for (int k = 0; k < PASSES; ++k) {
+    const int r = r0 + k * ROWS_PER_PASS;
+    const bool valid = page[k] >= 0;
+    const __nv_bfloat16* src = p.pages;
+    if (valid) src = p.pages + (size_t)page[k] * page_elems + ((size_t)kvh * p.page_size + slot[k]) * D + c * 8;
     cp_async_16(tile_at<D>(ks, r, c), src, valid);
     cp_async_16(tile_at<D>(vs, r, c), valid ? src + v_off : src, valid);
   }
@@ -369,33 +387,43 @@ attention_mma_kernel(const Params p) {
   }
 }
 
-// Merges the key splits of every (token, head): one warp each.
+// Merges the key splits of every (token, head): one block of D threads each, thread c
+// owning output element c.  The first threads turn each split's max into its weight.
 template <int D>
-__global__ void attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                         __nv_bfloat16* __restrict__ out, long long out_stride, int items, int nh,
-                                         int splits) {
-  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (item >= items) return;
-  float m_all = -INFINITY;
-  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, part_ml[((size_t)item * splits + s) * 2]);
-  const float m_ref = m_all == -INFINITY ? 0.f : m_all;
-  float l = 0.f;
-  float acc[D / 32];
-#pragma unroll
-  for (int c = 0; c < D / 32; ++c) acc[c] = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    const size_t base = (size_t)item * splits + s;
-    const float f = exp2f(part_ml[base * 2] - m_ref);
-    l += part_ml[base * 2 + 1] * f;
-#pragma unroll
-    for (int c = 0; c < D / 32; ++c) acc[c] += part_acc[base * D + lane + 32 * c] * f;
+__global__ void __launch_bounds__(D)
+attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                         __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int splits) {
+  __shared__ float weight[64];
+  __shared__ float total[2];
+  const int item = blockIdx.x, c = threadIdx.x;
+  const float* ml = part_ml + (size_t)item * splits * 2;
+  if (c < 32) {  // splits <= 64: two per lane
+    const float m0 = c < splits ? ml[2 * c] : -INFINITY;
+    const float m1 = c + 32 < splits ? ml[2 * (c + 32)] : -INFINITY;
+    const float m_all = tl::warp_max(fmaxf(m0, m1));
+    const float m_ref = m_all == -INFINITY ? 0.f : m_all;
+    const float f0 = c < splits ? exp2f(m0 - m_ref) : 0.f;
+    const float f1 = c + 32 < splits ? exp2f(m1 - m_ref) : 0.f;
+    weight[c] = f0;
+    weight[c + 32] = f1;
+    float l = (c < splits ? ml[2 * c + 1] * f0 : 0.f) + (c + 32 < splits ? ml[2 * (c + 32) + 1] * f1 : 0.f);
+    l = tl::warp_sum(l);
+    if (c == 0) total[0] = l;
   }
-  const int token = item / nh, head = item % nh;
-  const float inv = 1.f / l;
+  __syncthreads();
+  const float* src = part_acc + (size_t)item * splits * D + c;
+  float acc = 0.f;
+  int s = 0;
+  for (; s + 8 <= splits; s += 8) {
+    float v[8];
 #pragma unroll
-  for (int c = 0; c < D / 32; ++c)
-    out[(size_t)token * out_stride + (size_t)head * D + lane + 32 * c] = __float2bfloat16_rn(acc[c] * inv);
+    for (int j = 0; j < 8; ++j) v[j] = src[(size_t)(s + j) * D];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc = fmaf(v[j], weight[s + j], acc);
+  }
+  for (; s < splits; ++s) acc = fmaf(src[(size_t)s * D], weight[s], acc);
+  const int token = item / nh, head = item % nh;
+  out[(size_t)token * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / total[0]);
 }
 
 template <int D, bool ROWS16>
@@ -434,7 +462,7 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, const
   if (tiles <= 0 || tokens <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 2)
     return TL_ERR_UNSUPPORTED;
-  if (splits < 1 || (!rows16 && splits != 1) || nkv > 65535 || splits > 65535) return TL_ERR_UNSUPPORTED;
+  if (splits < 1 || (!rows16 && splits != 1) || nkv > 65535 || splits > 64) return TL_ERR_UNSUPPORTED;
   if (tl_attention_mma_workspace(tokens, nh, d, splits) > workspace_bytes) return TL_ERR_UNSUPPORTED;
   Params p;
   p.q = (const __nv_bfloat16*)q;
@@ -453,6 +481,9 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, const
   p.nh = nh;
   p.nkv = nkv;
   p.page_size = page_size;
+  p.page_shift = -1;
+  for (int b = 0; b < 20; ++b)
+    if ((1 << b) == page_size) p.page_shift = b;
   p.window = window;
   p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -464,11 +495,9 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, const
   if (rc || splits == 1) return rc;
   const int items = tokens * nh;
   if (d == 128)
-    attention_combine_kernel<128><<<(items + 3) / 4, 128, 0, stream>>>(p.part_acc, p.part_ml, p.out, out_stride,
-                                                                        items, nh, splits);
+    attention_combine_kernel<128><<<items, 128, 0, stream>>>(p.part_acc, p.part_ml, p.out, out_stride, nh, splits);
   else
-    attention_combine_kernel<64><<<(items + 3) / 4, 128, 0, stream>>>(p.part_acc, p.part_ml, p.out, out_stride, items,
-                                                                       nh, splits);
+    attention_combine_kernel<64><<<items, 64, 0, stream>>>(p.part_acc, p.part_ml, p.out, out_stride, nh, splits);
   return TL_LAUNCH_CHECK();
 }
 

@@ -29,21 +29,34 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
 // row(r) = rows ? rows[r] : r.  One block per row; the order of the additions
 // depends only on the width, never on which other rows are in the batch.
 template <typename T, int NT>
-__global__ void rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w,
-                                const int* __restrict__ rows, T* __restrict__ out, int hidden,
-                                float eps) {
+__global__ void __launch_bounds__(NT)
+rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w, const int* __restrict__ rows,
+                T* __restrict__ out, int hidden, float eps) {
   __shared__ float scratch[32];
+  constexpr int PER = 8;  // elements a thread keeps in registers; longer rows are re-read
   const int r = blockIdx.x;
   const float* x = acc + (size_t)(rows ? rows[r] : r) * hidden;
+  float v[PER];
   float ss = 0.f;
-  for (int j = threadIdx.x; j < hidden; j += NT) {
-    const float v = x[j];
-    ss = fmaf(v, v, ss);
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int j = threadIdx.x + k * NT;
+    v[k] = j < hidden ? x[j] : 0.f;
+    ss = fmaf(v[k], v[k], ss);
+  }
+  for (int j = threadIdx.x + PER * NT; j < hidden; j += NT) {
+    const float e = x[j];
+    ss = fmaf(e, e, ss);
   }
   ss = block_sum<NT>(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps);
   T* o = out + (size_t)r * hidden;
-  for (int j = threadIdx.x; j < hidden; j += NT) o[j] = from_float<T>(x[j] * inv * w[j]);
+#pragma unroll
+  for (int k = 0; k < PER; ++k) {
+    const int j = threadIdx.x + k * NT;
+    if (j < hidden) o[j] = from_float<T>(v[k] * inv * w[j]);
+  }
+  for (int j = threadIdx.x + PER * NT; j < hidden; j += NT) o[j] = from_float<T>(x[j] * inv * w[j]);
 }
 
 // ------------------------------------------------- rotary + cache page write
@@ -120,10 +133,18 @@ int tl_embed(const void* table, int dtype, const int* ids, float* acc, int token
 int tl_rms_norm(const float* acc, const float* weight, const int* rows, void* out, int out_dtype,
                 int num_rows, int hidden, float eps, cudaStream_t stream) {
   if (num_rows <= 0) return 0;
-  if (out_dtype == TL_DTYPE_F32)
-    rms_norm_kernel<float, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (float*)out, hidden, eps);
-  else
-    rms_norm_kernel<__nv_bfloat16, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+  // the block size depends on the width alone, so a row's sum never depends on the batch
+  if (hidden <= 2048) {
+    if (out_dtype == TL_DTYPE_F32)
+      rms_norm_kernel<float, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (float*)out, hidden, eps);
+    else
+      rms_norm_kernel<__nv_bfloat16, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+  } else {
+    if (out_dtype == TL_DTYPE_F32)
+      rms_norm_kernel<float, 512><<<num_rows, 512, 0, stream>>>(acc, weight, rows, (float*)out, hidden, eps);
+    else
+      rms_norm_kernel<__nv_bfloat16, 512><<<num_rows, 512, 0, stream>>>(acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+  }
   return TL_LAUNCH_CHECK();
 }
 

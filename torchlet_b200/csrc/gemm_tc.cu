@@ -215,17 +215,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 #pragma unroll
         for (int j = 16; j < 32; ++j) v[j] = 0.f;
       }
-      if (row >= p.rows || num_kb <= 0) continue;
+      const bool live = row < p.rows && num_kb > 0;
       if constexpr (SWAP) {
-        // row = weight row n, columns = tokens m; partial[split][m][n]
-        float* dst = p.partial + ((size_t)blockIdx.z * p.cols) * p.rows + row;
+        // row = weight row n, columns = tokens m
+        if (p.partial != nullptr) {  // partial[split][m][n]; the finishing kernel adds the splits
+          if (live) {
+            float* dst = p.partial + ((size_t)blockIdx.z * p.cols) * p.rows + row;
 #pragma unroll
-        for (int j = 0; j < CHUNK; ++j) {
-          const int m = col0 + c + j;
-          if (m < p.cols) dst[(size_t)m * p.rows] = v[j];
+            for (int j = 0; j < CHUNK; ++j) {
+              const int m = col0 + c + j;
+              if (m < p.cols) dst[(size_t)m * p.rows] = v[j];
+            }
+          }
+        } else if (p.epilogue == EPI_SWIGLU_BF16) {
+          // lanes 0-15 hold gate rows, lanes 16-31 the matching up rows (interleave of 16)
+          const int out_col = ((row0 + quarter * 32) >> 1) + lane;
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) {
+            const float up = __shfl_down_sync(0xffffffffu, v[j], 16);
+            const int m = col0 + c + j;
+            if (live && lane < 16 && m < p.cols)
+              ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_col] = __float2bfloat16_rn(silu(v[j]) * up);
+          }
+        } else if (live) {
+          const float b = p.bias ? p.bias[row] : 0.f;
+#pragma unroll
+          for (int j = 0; j < CHUNK; ++j) {
+            const int m = col0 + c + j;
+            if (m >= p.cols) break;
+            const float r = v[j] + b;
+            if (p.epilogue == EPI_STORE_BF16)
+              ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + row] = __float2bfloat16_rn(r);
+            else if (p.epilogue == EPI_ACCUM_F32)
+              ((float*)p.out)[(size_t)m * p.ldo + row] += r;
+            else
+              ((float*)p.out)[(size_t)m * p.ldo + row] = r;
+          }
         }
       } else {
-        epilogue_chunk(p, row, col0 + c, v);
+        if (live) epilogue_chunk(p, row, col0 + c, v);
       }
     }
   }
@@ -383,13 +411,15 @@ int tl_gemm_tc_error() {
   return value;
 }
 
+// defer != 0 (swapped orientation only): leave the float32 partials [splits][M][N] in the
+// workspace for a fused finishing kernel of the caller; *splits_out gets their number.
 // out (+)= x[M, K] . w[N, K]^T.  x and w bfloat16 with K contiguous, ldx/ldw elements
 // between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
 // 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
 // [M, N/2], 3 float32 out.  workspace: float32 scratch of at least tl_gemm_tc_plan bytes.
 int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long long ldo, int epilogue, int M,
-               int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes,
-               cudaStream_t stream) {
+               int N, int K, long long ldx, long long ldw, void* workspace, long long workspace_bytes, int defer,
+               int* splits_out, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || K % 8 || ldx % 8 || ldw % 8 || epilogue < 0 || epilogue > 3) return TL_ERR_UNSUPPORTED;
   if (epilogue == EPI_SWIGLU_BF16 && (N % 32 || bias)) return TL_ERR_UNSUPPORTED;
@@ -401,11 +431,18 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   p.out = out;
   p.ldo = ldo;
   p.epilogue = epilogue;
-  p.partial = (float*)workspace;
+  p.partial = nullptr;
+  if (splits_out) *splits_out = 0;
   CUtensorMap map_row, map_col;
   int rc;
+  if (!plan.swap && defer) return TL_ERR_UNSUPPORTED;
   if (plan.swap) {
-    if ((long long)plan.splits * M * N * 4 > workspace_bytes) return TL_ERR_UNSUPPORTED;
+    // one split writes its output directly; several (or a deferred finish) go through partials
+    const bool partials = plan.splits > 1 || defer;
+    if (partials) {
+      if ((long long)plan.splits * M * N * 4 > workspace_bytes) return TL_ERR_UNSUPPORTED;
+      p.partial = (float*)workspace;
+    }
     p.rows = N;
     p.cols = M;
     if (!cached_map(&map_row, w, N, K, ldw, BLOCK_P) || !cached_map(&map_col, x, M, K, ldx, plan.block_q))
@@ -418,7 +455,11 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
       case 128: rc = launch<128, 6, true>(map_row, map_col, p, grid, stream); break;
       default: rc = launch<256, 4, true>(map_row, map_col, p, grid, stream); break;
     }
-    if (rc) return rc;
+    if (rc || !partials) return rc;
+    if (defer) {
+      if (splits_out) *splits_out = plan.splits;
+      return 0;
+    }
     const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
     const long long total = (long long)M * out_cols;
     splitk_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p.partial, plan.splits, M, N, bias,

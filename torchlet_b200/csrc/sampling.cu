@@ -28,36 +28,26 @@ __device__ __forceinline__ float uniform_for(unsigned long long key, int index) 
 }
 
 constexpr int NT = 1024;
+constexpr int CHUNK = 8192;  // vocabulary entries one block scans when a row is split
 
-__global__ void __launch_bounds__(NT)
-sample_kernel(const float* __restrict__ logits, size_t row_stride, int vocab,
-              const float* __restrict__ temperature, const long long* __restrict__ seed,
-              const int* __restrict__ counter, int* __restrict__ out) {
+struct Best {
+  float value;
+  int index;
+};
+
+__device__ __forceinline__ bool better(float v, int i, float bv, int bi) {
+  return v > bv || (v == bv && i < bi);
+}
+
+// Best (value, lowest index) over a block; valid in thread 0.
+__device__ __forceinline__ Best block_best(float bv, int bi) {
   __shared__ float best_v[NT / 32];
   __shared__ int best_i[NT / 32];
-  const int r = blockIdx.x;
-  const float* row = logits + (size_t)r * row_stride;
-  const float temp = temperature ? temperature[r] : 0.f;
-  unsigned long long key = 0;
-  if (temp > 0.f)
-    key = mix64((unsigned long long)seed[r] * 0x9E3779B97F4A7C15ull + (unsigned long long)counter[r] +
-                0x632BE59BD9B4E019ull);
-  const float inv_temp = temp > 0.f ? 1.f / temp : 1.f;
-  float bv = -INFINITY;
-  int bi = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += NT) {
-    float v = row[i];
-    if (temp > 0.f) v = v * inv_temp - logf(-logf(uniform_for(key, i)));
-    if (v > bv || (v == bv && i < bi) || bi == 0x7fffffff) {
-      bv = v;
-      bi = i;
-    }
-  }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
     const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-    if (ov > bv || (ov == bv && oi < bi)) {
+    if (better(ov, oi, bv, bi)) {
       bv = ov;
       bi = oi;
     }
@@ -69,28 +59,104 @@ sample_kernel(const float* __restrict__ logits, size_t row_stride, int vocab,
   }
   __syncthreads();
   if (warp == 0) {
-    bv = best_v[lane];
-    bi = best_i[lane];
+    const int warps = blockDim.x >> 5;
+    bv = lane < warps ? best_v[lane] : -INFINITY;
+    bi = lane < warps ? best_i[lane] : 0x7fffffff;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
       const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-      if (ov > bv || (ov == bv && oi < bi)) {
+      if (better(ov, oi, bv, bi)) {
         bv = ov;
         bi = oi;
       }
     }
-    if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
   }
+  return Best{bv, bi};
+}
+
+// Block (row r, chunk c) scans vocabulary entries [c * span, (c + 1) * span) of row r.
+// gridDim.y == 1: writes the token; else writes its best to scratch[r][c].
+__global__ void __launch_bounds__(NT)
+sample_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, int span,
+              const float* __restrict__ temperature, const long long* __restrict__ seed,
+              const int* __restrict__ counter, int* __restrict__ out, Best* __restrict__ scratch) {
+  const int r = blockIdx.x;
+  const float* row = logits + (size_t)r * row_stride;
+  const float temp = temperature ? temperature[r] : 0.f;
+  unsigned long long key = 0;
+  if (temp > 0.f)
+    key = mix64((unsigned long long)seed[r] * 0x9E3779B97F4A7C15ull + (unsigned long long)counter[r] +
+                0x632BE59BD9B4E019ull);
+  const float inv_temp = temp > 0.f ? 1.f / temp : 1.f;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  const int begin = blockIdx.y * span, end = min(vocab, begin + span);
+  for (int i = begin + threadIdx.x; i < end; i += NT) {
+    float v = row[i];
+    if (temp > 0.f) v = v * inv_temp - logf(-logf(uniform_for(key, i)));
+    if (better(v, i, bv, bi) || bi == 0x7fffffff) {
+      bv = v;
+      bi = i;
+    }
+  }
+  const Best best = block_best(bv, bi);
+  if (threadIdx.x == 0) {
+    if (gridDim.y == 1)
+      out[r] = best.index == 0x7fffffff ? 0 : best.index;
+    else
+      scratch[(size_t)r * gridDim.y + blockIdx.y] = best;
+  }
+}
+
+__global__ void sample_merge_kernel(const Best* __restrict__ scratch, int chunks, int* __restrict__ out) {
+  const int r = blockIdx.x, lane = threadIdx.x;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int c = lane; c < chunks; c += 32) {
+    const Best b = scratch[(size_t)r * chunks + c];
+    if (better(b.value, b.index, bv, bi)) {
+      bv = b.value;
+      bi = b.index;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (better(ov, oi, bv, bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if (lane == 0) out[r] = bi == 0x7fffffff ? 0 : bi;
 }
 
 }  // namespace
 
-extern "C" int tl_sample(const float* logits, long long row_stride, int rows, int vocab,
-                         const float* temperature, const long long* seed, const int* counter,
-                         int* out, cudaStream_t stream) {
+extern "C" {
+
+// Bytes of scratch that let a row be scanned by several blocks (0: one block a row).
+long long tl_sample_scratch_bytes(int rows, int vocab) {
+  const int chunks = (vocab + CHUNK - 1) / CHUNK;
+  return chunks > 1 ? (long long)rows * chunks * (long long)sizeof(Best) : 0;
+}
+
+int tl_sample(const float* logits, long long row_stride, int rows, int vocab, const float* temperature,
+              const long long* seed, const int* counter, int* out, void* scratch, long long scratch_bytes,
+              cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0) return TL_ERR_UNSUPPORTED;
-  sample_kernel<<<rows, NT, 0, stream>>>(logits, (size_t)row_stride, vocab, temperature, seed, counter, out);
+  int chunks = (vocab + CHUNK - 1) / CHUNK;
+  if (chunks > 1 && (!scratch || scratch_bytes < tl_sample_scratch_bytes(rows, vocab))) chunks = 1;
+  if (chunks > 65535) return TL_ERR_UNSUPPORTED;
+  const int span = chunks > 1 ? CHUNK : vocab;
+  sample_kernel<<<dim3(rows, chunks), NT, 0, stream>>>(logits, (size_t)row_stride, vocab, span, temperature, seed,
+                                                      counter, out, (Best*)scratch);
+  int rc = TL_LAUNCH_CHECK();
+  if (rc || chunks == 1) return rc;
+  sample_merge_kernel<<<rows, 32, 0, stream>>>((const Best*)scratch, chunks, out);
   return TL_LAUNCH_CHECK();
 }
+
+}  // extern "C"

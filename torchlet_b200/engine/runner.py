@@ -66,9 +66,28 @@ class StepContext:
         # host copies (numpy int32) for parts that plan on the host
         self.req_indptr_host = self.kv_before_host = self.slots_host = None
         self.plans: dict = {}  # per-step plans parts share across layers
+        # a sum into the residual stream that a product left unfinished for the next norm
+        # to complete: (partials, splits, bias, acc) or None
+        self._pending = None
         # sampling rows of the step (device), None when every sampled row is greedy
         self.num_sampled = 0
         self.sample_temperature = self.sample_seed = self.sample_counter = None
+
+    @property
+    def pending(self):
+        return self._pending
+
+    @pending.setter
+    def pending(self, value) -> None:
+        self._pending = value
+        ops.workspace_holder = self if value is not None else None
+
+    def flush_pending(self) -> None:
+        """Complete an unfinished sum into the residual stream (see ``pending``)."""
+        if self._pending is not None:
+            partials, splits, bias, acc = self._pending
+            self.pending = None
+            ops.finish_accum_norm(partials, splits, bias, acc)
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         return self._runner.buffer(name, shape, dtype)

@@ -48,7 +48,7 @@ _SIGNATURES = {
     },
     "gemm_tc": {
         "tl_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong,
-                       c_longlong, c_void_p, c_longlong, c_void_p],
+                       c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_error": [],
     },
@@ -57,8 +57,15 @@ _SIGNATURES = {
                              c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                              c_int, c_void_p, c_longlong, c_void_p],
     },
+    "decode_fused": {
+        "tl_finish_qkv_rope": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_finish_accum_norm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                                 c_void_p],
+    },
     "sampling": {
-        "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_longlong, c_void_p],
     },
 }
 
@@ -188,21 +195,26 @@ def sample(logits, out, temperature=None, seed=None, counter=None) -> None:
     assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
     if temperature is not None:
         assert temperature.dtype == torch.float32 and seed.dtype == torch.int64 and counter.dtype == torch.int32
+    chunks = -(-vocab // 8192)
+    scratch = _workspace(("sample", logits.device), rows * chunks * 8) if chunks > 1 else None
     code = _fn("sampling", "tl_sample")(
         logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _ptr(counter),
-        out.data_ptr(), _stream())
-    _check(code, "sample")
+        out.data_ptr(), _ptr(scratch), scratch.numel() * 4 if scratch is not None else 0, _stream())
+    _check(code, "sample", 2 if chunks > 1 else 1)
 
 
 # ------------------------------------------------------- tensor-core products
 EPI_STORE_BF16, EPI_ACCUM_F32, EPI_SWIGLU_BF16, EPI_STORE_F32 = 0, 1, 2, 3
 _workspaces: dict = {}
+_outgrown: list = []  # kept alive: captured CUDA graphs may still hold their addresses
 
 
 def _workspace(device, nbytes: int) -> torch.Tensor:
     """A float32 scratch buffer per device that only grows (split-K partial sums)."""
     ws = _workspaces.get(device)
     if ws is None or ws.numel() * 4 < nbytes:
+        if ws is not None:
+            _outgrown.append(ws)
         where = device[1] if isinstance(device, tuple) else device
         ws = torch.empty(max(nbytes // 4 + 1, 1 << 22), dtype=torch.float32, device=where)
         _workspaces[device] = ws
@@ -218,22 +230,79 @@ def gemm_tc_supported(x: torch.Tensor, w: torch.Tensor) -> bool:
             and x.stride(1) == 1 and w.stride(1) == 1)
 
 
+# The step context that holds unfinished partial sums in the shared workspace, if any; it
+# is asked to finish them before another product overwrites the workspace.
+workspace_holder = None
+
+
+def _release_workspace() -> None:
+    if workspace_holder is not None:
+        workspace_holder.flush_pending()
+
+
 def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16) -> None:
     """out (+)= x @ w.T (+ bias) on the tcgen05 tensor cores; see csrc/gemm_tc.cu."""
     _need_cuda(x, w, out, bias)
+    _release_workspace()
     M, K = x.shape
     N = w.shape[0]
     assert w.shape[1] == K and out.stride(1) == 1
     want = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU_BF16) else torch.float32
     assert out.dtype == want and out.shape == (M, N // 2 if epilogue == EPI_SWIGLU_BF16 else N)
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
-    need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, None, None)
+    splits = ctypes.c_int(0)
+    need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, None, ctypes.byref(splits))
     ws = _workspace(x.device, need) if need else None
-    kernels = 2 if need else 1  # swapped orientation: product + split-K finish
+    kernels = 2 if need and splits.value > 1 else 1  # several splits: product + finishing pass
     code = _fn("gemm_tc", "tl_gemm_tc")(
         x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), epilogue, M, N, K, x.stride(0),
-        w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
+        w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, 0, None, _stream())
     _check(code, "gemm_tc", kernels)
+
+
+def gemm_tc_deferred(x, w):
+    """The product x @ w.T left as float32 partial sums ``[splits, M, N]`` for a fused
+    finishing kernel.  Returns (partials, splits), or None when the sizes run in the
+    orientation that writes its output directly (many tokens)."""
+    _need_cuda(x, w)
+    _release_workspace()
+    M, K = x.shape
+    N = w.shape[0]
+    swap = ctypes.c_int(0)
+    need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, ctypes.byref(swap), None)
+    if not swap.value:
+        return None
+    ws = _workspace(x.device, need)
+    splits = ctypes.c_int(0)
+    code = _fn("gemm_tc", "tl_gemm_tc")(
+        x.data_ptr(), w.data_ptr(), None, None, 0, EPI_STORE_F32, M, N, K, x.stride(0), w.stride(0), ws.data_ptr(),
+        ws.numel() * 4, 1, ctypes.byref(splits), _stream())
+    _check(code, "gemm_tc (deferred)")
+    return ws, splits.value
+
+
+def finish_qkv_rope(partials, splits, bias, qkv, positions, token_req, block_table, pages, inv_freq, nh, nkv, d,
+                    page_size, write_kv=True) -> None:
+    """Sum the qkv product's splits (+ bias), rotate q and k, store q to ``qkv`` and k, v to pages."""
+    _need_cuda(partials, bias, qkv, positions, token_req, block_table, pages, inv_freq)
+    assert qkv.dtype == torch.bfloat16 and qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * d
+    code = _fn("decode_fused", "tl_finish_qkv_rope")(
+        partials.data_ptr(), splits, _ptr(bias), qkv.data_ptr(), positions.data_ptr(), token_req.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], pages.data_ptr(), inv_freq.data_ptr(), qkv.shape[0], nh, nkv,
+        d, page_size, 1 if write_kv else 0, _stream())
+    _check(code, "finish_qkv_rope")
+
+
+def finish_accum_norm(partials, splits, bias, acc, weight=None, eps=0.0, out=None) -> None:
+    """acc += sum of the splits (+ bias); with ``out``: out = rmsnorm(acc) * weight (bfloat16)."""
+    _need_cuda(partials, bias, acc, weight, out)
+    tokens, hidden = acc.shape
+    assert acc.dtype == torch.float32 and acc.is_contiguous()
+    assert out is None or (out.dtype == torch.bfloat16 and out.is_contiguous() and out.shape == acc.shape)
+    code = _fn("decode_fused", "tl_finish_accum_norm")(
+        partials.data_ptr(), splits, _ptr(bias), acc.data_ptr(), _ptr(weight), _ptr(out), tokens, hidden,
+        float(eps), _stream())
+    _check(code, "finish_accum_norm")
 
 
 def gemm_tc_error() -> int:

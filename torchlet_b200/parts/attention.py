@@ -80,11 +80,15 @@ class AttentionMixer(Mixer):
     def forward(self, ctx, x, acc, cache) -> None:
         tokens = x.shape[0]
         qkv = ctx.buffer("attention.qkv", (tokens, self.q_size + 2 * self.kv_size), ctx.dtype)
-        self.qkv_proj.forward(x, qkv)
-        if self.positions is not None:
-            self.positions.encode_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, cache)
-        else:
+        if self.positions is None:
             raise NotImplementedError("an attention mixer needs a position encoding that stores k and v")
+        partials = self.qkv_proj.deferred(ctx, x) if getattr(self.positions, "accepts_partials", False) else None
+        if partials is not None:
+            self.positions.encode_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, cache,
+                                            partials=(partials[0], partials[1], self.qkv_proj.bias))
+        else:
+            self.qkv_proj.forward(x, qkv)
+            self.positions.encode_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, cache)
         out = ctx.buffer("attention.out", (tokens, self.q_size), ctx.dtype)
         from . import attention_bf16
 
@@ -92,4 +96,5 @@ class AttentionMixer(Mixer):
             ops.attention_generic(qkv, qkv.stride(0), cache.pages, cache.block_table, ctx.token_req,
                                   ctx.positions, out, tokens, self.num_heads, self.num_kv_heads,
                                   self.head_dim, cache.page_size, self.window, self.scale)
-        self.o_proj.forward(out, acc, accumulate=True)
+        if not self.o_proj.accumulate_later(ctx, out, acc):
+            self.o_proj.forward(out, acc, accumulate=True)

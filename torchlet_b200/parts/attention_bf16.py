@@ -20,9 +20,10 @@ SM_COUNT = 148
 
 
 def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
-    """Key splits so that about two CTAs per SM are busy; never more than one per 256 keys."""
-    want = -(-2 * SM_COUNT // max(1, num_requests * num_kv_heads))
-    return max(1, min(want, -(-max_kv_len // 256), 64))
+    """Key splits of a decode step: short chains of key tiles per CTA (a split of at least
+    128 keys) while the grid stays within about 8 CTAs per SM."""
+    room = max(1, 4 * SM_COUNT // max(1, num_requests * num_kv_heads))
+    return max(1, min(room, -(-max_kv_len // 128), 64))
 
 
 def _plan(ctx, group_size: int):

@@ -29,6 +29,23 @@ class Linear:
         self.weight, self.bias, self.dtype = weight, None, weight.dtype
         return self
 
+    def deferred(self, ctx, x: torch.Tensor):
+        """For few tokens in bfloat16: run the product but leave its split partial sums
+        for a fused finishing kernel.  Returns (partials, splits) or None (not applicable;
+        use ``forward``)."""
+        if self.dtype != torch.bfloat16 or not ops.gemm_tc_supported(x, self.weight):
+            return None
+        return ops.gemm_tc_deferred(x, self.weight)
+
+    def accumulate_later(self, ctx, x: torch.Tensor, acc: torch.Tensor) -> bool:
+        """acc += x W^T + b, with the final sum left to the next norm (``ctx.pending``).
+        False: not applicable, nothing was done."""
+        result = self.deferred(ctx, x)
+        if result is None:
+            return False
+        ctx.pending = (result[0], result[1], self.bias, acc)
+        return True
+
     def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:
         """out (+)= x W^T + b.  ``accumulate`` needs a float32 ``out`` (the residual stream)."""
         if self.dtype == torch.bfloat16:

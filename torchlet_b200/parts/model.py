@@ -108,6 +108,7 @@ class LayeredModel:
         ops.embed(self.embedding, ctx.tokens, acc)
         for i, entry in enumerate(self.spec.schedule):
             self.blocks[entry.layer].forward(ctx, acc, caches[i])
+        ctx.flush_pending()
         return acc
 
     def logits(self, ctx, acc: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:

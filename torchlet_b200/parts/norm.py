@@ -30,5 +30,12 @@ class RMSNorm(Norm):
         count = acc.shape[0] if rows is None else rows.numel()
         if out is None:
             out = ctx.buffer(name, (count, self.size), ctx.dtype)
+        pending = ctx.pending
+        if pending is not None and pending[3] is acc and rows is None and out.dtype == torch.bfloat16:
+            # a product left its last sum into ``acc`` to us: finish it and norm in one kernel
+            ctx.pending = None
+            ops.finish_accum_norm(pending[0], pending[1], pending[2], acc, self.weight, self.eps, out)
+            return out
+        ctx.flush_pending()
         ops.rms_norm(acc, self.weight, self.eps, out, rows)
         return out

@@ -32,6 +32,16 @@ class RotarySplitHalf(Positions):
         i = torch.arange(0, self.head_dim, 2, dtype=torch.float32)
         self.inv_freq = (1.0 / (self.theta ** (i / self.head_dim))).to(device)
 
-    def encode_and_store(self, ctx, qkv, num_heads, num_kv_heads, cache) -> None:
+    accepts_partials = True
+
+    def encode_and_store(self, ctx, qkv, num_heads, num_kv_heads, cache, partials=None) -> None:
+        """``partials``: (float32 split sums, splits, bias) of the qkv product when the
+        mixer left it unfinished; the sum, the bias, the rotation and the store then run as
+        one kernel and ``qkv`` receives the encoded q."""
+        if partials is not None:
+            ops.finish_qkv_rope(partials[0], partials[1], partials[2], qkv, ctx.positions, ctx.token_req,
+                                cache.block_table, cache.pages, self.inv_freq, num_heads, num_kv_heads,
+                                self.head_dim, cache.page_size, write_kv=cache.writable)
+            return
         ops.rope_kv(qkv, ctx.positions, ctx.token_req, cache.block_table, cache.pages, self.inv_freq,
                     num_heads, num_kv_heads, self.head_dim, cache.page_size, write_kv=cache.writable)

@@ -32,5 +32,6 @@ def forward(ffn, ctx, x, acc) -> bool:
     tokens = x.shape[0]
     act = ctx.buffer("swiglu.act", (tokens, ffn.intermediate_size), torch.bfloat16)
     ops.gemm_tc(x, ffn.gate_up_interleaved, act, None, ops.EPI_SWIGLU_BF16)
-    ffn.down_proj.forward(act, acc, accumulate=True)
+    if not ffn.down_proj.accumulate_later(ctx, act, acc):
+        ffn.down_proj.forward(act, acc, accumulate=True)
     return True
