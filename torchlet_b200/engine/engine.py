@@ -38,7 +38,14 @@ class Engine:
             entries = []
             for portion in plan.portions:
                 request = portion.request
-                tokens = request.all_tokens[portion.start:portion.start + portion.length]
+                prompt_len = len(request.prompt_tokens)
+                if portion.start >= prompt_len:  # decoding (or recomputing produced tokens)
+                    first = portion.start - prompt_len
+                    tokens = request.output_tokens[first:first + portion.length]
+                elif portion.start + portion.length <= prompt_len:
+                    tokens = request.prompt_tokens[portion.start:portion.start + portion.length]
+                else:
+                    tokens = request.all_tokens[portion.start:portion.start + portion.length]
                 entries.append(StepEntry(request.request_id, tokens,
                                          sample=scheduler.sample_spec(request) if portion.samples else None))
             result = self.runner.run(entries)

@@ -41,7 +41,7 @@ class RequestState(Enum):
 _arrival = itertools.count()
 
 
-@dataclass
+@dataclass(eq=False)  # requests compare by identity (and list searches stay cheap)
 class Request:
     prompt_tokens: list
     params: SamplingParams = field(default_factory=SamplingParams)
@@ -189,18 +189,22 @@ class Scheduler:
         scheduled: dict = {}  # request_id -> ScheduledPortion, in order
 
         # 1. decoding requests first, one token each (oldest first)
+        prompts_left = False
         for request in list(self.running):
-            if request not in self.running or budget <= 0:
+            if budget <= 0:
+                break
+            if request.state is not RequestState.RUNNING:  # preempted earlier in this loop
                 continue
-            if request.num_tokens - request.num_computed != 1:
+            if len(request.prompt_tokens) + len(request.output_tokens) - request.num_computed != 1:
+                prompts_left = True
                 continue
             if self._reserve(request, 1, scheduled, plan):
                 scheduled[request.request_id] = ScheduledPortion(request, request.num_computed, 1, True)
                 budget -= 1
 
         # 2. portions of requests that are still reading their prompt (or being recomputed)
-        for request in list(self.running):
-            if request not in self.running or budget <= 0 or request.request_id in scheduled:
+        for request in (list(self.running) if prompts_left else ()):
+            if request.state is not RequestState.RUNNING or budget <= 0 or request.request_id in scheduled:
                 continue
             remaining = request.num_tokens - request.num_computed
             length = min(remaining, budget)

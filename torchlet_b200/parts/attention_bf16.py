@@ -20,9 +20,10 @@ SM_COUNT = 148
 
 
 def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
-    """Key splits of a decode step: short chains of key tiles per CTA (a split of at least
-    128 keys) while the grid stays within about 8 CTAs per SM."""
-    room = max(1, 4 * SM_COUNT // max(1, num_requests * num_kv_heads))
+    """Key splits of a decode step: as many as fill ONE wave of CTAs (three are resident per
+    SM), but no split shorter than 128 keys and at most 64 splits."""
+    resident = 3 * SM_COUNT
+    room = max(1, resident // max(1, num_requests * num_kv_heads))
     return max(1, min(room, -(-max_kv_len // 128), 64))
 
 
