@@ -243,9 +243,12 @@ def time_e2e(model, batch: int, context: int, steps: int, warmup: int):
     llm = LLM.from_model(model, max_decode_slots=batch, kv_block_size=page, max_seq_len=context,
                          max_num_blocks=batch * (-(-context // page)) + 1, max_num_batched_tokens=2048)
     engine = llm.engine
-    prompt_len = context - steps - warmup - 1
+    # requests that finish their prompt early decode while the others still read theirs:
+    # leave room so that none reaches its last token inside the timed steps
+    slack = 2 * (batch * context // 2048 + 2)
+    prompt_len = context - steps - warmup - slack - 1
     generator = torch.Generator().manual_seed(5)
-    params = SamplingParams(max_new_tokens=steps + warmup + 1, ignore_eos=True)
+    params = SamplingParams(max_new_tokens=steps + warmup + slack + 1, ignore_eos=True)
     requests = [Request(torch.randint(0, model.spec.vocab_size, (prompt_len,), generator=generator).tolist(),
                         SamplingParams(**vars(params))) for _ in range(batch)]
     engine.add_requests(requests)
@@ -263,6 +266,8 @@ def time_e2e(model, batch: int, context: int, steps: int, warmup: int):
     seconds = time.perf_counter() - start
     produced = sum(len(r.output_tokens) for r in requests) - produced
     graph_steps = engine.runner.graph_steps - graph_before
+    if produced != batch * steps:
+        raise RuntimeError(f"e2e run produced {produced} tokens, expected {batch * steps}")
     words = engine.runner._graphs[engine.runner._bucket(batch)]["words"] if engine.runner._graphs else 0
     engine.scheduler.fail_all(RuntimeError("benchmark over"))
     del llm, engine

@@ -116,7 +116,7 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, c
 }
 
 template <int BLOCK_Q, int STAGES, bool SWAP>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
                const Params p) {
   constexpr int COL_TILE_BYTES = BLOCK_Q * BLOCK_K * 2;
@@ -362,7 +362,8 @@ Plan make_plan(int M, int N, int K) {
   if (plan.swap) {
     plan.block_q = pick_block_q_swapped(M);
     const int tiles = ((N + BLOCK_P - 1) / BLOCK_P) * ((M + plan.block_q - 1) / plan.block_q);
-    int splits = sm_count() / tiles;
+    const int ctas_per_sm = plan.block_q <= 16 ? 3 : (plan.block_q <= 128 ? 2 : 1);
+    int splits = ctas_per_sm * sm_count() / tiles;
     if (splits < 1) splits = 1;
     if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;  // at least 4 k-blocks a split
     plan.k_blocks_per_split = (k_blocks + splits - 1) / splits;
@@ -449,10 +450,12 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
       return TL_ERR_UNSUPPORTED;
     dim3 grid((N + BLOCK_P - 1) / BLOCK_P, (M + plan.block_q - 1) / plan.block_q, plan.splits);
     switch (plan.block_q) {
-      case 16: rc = launch<16, 8, true>(map_row, map_col, p, grid, stream); break;
-      case 32: rc = launch<32, 8, true>(map_row, map_col, p, grid, stream); break;
-      case 64: rc = launch<64, 8, true>(map_row, map_col, p, grid, stream); break;
-      case 128: rc = launch<128, 6, true>(map_row, map_col, p, grid, stream); break;
+      // few stages a CTA, several CTAs an SM: while one CTA starts up or runs its epilogue
+      // the others keep the weight stream going
+      case 16: rc = launch<16, 4, true>(map_row, map_col, p, grid, stream); break;    //  72 KB: 3 CTAs/SM
+      case 32: rc = launch<32, 4, true>(map_row, map_col, p, grid, stream); break;    //  80 KB: 2 CTAs/SM
+      case 64: rc = launch<64, 4, true>(map_row, map_col, p, grid, stream); break;    //  96 KB: 2 CTAs/SM
+      case 128: rc = launch<128, 3, true>(map_row, map_col, p, grid, stream); break;  //  96 KB: 2 CTAs/SM
       default: rc = launch<256, 4, true>(map_row, map_col, p, grid, stream); break;
     }
     if (rc || !partials) return rc;
