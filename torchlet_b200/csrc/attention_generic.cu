@@ -31,6 +31,9 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const int* __restrict__ token_req, const int* __restrict__ positions,
                          T* __restrict__ out, int out_stride, int tokens, int nh, int nkv, int d,
                          int page_size, int window, float scale) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   __shared__ float qs[WARPS][MAX_D];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long item = (long long)blockIdx.x * WARPS + warp;
@@ -113,11 +116,11 @@ extern "C" int tl_attention_generic(const void* q, int q_stride, const void* pag
   const long long items = (long long)tokens * nh;
   const unsigned blocks = (unsigned)((items + WARPS - 1) / WARPS);
   if (dtype == TL_DTYPE_F32)
-    attention_generic_kernel<float><<<blocks, WARPS * 32, 0, stream>>>(
+    tl::launch_kernel(attention_generic_kernel<float>, blocks, WARPS * 32, 0, stream, 
         (const float*)q, q_stride, (const float*)pages, block_table, table_width, token_req,
         positions, (float*)out, out_stride, tokens, nh, nkv, d, page_size, window, scale);
   else
-    attention_generic_kernel<__nv_bfloat16><<<blocks, WARPS * 32, 0, stream>>>(
+    tl::launch_kernel(attention_generic_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_table, table_width,
         token_req, positions, (__nv_bfloat16*)out, out_stride, tokens, nh, nkv, d, page_size, window,
         scale);

@@ -17,7 +17,66 @@
 
 #define TL_LAUNCH_CHECK() ((int)cudaGetLastError())
 
+#include <stdlib.h>
+
 namespace tl {
+
+// ---------------------------------------------------- programmatic dependent launch
+// Kernels are launched with the programmatic-stream-serialization attribute: a kernel
+// may START while its predecessor in the stream is still running, once every CTA of the
+// predecessor has executed pdl_launch_dependents() (or exited).  It must execute
+// pdl_wait() before it touches anything an earlier kernel wrote or still reads; the wait
+// returns when the predecessor has completed and its memory operations are visible.
+// Work that depends on no earlier kernel (barrier set-up, streaming weights) may come
+// before the wait and so overlaps the predecessor's tail.  Every kernel here executes
+// pdl_wait() in every CTA, so completion of a kernel implies completion of all before it.
+// TORCHLET_B200_PDL=0 in the environment launches everything fully serialized.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+inline bool pdl_enabled() {
+  static int enabled = -1;
+  if (enabled < 0) {
+    const char* v = getenv("TORCHLET_B200_PDL");
+    enabled = (v && v[0] == '0') ? 0 : 1;
+  }
+  return enabled == 1;
+}
+
+// ``overlap`` false: this launch waits for the full completion of its predecessor.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_opt(bool overlap, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = (overlap && pdl_enabled()) ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                 Args&&... args) {
+  cudaLaunchConfig_t config = {};
+  config.gridDim = grid;
+  config.blockDim = block;
+  config.dynamicSmemBytes = smem;
+  config.stream = stream;
+  cudaLaunchAttribute attribute[1];
+  attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute[0].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attribute;
+  config.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 v) { return __bfloat162float(v); }

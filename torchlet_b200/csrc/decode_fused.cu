@@ -24,6 +24,9 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ partial, int sp
                                        const int* __restrict__ block_table, int table_width,
                                        __nv_bfloat16* __restrict__ pages, const float* __restrict__ inv_freq,
                                        int tokens, int nh, int nkv, int d, int page_size, int write_kv) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   const int t = blockIdx.x, h = blockIdx.y;
   const int half = d >> 1;
   const int N = (nh + 2 * nkv) * d;
@@ -75,6 +78,9 @@ __global__ void __launch_bounds__(NT)
 finish_accum_norm_kernel(const float* __restrict__ partial, int splits, const float* __restrict__ bias,
                          float* __restrict__ acc, const float* __restrict__ weight,
                          __nv_bfloat16* __restrict__ out, int tokens, int hidden, float eps) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   __shared__ float scratch[32];
   const int t = blockIdx.x;
   const size_t plane = (size_t)tokens * hidden;
@@ -131,7 +137,7 @@ int tl_finish_qkv_rope(const float* partial, int splits, const float* bias, void
   if (heads > 65535) return TL_ERR_UNSUPPORTED;
   int nt = ((d / 2 + 31) / 32) * 32;
   if (nt > 128) nt = 128;
-  finish_qkv_rope_kernel<<<dim3(tokens, heads), nt, 0, stream>>>(
+  tl::launch_kernel(finish_qkv_rope_kernel, dim3(tokens, heads), nt, 0, stream, 
       partial, splits, bias, (__nv_bfloat16*)qkv, positions, token_req, block_table, table_width,
       (__nv_bfloat16*)pages, inv_freq, tokens, nh, nkv, d, page_size, write_kv);
   return TL_LAUNCH_CHECK();
@@ -145,11 +151,11 @@ int tl_finish_accum_norm(const float* partial, int splits, const float* bias, fl
   if (splits < 1 || hidden <= 0) return TL_ERR_UNSUPPORTED;
   __nv_bfloat16* o = (__nv_bfloat16*)out;
   if (hidden <= 1024)
-    finish_accum_norm_kernel<256, 4><<<tokens, 256, 0, stream>>>(partial, splits, bias, acc, weight, o, tokens, hidden, eps);
+    tl::launch_kernel(finish_accum_norm_kernel<256, 4>, tokens, 256, 0, stream, partial, splits, bias, acc, weight, o, tokens, hidden, eps);
   else if (hidden <= 4096)
-    finish_accum_norm_kernel<512, 8><<<tokens, 512, 0, stream>>>(partial, splits, bias, acc, weight, o, tokens, hidden, eps);
+    tl::launch_kernel(finish_accum_norm_kernel<512, 8>, tokens, 512, 0, stream, partial, splits, bias, acc, weight, o, tokens, hidden, eps);
   else if (hidden <= 16384)
-    finish_accum_norm_kernel<1024, 16><<<tokens, 1024, 0, stream>>>(partial, splits, bias, acc, weight, o, tokens, hidden, eps);
+    tl::launch_kernel(finish_accum_norm_kernel<1024, 16>, tokens, 1024, 0, stream, partial, splits, bias, acc, weight, o, tokens, hidden, eps);
   else
     return TL_ERR_UNSUPPORTED;
   return TL_LAUNCH_CHECK();

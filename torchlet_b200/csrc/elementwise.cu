@@ -16,6 +16,9 @@ using namespace tl;
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ acc, int hidden, int vocab) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   const int t = blockIdx.x;
   int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
@@ -32,6 +35,9 @@ template <typename T, int NT>
 __global__ void __launch_bounds__(NT)
 rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w, const int* __restrict__ rows,
                 T* __restrict__ out, int hidden, float eps) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   __shared__ float scratch[32];
   constexpr int PER = 8;  // elements a thread keeps in registers; longer rows are re-read
   const int r = blockIdx.x;
@@ -72,6 +78,9 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
                                const int* __restrict__ block_table, int table_width,
                                T* __restrict__ pages, const float* __restrict__ inv_freq, int nh,
                                int nkv, int d, int page_size, int write_kv) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   const int t = blockIdx.x;
   const int h = blockIdx.y;
   const int half = d >> 1;
@@ -106,6 +115,9 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               size_t total) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / inter;
@@ -124,9 +136,9 @@ int tl_embed(const void* table, int dtype, const int* ids, float* acc, int token
   if (tokens <= 0) return 0;
   const int nt = hidden >= 1024 ? 256 : 128;
   if (dtype == TL_DTYPE_F32)
-    embed_kernel<float><<<tokens, nt, 0, stream>>>((const float*)table, ids, acc, hidden, vocab);
+    tl::launch_kernel(embed_kernel<float>, tokens, nt, 0, stream, (const float*)table, ids, acc, hidden, vocab);
   else
-    embed_kernel<__nv_bfloat16><<<tokens, nt, 0, stream>>>((const __nv_bfloat16*)table, ids, acc, hidden, vocab);
+    tl::launch_kernel(embed_kernel<__nv_bfloat16>, tokens, nt, 0, stream, (const __nv_bfloat16*)table, ids, acc, hidden, vocab);
   return TL_LAUNCH_CHECK();
 }
 
@@ -136,14 +148,14 @@ int tl_rms_norm(const float* acc, const float* weight, const int* rows, void* ou
   // the block size depends on the width alone, so a row's sum never depends on the batch
   if (hidden <= 2048) {
     if (out_dtype == TL_DTYPE_F32)
-      rms_norm_kernel<float, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (float*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<float, 256>, num_rows, 256, 0, stream, acc, weight, rows, (float*)out, hidden, eps);
     else
-      rms_norm_kernel<__nv_bfloat16, 256><<<num_rows, 256, 0, stream>>>(acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<__nv_bfloat16, 256>, num_rows, 256, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
   } else {
     if (out_dtype == TL_DTYPE_F32)
-      rms_norm_kernel<float, 512><<<num_rows, 512, 0, stream>>>(acc, weight, rows, (float*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<float, 512>, num_rows, 512, 0, stream, acc, weight, rows, (float*)out, hidden, eps);
     else
-      rms_norm_kernel<__nv_bfloat16, 512><<<num_rows, 512, 0, stream>>>(acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+      tl::launch_kernel(rms_norm_kernel<__nv_bfloat16, 512>, num_rows, 512, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
   }
   return TL_LAUNCH_CHECK();
 }
@@ -160,11 +172,11 @@ int tl_rope_kv(void* qkv, int dtype, const int* positions, const int* token_req,
   if (nt > 128) nt = 128;
   dim3 grid(tokens, heads);
   if (dtype == TL_DTYPE_F32)
-    rope_kv_kernel<float><<<grid, nt, 0, stream>>>((float*)qkv, positions, token_req, block_table,
+    tl::launch_kernel(rope_kv_kernel<float>, grid, nt, 0, stream, (float*)qkv, positions, token_req, block_table,
                                                    table_width, (float*)pages, inv_freq, nh, nkv, d,
                                                    page_size, write_kv);
   else
-    rope_kv_kernel<__nv_bfloat16><<<grid, nt, 0, stream>>>(
+    tl::launch_kernel(rope_kv_kernel<__nv_bfloat16>, grid, nt, 0, stream, 
         (__nv_bfloat16*)qkv, positions, token_req, block_table, table_width, (__nv_bfloat16*)pages,
         inv_freq, nh, nkv, d, page_size, write_kv);
   return TL_LAUNCH_CHECK();
@@ -176,9 +188,9 @@ int tl_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter,
   if (total == 0) return 0;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   if (dtype == TL_DTYPE_F32)
-    swiglu_kernel<float><<<blocks, 256, 0, stream>>>((const float*)gate_up, (float*)out, inter, total);
+    tl::launch_kernel(swiglu_kernel<float>, blocks, 256, 0, stream, (const float*)gate_up, (float*)out, inter, total);
   else
-    swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
+    tl::launch_kernel(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, total);
   return TL_LAUNCH_CHECK();
 }
 

@@ -21,6 +21,9 @@ template <typename T, typename OutT, bool ACCUM>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ x, const T* __restrict__ w, const float* __restrict__ bias,
                  OutT* __restrict__ out, int M, int N, int K, int ldx, int ldw, int ldo) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   __shared__ float xs[BK][BM + 1];
   __shared__ float ws[BK][BN + 1];
   const int tid = threadIdx.x;
@@ -87,9 +90,9 @@ int launch(const void* x, const void* w, const float* bias, void* out, int accum
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (grid.y > 65535) return TL_ERR_UNSUPPORTED;
   if (accumulate)
-    gemm_simt_kernel<T, OutT, true><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, (OutT*)out, M, N, K, ldx, ldw, ldo);
+    tl::launch_kernel(gemm_simt_kernel<T, OutT, true>, grid, 256, 0, stream, (const T*)x, (const T*)w, bias, (OutT*)out, M, N, K, ldx, ldw, ldo);
   else
-    gemm_simt_kernel<T, OutT, false><<<grid, 256, 0, stream>>>((const T*)x, (const T*)w, bias, (OutT*)out, M, N, K, ldx, ldw, ldo);
+    tl::launch_kernel(gemm_simt_kernel<T, OutT, false>, grid, 256, 0, stream, (const T*)x, (const T*)w, bias, (OutT*)out, M, N, K, ldx, ldw, ldo);
   return TL_LAUNCH_CHECK();
 }
 

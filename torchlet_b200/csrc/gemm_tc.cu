@@ -50,6 +50,7 @@ struct Params {
   long long ldo;
   int epilogue;
   float* partial;  // swapped: [splits][M = cols][N = rows]
+  int ahead;       // stages of weight tiles requested before the wait on the preceding kernel
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
@@ -158,9 +159,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue
   if (warp == 0) {
     if (lane == 0) {
-      for (int it = 0; it < num_kb; ++it) {
+      // Swapped orientation: the row operand is the WEIGHT matrix, which no earlier kernel
+      // writes.  Its tiles for the first stages are requested before the wait on the
+      // preceding kernel, so the weight stream is already running when the activations
+      // (written by that kernel) become available.
+      const int ahead = SWAP ? min(min(STAGES, p.ahead), num_kb) : 0;
+      for (int it = 0; it < ahead; ++it) {
+        mbar_expect_tx(&full[it], STAGE_BYTES);
+        tma_load_2d(smem + it * STAGE_BYTES, &map_row, &full[it], (kb_begin + it) * BLOCK_K, row0);
+      }
+      tl::pdl_wait();
+      for (int it = 0; it < ahead; ++it)
+        tma_load_2d(smem + it * STAGE_BYTES + ROW_TILE_BYTES, &map_col, &full[it], (kb_begin + it) * BLOCK_K, col0);
+      for (int it = ahead; it < num_kb; ++it) {
         const int s = it % STAGES;
         const uint32_t phase = (it / STAGES) & 1;
         mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
@@ -170,8 +184,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         tma_load_2d(stage, &map_row, &full[s], k, row0);
         tma_load_2d(stage + ROW_TILE_BYTES, &map_col, &full[s], k, col0);
       }
+    } else {
+      tl::pdl_wait();
     }
   } else if (warp == 1) {
+    tl::pdl_wait();
     if (lane == 0) {
       for (int it = 0; it < num_kb; ++it) {
         const int s = it % STAGES;
@@ -191,6 +208,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       mma_commit(tmem_full);
     }
   } else {
+    tl::pdl_wait();  // the epilogue writes buffers that earlier kernels may still read
     mbar_wait(tmem_full, 0, abort_flag, &g_error_word, 3);
     fence_after_sync();
     const int quarter = warp & 3;  // the TMEM lane quarter this warp may read
@@ -268,6 +286,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
 // Adds the split partials [splits][M][N] in ascending split order and applies the epilogue.
 __global__ void splitk_finish_kernel(const float* __restrict__ partial, int splits, int M, int N,
                                      const float* __restrict__ bias, int epilogue, void* out, long long ldo) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)M * out_cols) return;
@@ -387,7 +408,7 @@ int launch(const CUtensorMap& map_row, const CUtensorMap& map_col, const Params&
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  gemm_tc_kernel<BLOCK_Q, STAGES, SWAP><<<grid, THREADS, SMEM, stream>>>(map_row, map_col, p);
+  tl::launch_kernel(gemm_tc_kernel<BLOCK_Q, STAGES, SWAP>, grid, THREADS, SMEM, stream, map_row, map_col, p);
   return TL_LAUNCH_CHECK();
 }
 
@@ -433,6 +454,7 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   p.ldo = ldo;
   p.epilogue = epilogue;
   p.partial = nullptr;
+  p.ahead = 8;  // all stages
   if (splits_out) *splits_out = 0;
   CUtensorMap map_row, map_col;
   int rc;
@@ -465,7 +487,7 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
     }
     const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
     const long long total = (long long)M * out_cols;
-    splitk_finish_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(p.partial, plan.splits, M, N, bias,
+    tl::launch_kernel(splitk_finish_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, p.partial, plan.splits, M, N, bias,
                                                                              epilogue, out, ldo);
     return TL_LAUNCH_CHECK();
   }

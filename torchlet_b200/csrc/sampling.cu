@@ -81,6 +81,9 @@ __global__ void __launch_bounds__(NT)
 sample_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, int span,
               const float* __restrict__ temperature, const long long* __restrict__ seed,
               const int* __restrict__ counter, int* __restrict__ out, Best* __restrict__ scratch) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   const int r = blockIdx.x;
   const float* row = logits + (size_t)r * row_stride;
   const float temp = temperature ? temperature[r] : 0.f;
@@ -110,6 +113,9 @@ sample_kernel(const float* __restrict__ logits, size_t row_stride, int vocab, in
 }
 
 __global__ void sample_merge_kernel(const Best* __restrict__ scratch, int chunks, int* __restrict__ out) {
+  tl::pdl_wait();               // everything before us in the stream is complete and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   const int r = blockIdx.x, lane = threadIdx.x;
   float bv = -INFINITY;
   int bi = 0x7fffffff;
@@ -151,11 +157,11 @@ int tl_sample(const float* logits, long long row_stride, int rows, int vocab, co
   if (chunks > 1 && (!scratch || scratch_bytes < tl_sample_scratch_bytes(rows, vocab))) chunks = 1;
   if (chunks > 65535) return TL_ERR_UNSUPPORTED;
   const int span = chunks > 1 ? CHUNK : vocab;
-  sample_kernel<<<dim3(rows, chunks), NT, 0, stream>>>(logits, (size_t)row_stride, vocab, span, temperature, seed,
+  tl::launch_kernel(sample_kernel, dim3(rows, chunks), NT, 0, stream, logits, (size_t)row_stride, vocab, span, temperature, seed,
                                                       counter, out, (Best*)scratch);
   int rc = TL_LAUNCH_CHECK();
   if (rc || chunks == 1) return rc;
-  sample_merge_kernel<<<rows, 32, 0, stream>>>((const Best*)scratch, chunks, out);
+  tl::launch_kernel(sample_merge_kernel, rows, 32, 0, stream, (const Best*)scratch, chunks, out);
   return TL_LAUNCH_CHECK();
 }
 
