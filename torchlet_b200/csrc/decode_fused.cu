@@ -94,15 +94,27 @@ finish_accum_norm_kernel(const float* __restrict__ partial, int splits, const fl
     v[k] = j < hidden ? row[j] : 0.f;
     sum[k] = (bias && j < hidden) ? bias[j] : 0.f;
   }
-  for (int s = 0; s < splits; ++s) {
-    float part[PER];
+  int s = 0;
+  for (; s + 2 <= splits; s += 2) {  // two splits a round: 2 * PER loads in flight
+    float part0[PER], part1[PER];
 #pragma unroll
     for (int k = 0; k < PER; ++k) {
       const int j = threadIdx.x + k * NT;
-      part[k] = j < hidden ? src[s * plane + j] : 0.f;
+      part0[k] = j < hidden ? src[s * plane + j] : 0.f;
+      part1[k] = j < hidden ? src[(s + 1) * plane + j] : 0.f;
     }
 #pragma unroll
-    for (int k = 0; k < PER; ++k) sum[k] += part[k];
+    for (int k = 0; k < PER; ++k) {
+      sum[k] += part0[k];
+      sum[k] += part1[k];
+    }
+  }
+  for (; s < splits; ++s) {
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+      const int j = threadIdx.x + k * NT;
+      sum[k] += j < hidden ? src[s * plane + j] : 0.f;
+    }
   }
   float ss = 0.f;
 #pragma unroll
