@@ -10,6 +10,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "sampling_static.h"
 
 namespace {
 
@@ -162,6 +163,41 @@ int tl_sample(const float* logits, long long row_stride, int rows, int vocab, co
   int rc = TL_LAUNCH_CHECK();
   if (rc || chunks == 1) return rc;
   tl::launch_kernel(sample_merge_kernel, rows, 32, 0, stream, (const Best*)scratch, chunks, out);
+  return TL_LAUNCH_CHECK();
+}
+
+// ---------------------------------------------------------------------------
+// The variant that allocates nothing (see sampling_static.h).  The partial results of
+// the blocks that share a row live in this array instead of a caller's buffer.
+static __device__ __align__(256) Best g_static_partials[TL_SAMPLE_STATIC_MAX_PARTIALS];
+
+int tl_sample_static(const float* logits, long long row_stride, int rows, int vocab, const float* temperature,
+                     const long long* seed, const int* counter, int* out, cudaStream_t stream) {
+  if (rows <= 0) return 0;
+  if (vocab <= 0 || !logits || !out) return TL_ERR_UNSUPPORTED;
+  const long long chunks = (vocab + CHUNK - 1) / CHUNK;
+  if (chunks > 65535 || (long long)rows * chunks > TL_SAMPLE_STATIC_MAX_PARTIALS) return TL_SAMPLE_STATIC_TOO_LARGE;
+  // In host code the array's name is only a stand-in: the device address is looked up
+  // once per device, with that device current, and kept.
+  constexpr int MAX_DEVICES = 64;
+  static Best* partials_on[MAX_DEVICES] = {};
+  int device = 0;
+  cudaError_t err = cudaGetDevice(&device);
+  if (err != cudaSuccess) return (int)err;
+  if (device < 0 || device >= MAX_DEVICES) return TL_ERR_UNSUPPORTED;
+  if (!partials_on[device]) {
+    void* address = nullptr;
+    err = cudaGetSymbolAddress(&address, g_static_partials);
+    if (err != cudaSuccess) return (int)err;
+    partials_on[device] = static_cast<Best*>(address);
+  }
+  Best* partials = partials_on[device];
+  const int span = chunks > 1 ? CHUNK : vocab;
+  tl::launch_kernel(sample_kernel, dim3(rows, (unsigned)chunks), NT, 0, stream, logits, (size_t)row_stride, vocab,
+                    span, temperature, seed, counter, out, partials);
+  int rc = TL_LAUNCH_CHECK();
+  if (rc || chunks == 1) return rc;
+  tl::launch_kernel(sample_merge_kernel, rows, 32, 0, stream, (const Best*)partials, (int)chunks, out);
   return TL_LAUNCH_CHECK();
 }
 
