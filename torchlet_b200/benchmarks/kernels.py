@@ -1,0 +1,111 @@
+"""Single kernels at chosen sizes, timed with CUDA events (also the small cases that are
+profiled with ncu for ``profiles/``).
+
+    python -m torchlet_b200.benchmarks.kernels gemm --m 8 --n 37888 --k 3584 --epilogue swiglu
+    python -m torchlet_b200.benchmarks.kernels attention --batch 8 --context 4096 --q-len 1
+    python -m torchlet_b200.benchmarks.kernels attention --batch 1 --context 0 --q-len 2048
+
+Weights rotate through several copies so that together they exceed the 126 MB L2; each
+line reports the mean time of ``--iters`` launches after ``--warmup``.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from .. import ops
+
+EPILOGUES = {"bf16": ops.EPI_STORE_BF16, "accum": ops.EPI_ACCUM_F32, "swiglu": ops.EPI_SWIGLU_BF16,
+             "f32": ops.EPI_STORE_F32}
+
+
+def _time(fn, iters: int, warmup: int) -> float:
+    for i in range(warmup):
+        fn(i)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for i in range(iters):
+        fn(warmup + i)
+    end.record()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) / iters
+
+
+def bench_gemm(args) -> None:
+    M, N, K = args.m, args.n, args.k
+    epilogue = EPILOGUES[args.epilogue]
+    copies = max(1, min(8, -(-(200 << 20) // (N * K * 2))))  # > L2 in total
+    generator = torch.Generator(device="cuda").manual_seed(0)
+    weights = [(torch.randn(N, K, device="cuda", generator=generator) * 0.02).bfloat16() for _ in range(copies)]
+    x = (torch.randn(M, K, device="cuda", generator=generator)).bfloat16()
+    out_cols = N // 2 if args.epilogue == "swiglu" else N
+    out = torch.zeros(M, out_cols, device="cuda", dtype=torch.bfloat16 if args.epilogue in ("bf16", "swiglu") else torch.float32)
+    ms = _time(lambda i: ops.gemm_tc(x, weights[i % copies], out, None, epilogue), args.iters, args.warmup)
+    flops, weight_bytes = 2.0 * M * N * K, N * K * 2
+    print(f"gemm M={M} N={N} K={K} epilogue={args.epilogue}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s, "
+          f"weights {weight_bytes / ms / 1e6:.0f} GB/s, wait-error {ops.gemm_tc_error()}")
+
+
+def bench_attention(args) -> None:
+    from ..parts.attention_bf16 import ROWS, decode_splits
+
+    nh, nkv, d, page = args.heads, args.kv_heads, args.head_dim, args.page_size
+    n, before, q_len = args.batch, args.context, args.q_len
+    total = before + q_len
+    width = -(-total // page)
+    pages = (torch.randn(n * width + 1, 2, nkv, page, d, device="cuda") * 0.5).bfloat16()
+    table = (torch.randperm(n * width, device="cuda").to(torch.int32) + 1).view(n, width).contiguous()
+    qkv = torch.randn(n * q_len, (nh + 2 * nkv) * d, device="cuda").bfloat16()
+    out = torch.zeros(n * q_len, nh * d, device="cuda", dtype=torch.bfloat16)
+    indptr = torch.arange(0, (n + 1) * q_len, q_len, dtype=torch.int32, device="cuda")
+    kv_before = torch.full((n,), before, dtype=torch.int32, device="cuda")
+    scale = d ** -0.5
+    group = nh // nkv
+    if q_len == 1:
+        splits = decode_splits(n, nkv, total)
+        run = lambda i: ops.attention_mma(qkv, pages, table, indptr, kv_before, None, None, n, out, n, nh, nkv, d, page,
+                                          None, scale, rows16=True, splits=splits)
+        kv_bytes = n * total * 2 * nkv * d * 2
+        what = f"decode splits={splits}"
+    else:
+        tiles = [(r, s) for r in range(n) for s in range(0, q_len * group, ROWS)]
+        tile_req = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+        tile_row = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+        run = lambda i: ops.attention_mma(qkv, pages, table, indptr, kv_before, tile_req, tile_row, len(tiles), out,
+                                          n * q_len, nh, nkv, d, page, None, scale, rows16=False)
+        kv_bytes = n * total * 2 * nkv * d * 2
+        what = f"prompt tiles={len(tiles)}"
+    ms = _time(run, args.iters, args.warmup)
+    flops = 4.0 * n * nh * d * (q_len * before + q_len * (q_len + 1) / 2)
+    print(f"attention batch={n} context={before} q_len={q_len} heads={nh}/{nkv} d={d} {what}: {ms * 1e3:.1f} us, "
+          f"{flops / ms / 1e9:.1f} TFLOP/s, KV {kv_bytes / ms / 1e6:.0f} GB/s")
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    sub = parser.add_subparsers(dest="what", required=True)
+    gemm = sub.add_parser("gemm")
+    gemm.add_argument("--m", type=int, default=8)
+    gemm.add_argument("--n", type=int, default=37888)
+    gemm.add_argument("--k", type=int, default=3584)
+    gemm.add_argument("--epilogue", choices=sorted(EPILOGUES), default="swiglu")
+    attention = sub.add_parser("attention")
+    attention.add_argument("--batch", type=int, default=8)
+    attention.add_argument("--context", type=int, default=4096)
+    attention.add_argument("--q-len", type=int, default=1)
+    attention.add_argument("--heads", type=int, default=28)
+    attention.add_argument("--kv-heads", type=int, default=4)
+    attention.add_argument("--head-dim", type=int, default=128)
+    attention.add_argument("--page-size", type=int, default=16)
+    for p in (gemm, attention):
+        p.add_argument("--iters", type=int, default=20)
+        p.add_argument("--warmup", type=int, default=3)
+    args = parser.parse_args(argv)
+    {"gemm": bench_gemm, "attention": bench_attention}[args.what](args)
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
