@@ -90,30 +90,33 @@ def test_gemm_simt(dtype, out_dtype, M, N, K):
     (100, 1000, 520, 3, True), (300, 512, 256, 0, True), (1000, 384, 512, 1, True), (700, 448, 96, 2, False),
     (513, 1000, 72, 3, False), (257, 331, 200, 0, True),
 ])
-def test_gemm_tc(M, N, K, epilogue, bias):
+@pytest.mark.parametrize("cta_pairs", [False, True])
+def test_gemm_tc(M, N, K, epilogue, bias, cta_pairs):
     ops = _ops()
+    if cta_pairs and M <= 256:
+        pytest.skip("CTA pairs serve the many-token orientation only")
     x, w = randn(M, K, dtype=torch.bfloat16, scale=0.5), randn(N, K, dtype=torch.bfloat16, scale=0.5, seed=1)
     b = randn(N, seed=2) if bias else None
     want = x.double() @ w.double().t() + (b.double() if bias else 0)
     if epilogue == ops.EPI_STORE_BF16:
         out = torch.zeros(M, N, device=DEV, dtype=torch.bfloat16)
-        ops.gemm_tc(x, w, out, b, epilogue)
+        ops.gemm_tc(x, w, out, b, epilogue, cta_pairs=cta_pairs)
         tol = 8e-3
     elif epilogue == ops.EPI_ACCUM_F32:
         base = randn(M, N, seed=3)
         out = base.clone()
-        ops.gemm_tc(x, w, out, b, epilogue)
+        ops.gemm_tc(x, w, out, b, epilogue, cta_pairs=cta_pairs)
         want, tol = want + base.double(), 2e-5
     elif epilogue == ops.EPI_STORE_F32:
         out = torch.zeros(M, N, device=DEV)
-        ops.gemm_tc(x, w, out, b, epilogue)
+        ops.gemm_tc(x, w, out, b, epilogue, cta_pairs=cta_pairs)
         tol = 2e-5
     else:
         from torchlet_b200.parts.swiglu_bf16 import interleave
 
         inter = N // 2
         out = torch.zeros(M, inter, device=DEV, dtype=torch.bfloat16)
-        ops.gemm_tc(x, interleave(w[:inter], w[inter:]), out, None, epilogue)
+        ops.gemm_tc(x, interleave(w[:inter], w[inter:]), out, None, epilogue, cta_pairs=cta_pairs)
         want = torch.nn.functional.silu(want[:, :inter]) * want[:, inter:]
         tol = 8e-3
     torch.cuda.synchronize()

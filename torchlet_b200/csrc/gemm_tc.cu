@@ -51,12 +51,14 @@ struct Params {
   int epilogue;
   float* partial;  // swapped: [splits][M = cols][N = rows]
   int ahead;       // stages of weight tiles requested before the wait on the preceding kernel
+  // persistent kernel (normal orientation): tile width, stages, tile counts
+  int block_q, stages, row_tiles, num_tiles;
 };
 
 __device__ __forceinline__ float silu(float g) { return g / (1.f + __expf(-g)); }
 
 // 32 accumulator values of output row m, columns n0 .. n0+31 (normal orientation).
-__device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, const float (&v)[32]) {
+__device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, const float (&v)[32], int cols = 32) {
   const int N = p.cols;
   if (p.epilogue == EPI_SWIGLU_BF16) {
     // columns n0..n0+15 are gate j..j+15, n0+16..n0+31 the matching up values
@@ -78,7 +80,7 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, c
 #pragma unroll
   for (int c = 0; c < 32; c += 8) {
     const int n = n0 + c;
-    if (n >= N) return;
+    if (n >= N || c >= cols) return;
     float r[8];
 #pragma unroll
     for (int j = 0; j < 8; ++j) r[j] = v[c + j] + ((p.bias && n + j < N) ? p.bias[n + j] : 0.f);
@@ -283,6 +285,274 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
   }
 }
 
+// Normal orientation, persistent: one CTA per SM walks over output tiles (row tiles
+// fastest, so CTAs running at the same time share weight tiles in L2).  The tile width
+// block_q (a multiple of 16 up to 256) is chosen on the host so that the tiles fill whole
+// waves.  The accumulator is double-buffered in tensor memory (2 x 256 columns): while the
+// four epilogue warps drain tile i, the MMA thread already accumulates tile i + 1, and the
+// TMA producer never stops between tiles.
+__global__ void __launch_bounds__(THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
+                          const Params p) {
+  constexpr int MAX_STAGES = 8;
+  constexpr int ACC_COLS = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int stage_bytes = ROW_TILE_BYTES + p.block_q * BLOCK_K * 2;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* tmem_full = empty + MAX_STAGES;   // [2]
+  uint64_t* tmem_empty = tmem_full + 2;        // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 4);  // one arrival from each epilogue warp
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&map_row);
+    prefetch_tensormap(&map_col);
+  }
+  if (warp == 1) {
+    tmem_alloc<512>(tmem_slot);
+    tmem_relinquish();
+  }
+  fence_before_sync();
+  __syncthreads();
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();  // activations come from the preceding kernel
+
+  const int num_kb = p.k_blocks;
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
+        const int row0 = (tile % p.row_tiles) * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t phase = (it / p.stages) & 1;
+          mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
+          mbar_expect_tx(&full[s], stage_bytes);
+          uint8_t* stage = smem + s * stage_bytes;
+          tma_load_2d(stage, &map_row, &full[s], kb * BLOCK_K, row0);
+          tma_load_2d(stage + ROW_TILE_BYTES, &map_col, &full[s], kb * BLOCK_K, col0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = idesc_bf16_f32(BLOCK_P, p.block_q);
+      int it = 0, local = 0;
+      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local) {
+        const int a = local & 1;
+        mbar_wait(&tmem_empty[a], ((local >> 1) & 1) ^ 1, abort_flag, &g_error_word, 4);
+        fence_after_sync();
+        const uint32_t acc = tmem_base + a * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t phase = (it / p.stages) & 1;
+          mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
+          fence_after_sync();
+          const uint32_t a_addr = smem_addr(smem + s * stage_bytes);
+          const uint64_t a_desc = smem_desc_sw128(a_addr);
+          const uint64_t b_desc = smem_desc_sw128(a_addr + ROW_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k) mma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
+          mma_commit(&empty[s]);
+        }
+        mma_commit(&tmem_full[a]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int local = 0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local) {
+      const int a = local & 1;
+      const int row0 = (tile % p.row_tiles) * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
+      mbar_wait(&tmem_full[a], (local >> 1) & 1, abort_flag, &g_error_word, 3);
+      fence_after_sync();
+      const int row = row0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + a * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      const bool live = row < p.rows;
+#pragma unroll 1
+      for (int c = 0; c < p.block_q; c += 32) {
+        float v[32];
+        const int cols = min(32, p.block_q - c);
+        if (cols == 32) {
+          uint32_t r[32];
+          tmem_ld_32(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        } else {
+          uint32_t r[16];
+          tmem_ld_16(taddr + c, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) v[j] = __uint_as_float(r[j]);
+#pragma unroll
+          for (int j = 16; j < 32; ++j) v[j] = 0.f;
+        }
+        if (live) epilogue_chunk(p, row, col0 + c, v, cols);
+      }
+      // the accumulator may be overwritten once all four warps have read it
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tmem_empty[a]);
+    }
+  }
+  fence_before_sync();
+  __syncthreads();
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc<512>(tmem_base);
+  }
+}
+
+// Normal orientation, persistent, CTA PAIRS (cta_group::2): a cluster of two CTAs on
+// neighbouring SMs computes a 256 x block_q tile.  CTA r of the pair loads rows
+// [128 r, 128 r + 128) of the A tile and columns [r block_q / 2, (r + 1) block_q / 2) of the
+// B tile into its own shared memory; one thread of CTA 0 issues tcgen05.mma.cta_group::2
+// (UMMA 256 x block_q x 16), which reads both CTAs' shared memory and writes 128
+// accumulator rows into each CTA's tensor memory.  Against the single-CTA kernel each SM
+// moves a third less data into shared memory per flop (32 KB instead of 48 KB per k-block
+// at block_q = 256), which is what bounds that kernel, and has 6 stages instead of 4.
+// Barriers: the TMA loads of both CTAs count on CTA 0's "full" barrier; tcgen05.commit
+// arrives on the "empty" and "accumulator full" barriers of both CTAs; the epilogue warps
+// of both CTAs arrive on CTA 0's "accumulator empty" barrier.
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
+                    const Params p) {
+  constexpr int MAX_STAGES = 8;
+  constexpr int ACC_COLS = 256;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const int half_q = p.block_q / 2;
+  const int stage_bytes = ROW_TILE_BYTES + half_q * BLOCK_K * 2;  // of ONE CTA
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + p.stages * stage_bytes);
+  uint64_t* empty = full + MAX_STAGES;
+  uint64_t* tmem_full = empty + MAX_STAGES;  // [2]
+  uint64_t* tmem_empty = tmem_full + 2;       // [2]
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_rank();
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tmem_full[a], 1);
+      mbar_init(&tmem_empty[a], 8);  // four epilogue warps in each CTA of the pair
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tensormap(&map_row);
+    prefetch_tensormap(&map_col);
+  }
+  if (warp == 1) {
+    tmem_alloc_pair<512>(tmem_slot);
+    tmem_relinquish_pair();
+  }
+  fence_before_sync();
+  cluster_sync();  // barriers of both CTAs are initialised before anyone signals them
+  fence_after_sync();
+  const uint32_t tmem_base = *tmem_slot;
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+
+  const int num_kb = p.k_blocks;
+  if (warp == 0) {
+    if (lane == 0) {
+      int it = 0;
+      for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+        const int row0 = (tile % p.row_tiles) * 256 + (int)rank * BLOCK_P;
+        const int col0 = (tile / p.row_tiles) * p.block_q + (int)rank * half_q;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t phase = (it / p.stages) & 1;
+          mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
+          if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);  // the bytes of both CTAs
+          const uint32_t bar = peer_addr(&full[s], 0);
+          uint8_t* stage = smem + s * stage_bytes;
+          tma_load_2d_pair(stage, &map_row, bar, kb * BLOCK_K, row0);
+          tma_load_2d_pair(stage + ROW_TILE_BYTES, &map_col, bar, kb * BLOCK_K, col0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = idesc_bf16_f32(256, p.block_q);
+      int it = 0, local = 0;
+      for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++local) {
+        const int a = local & 1;
+        mbar_wait(&tmem_empty[a], ((local >> 1) & 1) ^ 1, abort_flag, &g_error_word, 4);
+        fence_after_sync();
+        const uint32_t acc = tmem_base + a * ACC_COLS;
+        for (int kb = 0; kb < num_kb; ++kb, ++it) {
+          const int s = it % p.stages;
+          const uint32_t phase = (it / p.stages) & 1;
+          mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
+          fence_after_sync();
+          const uint32_t a_addr = smem_addr(smem + s * stage_bytes);
+          const uint64_t a_desc = smem_desc_sw128(a_addr);
+          const uint64_t b_desc = smem_desc_sw128(a_addr + ROW_TILE_BYTES);
+#pragma unroll
+          for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+            mma_bf16_pair(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
+          mma_commit_pair(&empty[s]);
+        }
+        mma_commit_pair(&tmem_full[a]);
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int local = 0;
+    for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++local) {
+      const int a = local & 1;
+      const int row0 = (tile % p.row_tiles) * 256 + (int)rank * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
+      mbar_wait(&tmem_full[a], (local >> 1) & 1, abort_flag, &g_error_word, 3);
+      fence_after_sync();
+      const int row = row0 + quarter * 32 + lane;
+      const uint32_t taddr = tmem_base + a * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
+      const bool live = row < p.rows;
+#pragma unroll 1
+      for (int c = 0; c < p.block_q; c += 32) {
+        float v[32];
+        uint32_t r[32];
+        tmem_ld_32(taddr + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+        if (live) epilogue_chunk(p, row, col0 + c, v, 32);
+      }
+      fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(peer_addr(&tmem_empty[a], 0));
+    }
+  }
+  __syncwarp();
+  fence_before_sync();
+  cluster_sync();  // neither CTA leaves while its peer may still read its memory or signal it
+  if (warp == 1) {
+    fence_after_sync();
+    tmem_dealloc_pair<512>(tmem_base);
+  }
+}
+
 // Adds the split partials [splits][M][N] in ascending split order and applies the epilogue.
 __global__ void splitk_finish_kernel(const float* __restrict__ partial, int splits, int M, int N,
                                      const float* __restrict__ bias, int epilogue, void* out, long long ldo) {
@@ -390,8 +660,20 @@ Plan make_plan(int M, int N, int K) {
     plan.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     plan.splits = (k_blocks + plan.k_blocks_per_split - 1) / plan.k_blocks_per_split;
   } else {
+    // persistent kernel: the tile width that gives the shortest schedule
+    // (waves of one tile per SM, a tile's time in proportion to its width)
     const int row_tiles = (M + BLOCK_P - 1) / BLOCK_P;
-    plan.block_q = row_tiles * ((N + 255) / 256) >= sm_count() ? 256 : 128;
+    long long best_cost = -1;
+    plan.block_q = 256;
+    for (int q = 256; q >= 64; q -= 16) {
+      const long long tiles = (long long)row_tiles * ((N + q - 1) / q);
+      const long long waves = (tiles + sm_count() - 1) / sm_count();
+      const long long cost = waves * (q + 24);  // + a fixed part of a tile's time
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        plan.block_q = q;
+      }
+    }
     plan.splits = 1;
     plan.k_blocks_per_split = k_blocks;
   }
@@ -433,8 +715,10 @@ int tl_gemm_tc_error() {
   return value;
 }
 
-// defer != 0 (swapped orientation only): leave the float32 partials [splits][M][N] in the
+// defer == 1 (swapped orientation only): leave the float32 partials [splits][M][N] in the
 // workspace for a fused finishing kernel of the caller; *splits_out gets their number.
+// defer == 2: with many tokens, use the CTA-pair kernel (cta_group::2) instead of the
+// single-CTA persistent kernel; it measures the same speed here and is kept selectable.
 // out (+)= x[M, K] . w[N, K]^T.  x and w bfloat16 with K contiguous, ldx/ldw elements
 // between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
 // 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
@@ -458,7 +742,8 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   if (splits_out) *splits_out = 0;
   CUtensorMap map_row, map_col;
   int rc;
-  if (!plan.swap && defer) return TL_ERR_UNSUPPORTED;
+  if (!plan.swap && defer == 1) return TL_ERR_UNSUPPORTED;
+  if (plan.swap && defer == 2) defer = 0;
   if (plan.swap) {
     // one split writes its output directly; several (or a deferred finish) go through partials
     const bool partials = plan.splits > 1 || defer;
@@ -493,14 +778,62 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   }
   p.rows = M;
   p.cols = N;
-  if (!cached_map(&map_row, x, M, K, ldx, BLOCK_P) || !cached_map(&map_col, w, N, K, ldw, plan.block_q))
+  constexpr int SMEM_LIMIT = 227 * 1024;
+  if (defer == 2 && sm_count() % 2 == 0) {
+    // CTA pairs: 256-row tiles, tile width a multiple of 64 chosen for whole waves of pairs
+    const int pairs = sm_count() / 2;
+    const int row_tiles = (M + 255) / 256;
+    long long best_cost = -1;
+    int block_q = 256;
+    for (int q = 256; q >= 128; q -= 64) {
+      const long long tiles = (long long)row_tiles * ((N + q - 1) / q);
+      const long long cost = ((tiles + pairs - 1) / pairs) * (q + 24);
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        block_q = q;
+      }
+    }
+    if (!cached_map(&map_row, x, M, K, ldx, BLOCK_P) || !cached_map(&map_col, w, N, K, ldw, block_q / 2))
+      return TL_ERR_UNSUPPORTED;
+    p.block_q = block_q;
+    p.row_tiles = row_tiles;
+    p.num_tiles = row_tiles * ((N + block_q - 1) / block_q);
+    const int stage_bytes = ROW_TILE_BYTES + (block_q / 2) * BLOCK_K * 2;
+    p.stages = (SMEM_LIMIT - 1024 - 512) / stage_bytes;
+    if (p.stages > 8) p.stages = 8;
+    const int smem = p.stages * stage_bytes + 1024 + 512;
+    static bool configured = false;
+    if (!configured) {
+      cudaError_t err = cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             SMEM_LIMIT);
+      if (err != cudaSuccess) return (int)err;
+      configured = true;
+    }
+    const int ctas = 2 * (p.num_tiles < pairs ? p.num_tiles : pairs);
+    tl::launch_kernel(gemm_tc_pair_kernel, dim3(ctas), THREADS, smem, stream, map_row, map_col, p);
+    return TL_LAUNCH_CHECK();
+  }
+  int block_q = plan.block_q;
+  if (epilogue == EPI_SWIGLU_BF16) block_q = (block_q + 31) / 32 * 32 > 256 ? 256 : (block_q + 31) / 32 * 32;
+  if (!cached_map(&map_row, x, M, K, ldx, BLOCK_P) || !cached_map(&map_col, w, N, K, ldw, block_q))
     return TL_ERR_UNSUPPORTED;
-  dim3 grid((M + BLOCK_P - 1) / BLOCK_P, (N + plan.block_q - 1) / plan.block_q, 1);
-  if (plan.block_q == 256)
-    rc = launch<256, 4, false>(map_row, map_col, p, grid, stream);
-  else
-    rc = launch<128, 6, false>(map_row, map_col, p, grid, stream);
-  return rc;
+  p.block_q = block_q;
+  p.row_tiles = (M + BLOCK_P - 1) / BLOCK_P;
+  p.num_tiles = p.row_tiles * ((N + block_q - 1) / block_q);
+  const int stage_bytes = ROW_TILE_BYTES + block_q * BLOCK_K * 2;
+  p.stages = (SMEM_LIMIT - 1024 - 512) / stage_bytes;
+  if (p.stages > 8) p.stages = 8;
+  const int smem = p.stages * stage_bytes + 1024 + 512;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           SMEM_LIMIT);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  const int ctas = p.num_tiles < sm_count() ? p.num_tiles : sm_count();
+  tl::launch_kernel(gemm_tc_persistent_kernel, dim3(ctas), THREADS, smem, stream, map_row, map_col, p);
+  return TL_LAUNCH_CHECK();
 }
 
 }  // extern "C"
