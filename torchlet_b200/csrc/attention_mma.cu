@@ -130,7 +130,7 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
 }
 
 template <int D, bool ROWS16>
-__global__ void __launch_bounds__(THREADS)
+__global__ void __launch_bounds__(THREADS, 3)
 attention_mma_kernel(const Params p) {
   tl::pdl_wait();               // everything before us in the stream is complete and visible
   tl::pdl_launch_dependents();  // the next kernel may start its own prologue
@@ -142,9 +142,12 @@ attention_mma_kernel(const Params p) {
   constexpr int WARP_KEYS = ROWS16 ? 16 : 64;
   constexpr int NTILES = WARP_KEYS / 8;
 
+  // Shared memory: 2 stages x (K, V) x [64][D].  The Q rows are first loaded into the
+  // second stage's space; once every warp holds its Q fragments in registers that space
+  // is free for the key/value tiles, so three CTAs fit an SM.
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  __nv_bfloat16* qs = reinterpret_cast<__nv_bfloat16*>(smem_raw);  // [BLOCK_M][D]
-  __nv_bfloat16* kv = qs + BLOCK_M * D;                             // 2 stages x (K, V) x [64][D]
+  __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  __nv_bfloat16* qs = kv + 2 * BLOCK_N * D;  // [BLOCK_M][D], inside stage 1
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.x;
@@ -220,6 +223,7 @@ attention_mma_kernel(const Params p) {
     const int c = 2 * ks + (lane >> 4);
     ldmatrix_x4(q_frag[ks], tile_at<D>(qs, r, c));
   }
+  __syncthreads();  // stage 1 may now be overwritten by key/value tiles
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int stage = (tile - tile_begin) & 1;
@@ -435,7 +439,8 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
 template <int D, bool ROWS16>
 int launch(const Params& p, int tiles, cudaStream_t stream) {
   constexpr int BLOCK_M = ROWS16 ? 16 : 64;
-  constexpr int SMEM = (BLOCK_M * D + 2 * 2 * BLOCK_N * D) * 2;
+  constexpr int SMEM = 2 * 2 * BLOCK_N * D * 2;
+  static_assert(BLOCK_M * D <= 2 * BLOCK_N * D, "the Q rows fit one stage");
   static_assert(!ROWS16 || WARPS * 16 * (D + 2) * 4 <= 2 * 2 * BLOCK_N * D * 2, "merge buffer fits the stages");
   static bool configured = false;
   if (!configured) {
