@@ -276,19 +276,127 @@ def time_e2e(model, batch: int, context: int, steps: int, warmup: int):
             "d2h_bytes": batch * 4, "graph_steps": graph_steps}
 
 
+def _write_reference_folder(folder: str, cfg: dict, layers: int, context: int, seed: int) -> None:
+    """A model folder the reference can load: config.json, random weights (the same
+    generator and seed as our arm), and a word-level tokenizer whose word ``t<i>`` is token i
+    and whose chat template is the message text itself, so a prompt's length is exact."""
+    import torch
+    from safetensors.torch import save_file
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    from torchlet_b200.config import Qwen2Config
+    from torchlet_b200.weights import random_tensors
+
+    os.makedirs(folder, exist_ok=True)
+    raw = dict(cfg, num_hidden_layers=layers, max_position_embeddings=context)
+    config = Qwen2Config.from_dict(raw)
+    tensors = random_tensors(config, seed, std=0.02, norm_std=0.0, dtype="bfloat16", device="cuda:0")
+    save_file({k: v.cpu().contiguous() for k, v in tensors.items()}, os.path.join(folder, "model.safetensors"))
+    del tensors
+    torch.cuda.empty_cache()
+    with open(os.path.join(folder, "config.json"), "w") as handle:
+        json.dump(dict(raw, torch_dtype="bfloat16"), handle)
+    words = 4096  # prompts use only the first ids
+    vocab = {f"t{i}": i for i in range(words)}
+    vocab["<|im_end|>"] = words
+    vocab["<unk>"] = words + 1
+    tokenizer = Tokenizer(models.WordLevel(vocab, unk_token="<unk>"))
+    tokenizer.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    PreTrainedTokenizerFast(tokenizer_object=tokenizer, eos_token="<|im_end|>", unk_token="<unk>",
+                            chat_template="{% for m in messages %}{{ m['content'] }}{% endfor %}").save_pretrained(folder)
+
+
 def reference_arm(args) -> int:
-    """The unmodified reference through its own public API.  Its ``LLM(model_id)`` downloads
-    the model with ``modelscope.snapshot_download`` (v10_triton_paged_gqa/llm.py:9, 34), which
-    is not installed here and needs the network, so the arm reports itself unavailable."""
-    sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
+    """The UNMODIFIED reference (installed under baseline/_ref) through its own public API:
+    ``LLM(model_id, max_decode_slots=batch).generate(list[str], max_new_tokens)``
+    (v10_triton_paged_gqa/llm.py:20-110).  The only thing supplied from outside is the
+    package ``modelscope``, which is not installed here and would download the model from
+    the network (llm.py:9, 34): a stand-in module whose ``snapshot_download`` returns a
+    local folder with random weights of the same configuration and seed.  Decode tokens a
+    second are taken from two ``generate`` calls that differ only in ``max_new_tokens``
+    (same prompts, same prefill), so the prefill cancels out."""
+    import asyncio
+    import shutil
+    import tempfile
+    import types
+
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref_dir, "torchlet")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref/torchlet is not installed"}))
+        return 0
+    sys.path.insert(0, ref_dir)
+    stand_in = types.ModuleType("modelscope")
+    stand_in.snapshot_download = lambda model_id, *a, **k: model_id
+    sys.modules.setdefault("modelscope", stand_in)
     try:
-        from torchlet.v10_triton_paged_gqa.llm import LLM  # noqa: F401
+        import torch
+        from torchlet.v10_triton_paged_gqa.llm import LLM
     except Exception as exc:  # noqa: BLE001
         print(json.dumps({"impl": "reference",
                           "unavailable": f"the reference's LLM cannot be imported: {type(exc).__name__}: {exc}"}))
         return 0
-    print(json.dumps({"impl": "reference", "unavailable": "the reference's LLM(model_id) downloads the model with "
-                      "modelscope from the network; there is no network and no local model of it here"}))
+    cfg = QWEN25_7B
+    layers = args.layers or cfg["num_hidden_layers"]
+    batch, context, steps = args.batch, args.context, args.steps
+    folder = tempfile.mkdtemp(prefix="torchlet_ref_model_")
+    try:
+        _write_reference_folder(folder, cfg, layers, context, seed=4)
+        llm = LLM(folder, max_decode_slots=batch, kv_block_size=16)
+        generator = torch.Generator().manual_seed(5)
+        short, long = 8, 8 + steps
+        prompt_len = context - long - 1
+        prompts = [" ".join(f"t{int(i)}" for i in torch.randint(0, 4096, (prompt_len,), generator=generator))
+                   for _ in range(batch)]
+
+        async def run(max_new_tokens):
+            torch.cuda.synchronize()
+            begin = time.perf_counter()
+            outputs = await llm.generate(prompts, max_new_tokens=max_new_tokens)
+            torch.cuda.synchronize()
+            return time.perf_counter() - begin, outputs
+
+        async def everything():
+            try:
+                await run(4)  # warm-up: Triton compilation, CUDA-graph capture
+                clock = ClockSampler()
+                clock.start()
+                t_short, _ = await run(short)
+                t_long, outputs = await run(long)
+                stats = clock.stop()
+                one = [" ".join(f"t{int(i)}" for i in torch.randint(0, 4096, (2048,), generator=generator))]
+                old_prompts = list(prompts)
+                prompts[:] = one
+                await run(1)  # warm-up of this shape (the reference's Triton kernels autotune per shape)
+                t_prefill, _ = await run(1)
+                prompts[:] = old_prompts
+                return t_short, t_long, t_prefill, stats, outputs
+            finally:
+                await llm.engine.shutdown()
+
+        t_short, t_long, t_prefill, stats, outputs = asyncio.run(everything())
+    except Exception as exc:  # noqa: BLE001
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference failed to run here: "
+                          f"{type(exc).__name__}: {str(exc)[:300]}"}))
+        return 0
+    finally:
+        shutil.rmtree(folder, ignore_errors=True)
+    seconds = t_long - t_short
+    tok_s = batch * steps / seconds
+    print(json.dumps({
+        "impl": "reference", "metric": f"decode tok/s @ batch {batch} (Qwen2.5-7B layer sizes, bf16)",
+        "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
+        "ms_per_step": round(seconds * 1e3 / steps, 4), "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"model": "Qwen2.5-7B layer sizes, random weights seed 4", "global_batch": batch, "seq_len": context,
+                   "parallelism": "single GPU", "layers": layers, "layers_of_configuration": cfg["num_hidden_layers"],
+                   "how": "difference of two generate() calls with the same prompts",
+                   "modelscope": "stand-in module returning a local folder (no network)"},
+        "e2e": {"value": round(tok_s, 1), "unit": "tok/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
+        "prefill": {"value": round(2048 / t_prefill, 1), "tokens": 2048, "ms": round(t_prefill * 1e3, 2),
+                    "note": "one generate() call of 1 new token, tokenizer included"},
+        "clocks": stats, "gpu_launches": None,
+    }))
     return 0
 
 
