@@ -1,0 +1,73 @@
+"""Continuous batching under load: many requests of random lengths arriving while others
+run, greedy and temperature sampling mixed, a page pool too small for all of them.  Every
+request must finish, every page and slot must come back, and in float32 every output must
+equal the same request run alone (Qwen2.5-0.5B head geometry: 14 heads in 2 groups of 7,
+head_dim 64, so the tensor-core kernels run in the bfloat16 case)."""
+import random
+
+import pytest
+import torch
+
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 2048, "hidden_size": 896, "intermediate_size": 1216,
+    "num_hidden_layers": 2, "num_attention_heads": 14, "num_key_value_heads": 2, "max_position_embeddings": 512,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
+}
+
+
+def build(dtype, **engine):
+    from torchlet_b200.config import EngineConfig, Qwen2Config
+    from torchlet_b200.engine.engine import Engine
+    from torchlet_b200.engine.loading import build_model
+
+    weights = tiny_configs.make_weights(CONFIG, seed=5, std=0.02, norm_std=0.01, dtype=torch.bfloat16)
+    model = build_model(Qwen2Config.from_dict(CONFIG), weights, dtype)
+    return Engine(model, EngineConfig(dtype=dtype, max_seq_len=256, **engine))
+
+
+def make_requests(count, seed):
+    from torchlet_b200.engine.scheduler import Request
+    from torchlet_b200.sampling import SamplingParams
+
+    rng = random.Random(seed)
+    requests = []
+    for i in range(count):
+        prompt = [rng.randrange(CONFIG["vocab_size"]) for _ in range(rng.randint(4, 150))]
+        params = SamplingParams(max_new_tokens=rng.randint(4, 40), temperature=rng.choice([0.0, 0.0, 0.7]), seed=1000 + i)
+        requests.append(Request(prompt, params))
+    return requests
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_requests_arriving_while_others_run(dtype):
+    count = 40
+    engine = build(dtype, max_decode_slots=8, kv_block_size=16, max_num_blocks=41, max_num_batched_tokens=96)
+    requests = make_requests(count, seed=1)
+    rng = random.Random(2)
+    pending = list(requests)
+    steps = 0
+    while pending or engine.scheduler.has_work():
+        arrivals = min(len(pending), rng.choice([0, 0, 1, 1, 2, 3]))  # a seeded arrival pattern
+        if arrivals:
+            engine.add_requests([pending.pop(0) for _ in range(arrivals)])
+        if engine.scheduler.has_work():
+            engine.step()
+        engine.runner.cache.check()
+        steps += 1
+        assert steps < 20000
+    stats = engine.scheduler.stats
+    assert stats.finished == count and stats.failed == 0
+    assert stats.preemptions > 0, "the pool was meant to be too small"
+    assert all(r.error is None and len(r.output_tokens) == r.params.max_new_tokens for r in requests)
+    assert engine.runner.cache.live_requests() == []
+    assert engine.runner.cache.pools[0].num_free == 40 and engine.runner.cache.num_free_slots == 8
+    if dtype == "float32":
+        alone = build(dtype, max_decode_slots=1, kv_block_size=16, max_num_batched_tokens=512)
+        again = make_requests(count, seed=1)
+        for request, fresh in zip(requests, again):
+            alone.generate([fresh])
+            assert fresh.output_tokens == request.output_tokens, f"request {request.request_id} depends on its batch"
