@@ -48,6 +48,7 @@ struct Params {
   float* part_ml;   // [tokens*nh][splits][2]
   int nh, nkv, page_size, window, splits;
   int page_shift;  // log2(page_size) when it is a power of two, else -1
+  int overlap_max_tiles;  // host only: overlapped launch up to this many row tiles
   float scale_log2;  // scale * log2(e)
 };
 
@@ -132,9 +133,9 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
 template <int D, bool ROWS16>
 __global__ void __launch_bounds__(THREADS, 3)
 attention_mma_kernel(const Params p) {
-  tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
-
+  // The wait on the preceding kernel comes further down: the step's metadata is written
+  // by a host copy before any kernel of the step, and key/value tiles that lie wholly
+  // before the step's own tokens were written by earlier steps, so both may be read first.
   constexpr int BLOCK_M = ROWS16 ? 16 : 64;
   constexpr int KSTEPS = D / 16;   // k-steps of Q K^T
   constexpr int DTILES = D / 8;    // n-tiles of the output
@@ -147,7 +148,9 @@ attention_mma_kernel(const Params p) {
   // is free for the key/value tiles, so three CTAs fit an SM.
   extern __shared__ __align__(128) uint8_t smem_raw[];
   __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-  __nv_bfloat16* qs = kv + 2 * BLOCK_N * D;  // [BLOCK_M][D], inside stage 1
+  // 64-row tiles: Q [64][D] inside stage 1.  16-row tiles (decode): Q [16][D] after the
+  // stages, so that both stages can be filled before the wait on the preceding kernel.
+  __nv_bfloat16* qs = ROWS16 ? kv + 2 * 2 * BLOCK_N * D : kv + 2 * BLOCK_N * D;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.x;
@@ -163,7 +166,10 @@ attention_mma_kernel(const Params p) {
 
   // rows of this tile: [row_start, row_end)
   const int row_end = min(total_rows, row_start + BLOCK_M);
-  if (row_start >= row_end) return;
+  if (row_start >= row_end) {
+    tl::pdl_wait();
+    return;
+  }
   const int first_tok = row_start / g, last_tok = (row_end - 1) / g;
   const int hi_key = before + last_tok;  // last key any row of the tile may see
   int lo_key = 0;
@@ -177,6 +183,21 @@ attention_mma_kernel(const Params p) {
     tile_end = min(tile_end, tile_begin + per);
   }
 
+  // ---- key/value tiles that earlier steps wrote may be requested before the wait
+  constexpr int STAGE_ELEMS = 2 * BLOCK_N * D;
+  const int num_tiles = max(0, tile_end - tile_begin);
+  int issued = 0;  // tiles requested so far, counted from tile_begin
+  if constexpr (ROWS16) {
+    while (issued < min(2, num_tiles) && (tile_begin + issued) * BLOCK_N + BLOCK_N - 1 < before) {
+      __nv_bfloat16* stage = kv + issued * STAGE_ELEMS;
+      load_kv_tile<D>(p, table, kvh, (tile_begin + issued) * BLOCK_N, lo_key, hi_key, stage, stage + BLOCK_N * D);
+      cp_async_commit();
+      ++issued;
+    }
+  }
+  tl::pdl_wait();               // q and this step's keys and values are now written and visible
+  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
+
   // ---- Q rows into shared memory (zero for rows past the tile's end)
   for (int i = threadIdx.x; i < BLOCK_M * (D / 8); i += THREADS) {
     const int r = i / (D / 8), c = i % (D / 8);
@@ -185,6 +206,11 @@ attention_mma_kernel(const Params p) {
     const __nv_bfloat16* src = p.q;
     if (valid) src = p.q + (size_t)(tok0 + row / g) * p.q_stride + (size_t)(kvh * g + row % g) * D + c * 8;
     cp_async_16(tile_at<D>(qs, r, c), src, valid);
+  }
+  cp_async_commit();
+  if (issued == 0 && num_tiles > 0) {
+    load_kv_tile<D>(p, table, kvh, tile_begin * BLOCK_N, lo_key, hi_key, kv, kv + BLOCK_N * D);
+    issued = 1;
   }
   cp_async_commit();
 
@@ -208,12 +234,7 @@ attention_mma_kernel(const Params p) {
 #pragma unroll
   for (int i = 0; i < DTILES; ++i) o_acc[i][0] = o_acc[i][1] = o_acc[i][2] = o_acc[i][3] = 0.f;
 
-  constexpr int STAGE_ELEMS = 2 * BLOCK_N * D;
-  if (tile_begin < tile_end) {
-    load_kv_tile<D>(p, table, kvh, tile_begin * BLOCK_N, lo_key, hi_key, kv, kv + BLOCK_N * D);
-  }
-  cp_async_commit();
-  cp_async_wait<1>();  // Q has landed
+  cp_async_wait<0>();  // Q (and what was requested so far) has landed
   __syncthreads();
 
   unsigned q_frag[KSTEPS][4];
@@ -226,15 +247,17 @@ attention_mma_kernel(const Params p) {
   __syncthreads();  // stage 1 may now be overwritten by key/value tiles
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
-    const int stage = (tile - tile_begin) & 1;
+    const int index = tile - tile_begin;
+    const int stage = index & 1;
     __nv_bfloat16* ks_tile = kv + stage * STAGE_ELEMS;
     __nv_bfloat16* vs_tile = ks_tile + BLOCK_N * D;
-    if (tile + 1 < tile_end) {
+    if (issued == index + 1 && index + 1 < num_tiles) {  // request the next tile into the other stage
       __nv_bfloat16* next = kv + (stage ^ 1) * STAGE_ELEMS;
       load_kv_tile<D>(p, table, kvh, (tile + 1) * BLOCK_N, lo_key, hi_key, next, next + BLOCK_N * D);
+      ++issued;
     }
     cp_async_commit();
-    cp_async_wait<1>();  // this tile has landed
+    cp_async_wait<1>();  // everything but the request just made has landed: this tile is here
     __syncthreads();
 
     const int key_base = tile * BLOCK_N + (ROWS16 ? warp * 16 : 0);  // first key this warp multiplies
@@ -400,8 +423,8 @@ template <int D>
 __global__ void __launch_bounds__(D)
 attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                          __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int splits) {
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   __shared__ float weight[64];
   __shared__ float total[2];
@@ -439,7 +462,7 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
 template <int D, bool ROWS16>
 int launch(const Params& p, int tiles, cudaStream_t stream) {
   constexpr int BLOCK_M = ROWS16 ? 16 : 64;
-  constexpr int SMEM = 2 * 2 * BLOCK_N * D * 2;
+  constexpr int SMEM = (2 * 2 * BLOCK_N * D + (ROWS16 ? BLOCK_M * D : 0)) * 2;
   static_assert(BLOCK_M * D <= 2 * BLOCK_N * D, "the Q rows fit one stage");
   static_assert(!ROWS16 || WARPS * 16 * (D + 2) * 4 <= 2 * 2 * BLOCK_N * D * 2, "merge buffer fits the stages");
   static bool configured = false;
@@ -450,10 +473,13 @@ int launch(const Params& p, int tiles, cudaStream_t stream) {
     configured = true;
   }
   dim3 grid(tiles, p.nkv, p.splits);
-  // Launched WITHOUT overlap with its predecessor: CTAs that start while the small kernel
-  // before them still occupies the SMs are placed unevenly, and this kernel's time is set
-  // by its most loaded SM (measured: batch 64 decode lost 10% with an overlapped launch).
-  tl::launch_kernel_opt(false, attention_mma_kernel<D, ROWS16>, grid, THREADS, SMEM, stream, p);
+  // Decode steps of up to 32 requests are launched overlapped with the preceding kernel:
+  // the CTAs request their old key/value tiles while q is still being written.  Larger
+  // grids are launched WITHOUT overlap: CTAs that start while the small kernel before them
+  // still occupies the SMs are placed unevenly, and a bandwidth-bound grid's time is set by
+  // its most loaded SM (measured: batch 64 decode lost 9% with an overlapped launch).
+  tl::launch_kernel_opt(ROWS16 && tiles <= p.overlap_max_tiles, attention_mma_kernel<D, ROWS16>, grid, THREADS, SMEM,
+                        stream, p);
   return TL_LAUNCH_CHECK();
 }
 
@@ -495,6 +521,7 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, const
   p.nh = nh;
   p.nkv = nkv;
   p.page_size = page_size;
+  p.overlap_max_tiles = 32;
   p.page_shift = -1;
   for (int b = 0; b < 20; ++b)
     if ((1 << b) == page_size) p.page_shift = b;

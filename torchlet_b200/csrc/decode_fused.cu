@@ -24,8 +24,8 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ partial, int sp
                                        const int* __restrict__ block_table, int table_width,
                                        __nv_bfloat16* __restrict__ pages, const float* __restrict__ inv_freq,
                                        int tokens, int nh, int nkv, int d, int page_size, int write_kv) {
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   const int t = blockIdx.x, h = blockIdx.y;
   const int half = d >> 1;
@@ -78,8 +78,8 @@ __global__ void __launch_bounds__(NT)
 finish_accum_norm_kernel(const float* __restrict__ partial, int splits, const float* __restrict__ bias,
                          float* __restrict__ acc, const float* __restrict__ weight,
                          __nv_bfloat16* __restrict__ out, int tokens, int hidden, float eps) {
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   __shared__ float scratch[32];
   const int t = blockIdx.x;

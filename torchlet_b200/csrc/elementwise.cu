@@ -16,8 +16,8 @@ using namespace tl;
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ acc, int hidden, int vocab) {
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   const int t = blockIdx.x;
   int id = ids[t];
@@ -35,8 +35,8 @@ template <typename T, int NT>
 __global__ void __launch_bounds__(NT)
 rms_norm_kernel(const float* __restrict__ acc, const float* __restrict__ w, const int* __restrict__ rows,
                 T* __restrict__ out, int hidden, float eps) {
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   __shared__ float scratch[32];
   constexpr int PER = 8;  // elements a thread keeps in registers; longer rows are re-read
@@ -78,8 +78,8 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
                                const int* __restrict__ block_table, int table_width,
                                T* __restrict__ pages, const float* __restrict__ inv_freq, int nh,
                                int nkv, int d, int page_size, int write_kv) {
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   const int t = blockIdx.x;
   const int h = blockIdx.y;
@@ -115,8 +115,8 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter,
                               size_t total) {
+  tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
-  tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
