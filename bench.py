@@ -403,7 +403,7 @@ def reference_arm(args) -> int:
 def main() -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=128)
+    parser.add_argument("--steps", type=int, default=256)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
     parser.add_argument("--batch", type=int, default=8)

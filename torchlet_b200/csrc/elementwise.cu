@@ -110,6 +110,57 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
   }
 }
 
+// bfloat16, head_dim a multiple of 16: each thread takes 8 consecutive elements of the
+// first half of a head and the matching 8 of the second half (two 16-byte loads and
+// stores); one block covers several heads of one token.
+__global__ void __launch_bounds__(256)
+rope_kv_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
+                   const int* __restrict__ token_req, const int* __restrict__ block_table, int table_width,
+                   __nv_bfloat16* __restrict__ pages, const float* __restrict__ inv_freq, int nh, int nkv, int d,
+                   int page_size, int heads) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const int t = blockIdx.x;
+  const int half = d >> 1;
+  const int per_head = half >> 3;  // threads a head
+  const int pos = positions[t];
+  const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+  const int slot = pos % page_size;
+  for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
+    const int h = item / per_head, i = (item % per_head) * 8;
+    __nv_bfloat16* row = qkv + (size_t)t * (nh + 2 * nkv) * d + (size_t)h * d;
+    __nv_bfloat16* dst = row;
+    const bool is_v = h >= nh + nkv;
+    if (h >= nh) {
+      const int kvh = is_v ? h - nh - nkv : h - nh;
+      dst = pages + ((((size_t)page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + slot) * d;
+    }
+    const uint4 lo = *reinterpret_cast<const uint4*>(row + i);
+    const uint4 hi = *reinterpret_cast<const uint4*>(row + i + half);
+    if (is_v) {
+      *reinterpret_cast<uint4*>(dst + i) = lo;
+      *reinterpret_cast<uint4*>(dst + i + half) = hi;
+      continue;
+    }
+    float x1[8], x2[8];
+    load8(reinterpret_cast<const __nv_bfloat16*>(&lo), x1);
+    load8(reinterpret_cast<const __nv_bfloat16*>(&hi), x2);
+    uint32_t out_lo[4], out_hi[4];
+#pragma unroll
+    for (int j = 0; j < 8; j += 2) {
+      float s0, c0, s1, c1;
+      sincosf((float)pos * inv_freq[i + j], &s0, &c0);
+      sincosf((float)pos * inv_freq[i + j + 1], &s1, &c1);
+      __nv_bfloat162 a = __floats2bfloat162_rn(x1[j] * c0 - x2[j] * s0, x1[j + 1] * c1 - x2[j + 1] * s1);
+      __nv_bfloat162 b = __floats2bfloat162_rn(x2[j] * c0 + x1[j] * s0, x2[j + 1] * c1 + x1[j + 1] * s1);
+      out_lo[j >> 1] = *reinterpret_cast<uint32_t*>(&a);
+      out_hi[j >> 1] = *reinterpret_cast<uint32_t*>(&b);
+    }
+    *reinterpret_cast<uint4*>(dst + i) = make_uint4(out_lo[0], out_lo[1], out_lo[2], out_lo[3]);
+    *reinterpret_cast<uint4*>(dst + i + half) = make_uint4(out_hi[0], out_hi[1], out_hi[2], out_hi[3]);
+  }
+}
+
 // ------------------------------------------------------------------- SwiGLU
 // out[t, j] = silu(gu[t, j]) * gu[t, I + j],  silu(a) = a * sigmoid(a)
 template <typename T>
@@ -170,6 +221,13 @@ int tl_rope_kv(void* qkv, int dtype, const int* positions, const int* token_req,
   if (heads > 65535) return TL_ERR_UNSUPPORTED;
   int nt = ((d / 2 + 31) / 32) * 32;
   if (nt > 128) nt = 128;
+  if (dtype == TL_DTYPE_BF16 && d % 16 == 0) {
+    const int items = heads * (d / 16);
+    const int threads = items >= 256 ? 256 : ((items + 31) / 32) * 32;
+    tl::launch_kernel(rope_kv_vec_kernel, tokens, threads, 0, stream, (__nv_bfloat16*)qkv, positions, token_req,
+                      block_table, table_width, (__nv_bfloat16*)pages, inv_freq, nh, nkv, d, page_size, heads);
+    return TL_LAUNCH_CHECK();
+  }
   dim3 grid(tokens, heads);
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(rope_kv_kernel<float>, grid, nt, 0, stream, (float*)qkv, positions, token_req, block_table,
