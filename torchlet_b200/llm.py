@@ -47,6 +47,9 @@ class LLM:
         from .engine.engine import Engine
         from .engine.loading import load_model
 
+        from .utils import get_backend_info
+
+        logger.info("backend info:\n%s", get_backend_info())
         self.model_dir = Path(model_dir)
         self.engine_config = EngineConfig(
             dtype=dtype, max_decode_slots=max_decode_slots, kv_block_size=kv_block_size,

@@ -85,4 +85,8 @@ def check_and_normalise(tensors: dict, expected: list) -> dict:
 def load_checkpoint(model_dir: str | Path, expected: list) -> dict:
     tensors = check_and_normalise(read_safetensors(model_dir), expected)
     logger.info("loaded %d tensors from %s", len(tensors), model_dir)
+    if logger.isEnabledFor(10):  # DEBUG: the whole table, as the reference logs it
+        from ..utils import get_weights_info
+
+        logger.debug("weight info:\n%s", get_weights_info(tensors))
     return tensors
