@@ -413,3 +413,37 @@ def test_sampling_over_a_vocabulary_scanned_by_several_blocks():
         scores = plain_model.temperature_scores(host[r], float(temperature[r]), int(seed[r]), int(counter[r]))
         assert scores[int(out[r])] >= max(scores) - 1e-3
     assert out[1] == vocab - 1
+
+
+@pytest.mark.parametrize("case", [
+    # lens_before, q_lens, nh, nkv, page, window
+    ([0], [40], 7, 1, 16, None),
+    ([0], [300], 28, 4, 16, None),
+    ([100, 0, 700], [70, 257, 19], 14, 2, 16, None),
+    ([5, 1000], [333, 40], 8, 8, 32, None),
+    ([64, 0], [200, 129], 4, 2, 8, 100),
+    ([0], [130], 16, 1, 128, None),
+])
+def test_attention_tc(case):
+    """Prompt-portion attention on tcgen05 (head_dim 128) against the plain formula."""
+    ops = _ops()
+    before, q_lens, nh, nkv, page, window = case
+    d, group = 128, nh // nkv
+    assert ops.attention_tc_supported(d, group, page)
+    x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=5)
+    scale = 0.37 / math.sqrt(d)
+    want = plain_attention(x["dense"], before, nh, nkv, window, scale)
+    rows = ops.attention_tc_rows(group)
+    assert rows == (128 // group) * group
+    tile_req, tile_row = [], []
+    for r, q in enumerate(q_lens):
+        for start in range(0, q * group, rows):
+            tile_req.append(r)
+            tile_row.append(start)
+    to = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = torch.full((x["T"], nh * d), 7.0, device=DEV, dtype=torch.bfloat16)
+    ops.attention_tc(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(tile_req), to(tile_row),
+                     len(tile_req), out, nh, nkv, d, page, window, scale)
+    torch.cuda.synchronize()
+    assert ops.attention_tc_error() == 0
+    assert (out.float().cpu() - want).abs().max() <= 1.5e-2 * want.abs().max()

@@ -132,3 +132,24 @@ def test_schedule_runs_a_layer_twice_and_shares_a_cache(dtype):
     got = replay(runner, "s", ids, [20, 2, 17, 1, 1, 19])
     assert_close(got, want, dtype, "schedule with repeats")
     assert len(runner.storage.pages[0]) == 3  # three executions own cache layers, one reads another's
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_head_dim_128_through_the_tensor_core_attention(dtype):
+    """Tiny D (head_dim 128, 3 heads a KV head): in bfloat16 prompt portions run on the
+    tcgen05 attention kernel and decode on the mma.sync kernel; cut into portions with
+    cached context before them, beside a second request."""
+    from torchlet_b200.engine import StepEntry
+
+    runner = make_runner("D", dtype, num_pages=80)
+    ids, want = plain_logits("D", 420, 21)
+    got = replay(runner, "h", ids, [150, 2, 129, 1, 1, 100, 37])
+    assert_close(got, want, dtype, "head_dim 128, portions")
+    other, want_other = plain_logits("D", 140, 22)
+    runner.admit("x"); runner.admit("y")
+    a = runner.step([StepEntry("x", ids[:300], [299]), StepEntry("y", other[:1], [0])]).cpu().clone()
+    b = runner.step([StepEntry("x", ids[300:301], [0]), StepEntry("y", other[1:140], list(range(139)))]).cpu().clone()
+    assert_close(torch.cat([a[:1], b[:1]]), want[[299, 300]], dtype, "request x")
+    assert_close(torch.cat([a[1:], b[1:]]), want_other, dtype, "request y")
+    runner.finish("x"); runner.finish("y")
+    runner.cache.check()

@@ -59,7 +59,24 @@ TINY_C = {
 }
 TINY_C_INIT = {"seed": 5, "std": 0.04, "norm_std": 0.02, "page_size": 32}
 
-ALL = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT)}
+# head_dim 128 with 3 query heads a KV head: the shapes the tcgen05 attention kernel takes
+TINY_D = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 300,
+    "hidden_size": 768,
+    "intermediate_size": 320,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 6,
+    "num_key_value_heads": 2,
+    "max_position_embeddings": 1024,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "attention_bias": True,
+    "tie_word_embeddings": False,
+}
+TINY_D_INIT = {"seed": 7, "std": 0.02, "norm_std": 0.02, "page_size": 16}
+
+ALL = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT)}
 
 
 def head_dim(cfg: dict) -> int:

@@ -69,6 +69,15 @@ def bench_attention(args) -> None:
                                           None, scale, rows16=True, splits=splits)
         kv_bytes = n * total * 2 * nkv * d * 2
         what = f"decode splits={splits}"
+    elif args.kernel == "tc" and ops.attention_tc_supported(d, group, page):
+        rows = ops.attention_tc_rows(group)
+        tiles = sorted(((r, s) for r in range(n) for s in range(0, q_len * group, rows)), key=lambda t: -t[1])
+        tile_req = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
+        tile_row = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+        run = lambda i: ops.attention_tc(qkv, pages, table, indptr, kv_before, tile_req, tile_row, len(tiles), out,
+                                         nh, nkv, d, page, None, scale)
+        kv_bytes = n * total * 2 * nkv * d * 2
+        what = f"prompt (tcgen05) tiles={len(tiles)}"
     else:
         tiles = [(r, s) for r in range(n) for s in range(0, q_len * group, ROWS)]
         tile_req = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
@@ -99,6 +108,8 @@ def main(argv=None) -> int:
     attention.add_argument("--kv-heads", type=int, default=4)
     attention.add_argument("--head-dim", type=int, default=128)
     attention.add_argument("--page-size", type=int, default=16)
+    attention.add_argument("--kernel", choices=["tc", "mma"], default="tc",
+                           help="prompt portions: tcgen05 kernel (head_dim 128) or the mma.sync kernel")
     for p in (gemm, attention):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)

@@ -63,6 +63,13 @@ _SIGNATURES = {
         "tl_finish_accum_norm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                  c_void_p],
     },
+    "attention_tc": {
+        "tl_attention_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                            c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
+                            c_void_p],
+        "tl_attention_tc_error": [],
+        "tl_attention_tc_rows": [c_int],
+    },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_longlong, c_void_p],
@@ -326,3 +333,30 @@ def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile
         out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale), 1 if rows16 else 0, splits,
         _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
     _check(code, "attention_mma", 2 if splits > 1 else 1)
+
+
+def attention_tc_rows(group: int) -> int:
+    """Packed rows a tile of the tcgen05 attention kernel holds for ``group`` heads a KV head."""
+    return _fn("attention_tc", "tl_attention_tc_rows")(group)
+
+
+def attention_tc_supported(d: int, group: int, page_size: int) -> bool:
+    return d == 128 and 1 <= group <= 128 and 8 <= page_size <= 128 and 128 % page_size == 0
+
+
+def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, nh, nkv, d,
+                 page_size, window, scale) -> None:
+    """Prompt-portion attention on tcgen05 (csrc/attention_tc.cu): tiles of packed rows
+    (``tile_row`` multiples of ``attention_tc_rows(nh // nkv)``)."""
+    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
+    assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16 and pages.is_contiguous()
+    code = _fn("attention_tc", "tl_attention_tc")(
+        qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),
+        block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), tile_req.data_ptr(), tile_row.data_ptr(),
+        tiles, out.data_ptr(), out.stride(0), nh, nkv, d, page_size, int(window or 0), float(scale), _stream())
+    _check(code, "attention_tc")
+
+
+def attention_tc_error() -> int:
+    """0, or the code a bounded wait in the tcgen05 attention kernel left when it gave up."""
+    return _fn("attention_tc", "tl_attention_tc_error")()

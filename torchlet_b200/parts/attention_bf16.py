@@ -27,9 +27,9 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
     return max(1, min(room, -(-max_kv_len // 128), 64))
 
 
-def _plan(ctx, group_size: int):
-    """Which requests decode, and the 64-row tiles of the others (uploaded once a step)."""
-    key = ("attention_mma", group_size)
+def _plan(ctx, group_size: int, rows_per_tile: int = ROWS):
+    """Which requests decode, and the row tiles of the others (uploaded once a step)."""
+    key = ("attention_mma", group_size, rows_per_tile)
     plan = ctx.plans.get(key)
     if plan is not None:
         return plan
@@ -43,7 +43,7 @@ def _plan(ctx, group_size: int):
         tile_req, tile_row = [], []
         for r in others:
             rows = int(q_lens[r]) * group_size
-            starts = np.arange(0, rows, ROWS, dtype=np.int32)
+            starts = np.arange(0, rows, rows_per_tile, dtype=np.int32)
             tile_req.append(np.full(starts.size, r, dtype=np.int32))
             tile_row.append(starts)
         plan = {"decode": None, "prefill": None}
@@ -51,6 +51,10 @@ def _plan(ctx, group_size: int):
             plan["decode"] = (ctx.upload(decode), int(decode.size))
         if others.size:
             req, row = np.concatenate(tile_req), np.concatenate(tile_row)
+            # tiles that see the most keys first: the last CTAs to start are the short ones
+            keys_seen = ctx.kv_before_host[req] + row // group_size
+            order = np.argsort(-keys_seen, kind="stable")
+            req, row = req[order], row[order]
             both = ctx.upload(np.concatenate([req, row]))
             plan["prefill"] = (both[:req.size], both[req.size:], int(req.size))
     ctx.plans[key] = plan
@@ -62,7 +66,9 @@ def forward(mixer, ctx, qkv, cache, out) -> bool:
     group = nh // nkv
     if d not in (64, 128) or group > 16 or qkv.stride(0) % 8:
         return False
-    plan = _plan(ctx, group)
+    # prompt portions: the tcgen05 kernel for head_dim 128, else the mma.sync kernel
+    use_tc = (not ctx.decode_only) and ops.attention_tc_supported(d, group, cache.page_size)
+    plan = _plan(ctx, group, ops.attention_tc_rows(group) if use_tc else ROWS)
     common = dict(out=out, tokens=ctx.num_tokens, nh=nh, nkv=nkv, d=d, page_size=cache.page_size,
                   window=mixer.window, scale=mixer.scale)
     if plan["decode"] is not None:
@@ -70,7 +76,11 @@ def forward(mixer, ctx, qkv, cache, out) -> bool:
         splits = decode_splits(count, nkv, ctx.max_kv_len)
         ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, None,
                           count, rows16=True, splits=splits, **common)
-    if plan["prefill"] is not None:
+    if plan["prefill"] is not None and use_tc:
+        tile_req, tile_row, count = plan["prefill"]
+        ops.attention_tc(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row, count,
+                         out, nh, nkv, d, cache.page_size, mixer.window, mixer.scale)
+    elif plan["prefill"] is not None:
         tile_req, tile_row, count = plan["prefill"]
         ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row,
                           count, rows16=False, splits=1, **common)
