@@ -1,22 +1,25 @@
 // bfloat16 matrix product on the 5th-generation tensor cores:
 //     out[M, N] (+)= x[M, K] . w[N, K]^T (+ bias)          float32 accumulation in TMEM
 //
-// One CTA computes a 128 x BLOCK_Q tile.  Warp 0 streams 128-byte-swizzled K-major tiles
-// of both operands into a ring of shared-memory stages with TMA; one thread of warp 1
-// issues tcgen05.mma (UMMA 128 x BLOCK_Q x 16) from shared-memory descriptors into an
-// accumulator in tensor memory and commits each stage back to the producer; warps 2-5
-// read the accumulator with tcgen05.ld and run the epilogue.
+// All kernels share one structure: a producer thread streams 128-byte-swizzled K-major
+// tiles of both operands into a ring of shared-memory stages with TMA; one thread issues
+// tcgen05.mma (UMMA with 128 or 256 rows, K = 16) from shared-memory descriptors into an
+// accumulator in tensor memory and commits each stage back to the producer; four warps
+// read the accumulator with tcgen05.ld and run the epilogue (bias -> bf16, accumulate into
+// the float32 residual stream, SwiGLU over 16-interleaved gate/up rows, or float32 logits).
 //
-// Two orientations share the kernel:
-//   normal  (many tokens):  the 128 rows of the tile are tokens, the BLOCK_Q columns are
-//           weight rows; the epilogue writes the output directly (bias, accumulate into
-//           the float32 residual stream, SwiGLU over interleaved gate/up columns, or
-//           float32 logits).
-//   swapped (few tokens, decode): the 128 rows are WEIGHT rows, so that a handful of
-//           tokens still fills the tensor core's M; the tokens are the BLOCK_Q columns.
-//           K is split over blockIdx.z so that about one CTA per SM streams weights;
-//           each split writes a float32 partial [split][M][N], and a second small
-//           kernel adds the partials in a fixed order and applies the same epilogues.
+//   gemm_tc_swapped_kernel     few tokens (decode, M <= 256): the 128 tile rows are WEIGHT
+//       rows, so that a handful of tokens still fills the tensor core's M; the tokens are
+//       the 16..256 tile columns.  K is split over blockIdx.z and several small CTAs share
+//       an SM, so that the weight stream never pauses.  One split writes its output
+//       directly; several leave float32 partials [split][M][N] that splitk_finish_kernel
+//       (or a fused finishing kernel of the caller) adds in a fixed order.  The weight
+//       tiles of the first stages are requested before the wait on the preceding kernel.
+//   gemm_tc_persistent_kernel  many tokens: the rows are tokens; one CTA per SM walks over
+//       128 x block_q tiles with two accumulators in tensor memory, so that the epilogue of
+//       a tile overlaps the next tile's products; block_q is chosen for whole waves.
+//   gemm_tc_pair_kernel        the same with pairs of CTAs (cta_group::2) sharing a
+//       256 x block_q tile; selectable, it measures the same speed as the single-CTA form.
 //
 // Reference counterparts: cuBLAS through nn.Linear (v10_triton_paged_gqa/layer/gqa.py:
 // 122-124, 84; model/qwen2_5.py:83-87) and the Triton GEMMs swiglu_kernel/down_kernel
@@ -118,9 +121,9 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, c
   }
 }
 
-template <int BLOCK_Q, int STAGES, bool SWAP>
+template <int BLOCK_Q, int STAGES>
 __global__ void __launch_bounds__(THREADS)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
+gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
                const Params p) {
   constexpr int COL_TILE_BYTES = BLOCK_Q * BLOCK_K * 2;
   constexpr int STAGE_BYTES = ROW_TILE_BYTES + COL_TILE_BYTES;
@@ -168,7 +171,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
       // writes.  Its tiles for the first stages are requested before the wait on the
       // preceding kernel, so the weight stream is already running when the activations
       // (written by that kernel) become available.
-      const int ahead = SWAP ? min(min(STAGES, p.ahead), num_kb) : 0;
+      const int ahead = min(min(STAGES, p.ahead), num_kb);
       for (int it = 0; it < ahead; ++it) {
         mbar_expect_tx(&full[it], STAGE_BYTES);
         tma_load_2d(smem + it * STAGE_BYTES, &map_row, &full[it], (kb_begin + it) * BLOCK_K, row0);
@@ -236,44 +239,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constan
         for (int j = 16; j < 32; ++j) v[j] = 0.f;
       }
       const bool live = row < p.rows && num_kb > 0;
-      if constexpr (SWAP) {
-        // row = weight row n, columns = tokens m
-        if (p.partial != nullptr) {  // partial[split][m][n]; the finishing kernel adds the splits
-          if (live) {
-            float* dst = p.partial + ((size_t)blockIdx.z * p.cols) * p.rows + row;
-#pragma unroll
-            for (int j = 0; j < CHUNK; ++j) {
-              const int m = col0 + c + j;
-              if (m < p.cols) dst[(size_t)m * p.rows] = v[j];
-            }
-          }
-        } else if (p.epilogue == EPI_SWIGLU_BF16) {
-          // lanes 0-15 hold gate rows, lanes 16-31 the matching up rows (interleave of 16)
-          const int out_col = ((row0 + quarter * 32) >> 1) + lane;
-#pragma unroll
-          for (int j = 0; j < CHUNK; ++j) {
-            const float up = __shfl_down_sync(0xffffffffu, v[j], 16);
-            const int m = col0 + c + j;
-            if (live && lane < 16 && m < p.cols)
-              ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_col] = __float2bfloat16_rn(silu(v[j]) * up);
-          }
-        } else if (live) {
-          const float b = p.bias ? p.bias[row] : 0.f;
+      // row = weight row n, columns = tokens m
+      if (p.partial != nullptr) {  // partial[split][m][n]; the finishing kernel adds the splits
+        if (live) {
+          float* dst = p.partial + ((size_t)blockIdx.z * p.cols) * p.rows + row;
 #pragma unroll
           for (int j = 0; j < CHUNK; ++j) {
             const int m = col0 + c + j;
-            if (m >= p.cols) break;
-            const float r = v[j] + b;
-            if (p.epilogue == EPI_STORE_BF16)
-              ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + row] = __float2bfloat16_rn(r);
-            else if (p.epilogue == EPI_ACCUM_F32)
-              ((float*)p.out)[(size_t)m * p.ldo + row] += r;
-            else
-              ((float*)p.out)[(size_t)m * p.ldo + row] = r;
+            if (m < p.cols) dst[(size_t)m * p.rows] = v[j];
           }
         }
-      } else {
-        if (live) epilogue_chunk(p, row, col0 + c, v);
+      } else if (p.epilogue == EPI_SWIGLU_BF16) {
+        // lanes 0-15 hold gate rows, lanes 16-31 the matching up rows (interleave of 16)
+        const int out_col = ((row0 + quarter * 32) >> 1) + lane;
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) {
+          const float up = __shfl_down_sync(0xffffffffu, v[j], 16);
+          const int m = col0 + c + j;
+          if (live && lane < 16 && m < p.cols)
+            ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + out_col] = __float2bfloat16_rn(silu(v[j]) * up);
+        }
+      } else if (live) {
+        const float b = p.bias ? p.bias[row] : 0.f;
+#pragma unroll
+        for (int j = 0; j < CHUNK; ++j) {
+          const int m = col0 + c + j;
+          if (m >= p.cols) break;
+          const float r = v[j] + b;
+          if (p.epilogue == EPI_STORE_BF16)
+            ((__nv_bfloat16*)p.out)[(size_t)m * p.ldo + row] = __float2bfloat16_rn(r);
+          else if (p.epilogue == EPI_ACCUM_F32)
+            ((float*)p.out)[(size_t)m * p.ldo + row] += r;
+          else
+            ((float*)p.out)[(size_t)m * p.ldo + row] = r;
+        }
       }
     }
   }
@@ -680,17 +679,17 @@ Plan make_plan(int M, int N, int K) {
   return plan;
 }
 
-template <int BLOCK_Q, int STAGES, bool SWAP>
-int launch(const CUtensorMap& map_row, const CUtensorMap& map_col, const Params& p, dim3 grid, cudaStream_t stream) {
+template <int BLOCK_Q, int STAGES>
+int launch_swapped(const CUtensorMap& map_row, const CUtensorMap& map_col, const Params& p, dim3 grid, cudaStream_t stream) {
   constexpr int SMEM = STAGES * (ROW_TILE_BYTES + BLOCK_Q * BLOCK_K * 2) + 1024 + 256;
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(gemm_tc_kernel<BLOCK_Q, STAGES, SWAP>,
+    cudaError_t err = cudaFuncSetAttribute(gemm_tc_swapped_kernel<BLOCK_Q, STAGES>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  tl::launch_kernel(gemm_tc_kernel<BLOCK_Q, STAGES, SWAP>, grid, THREADS, SMEM, stream, map_row, map_col, p);
+  tl::launch_kernel(gemm_tc_swapped_kernel<BLOCK_Q, STAGES>, grid, THREADS, SMEM, stream, map_row, map_col, p);
   return TL_LAUNCH_CHECK();
 }
 
@@ -759,11 +758,11 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
     switch (plan.block_q) {
       // few stages a CTA, several CTAs an SM: while one CTA starts up or runs its epilogue
       // the others keep the weight stream going
-      case 16: rc = launch<16, 4, true>(map_row, map_col, p, grid, stream); break;    //  72 KB: 3 CTAs/SM
-      case 32: rc = launch<32, 4, true>(map_row, map_col, p, grid, stream); break;    //  80 KB: 2 CTAs/SM
-      case 64: rc = launch<64, 4, true>(map_row, map_col, p, grid, stream); break;    //  96 KB: 2 CTAs/SM
-      case 128: rc = launch<128, 3, true>(map_row, map_col, p, grid, stream); break;  //  96 KB: 2 CTAs/SM
-      default: rc = launch<256, 4, true>(map_row, map_col, p, grid, stream); break;
+      case 16: rc = launch_swapped<16, 4>(map_row, map_col, p, grid, stream); break;    //  72 KB: 3 CTAs/SM
+      case 32: rc = launch_swapped<32, 4>(map_row, map_col, p, grid, stream); break;    //  80 KB: 2 CTAs/SM
+      case 64: rc = launch_swapped<64, 4>(map_row, map_col, p, grid, stream); break;    //  96 KB: 2 CTAs/SM
+      case 128: rc = launch_swapped<128, 3>(map_row, map_col, p, grid, stream); break;  //  96 KB: 2 CTAs/SM
+      default: rc = launch_swapped<256, 4>(map_row, map_col, p, grid, stream); break;
     }
     if (rc || !partials) return rc;
     if (defer) {
