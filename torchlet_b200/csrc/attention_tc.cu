@@ -12,7 +12,8 @@
 //   MMA thread      S = Q K^T   (tcgen05.mma 128 x 128 x 16, Q and K K-major in shared
 //                   memory, S in tensor memory, double-buffered) and, one tile behind,
 //                   O += P V    (P K-major from shared memory, V as the MN-major operand);
-//   softmax warps   four warps, one thread per row: read S from tensor memory, mask by
+//   softmax warps   eight warps, two threads per row (each half of a tile's keys): read S
+//                   from tensor memory, mask by
 //                   position, keep the running max and sum in float32, write P as bfloat16
 //                   into shared memory, and rescale O in tensor memory when the row's max
 //                   has grown by more than 2^8 since O was last scaled (a smaller growth is
@@ -40,12 +41,23 @@ using namespace tc;
 constexpr int D = 128;          // head_dim
 constexpr int ROWS = 128;       // packed rows a CTA (UMMA M)
 constexpr int KEYS = 128;       // keys a tile (UMMA N of S, K of P V)
-constexpr int THREADS = 192;    // warps 0-3 softmax, 4 MMA, 5 loader
+constexpr int THREADS = 320;    // warps 0-7 softmax (two per TMEM lane quarter), 8 MMA, 9 loader
 constexpr int SLAB = ROWS * 128;  // bytes of a [128 rows][64 bf16] swizzled slab
 constexpr int TILE_BYTES = 2 * SLAB;  // a 128 x 128 bf16 operand tile = two slabs
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 __device__ int g_error_word = 0;
+
+#ifdef ATTN_TIMING
+__device__ unsigned long long g_timing[32];
+#define TIMING_BEGIN() long long t_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64();
+#define TICK(slot) { const long long t_now = clock64(); t_acc[slot] += t_now - t_last; t_last = t_now; }
+#define TIMING_END(base) if (lane == 0) { for (int t_i = 0; t_i < 8; ++t_i) atomicAdd(&g_timing[(base) + t_i], (unsigned long long)t_acc[t_i]); }
+#else
+#define TIMING_BEGIN()
+#define TICK(slot)
+#define TIMING_END(base)
+#endif
 
 struct Params {
   const __nv_bfloat16* q;
@@ -103,6 +115,15 @@ __device__ __forceinline__ void tmem_st_32(uint32_t taddr, const uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// float <-> unsigned code whose unsigned order is the floats' order (0 is below every float)
+__device__ __forceinline__ uint32_t ordered_code(float f) {
+  const uint32_t b = __float_as_uint(f);
+  return (b >> 31) ? ~b : (b | 0x80000000u);
+}
+__device__ __forceinline__ float ordered_value(uint32_t u) {
+  return __uint_as_float((u >> 31) ? (u & 0x7fffffffu) : ~u);
+}
+
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) {
   extern __shared__ uint8_t smem_raw[];
@@ -117,11 +138,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   uint64_t* k_empty = bars + 4;   // [2]
   uint64_t* v_empty = bars + 6;   // [2]
   uint64_t* s_full = bars + 8;    // [2]
-  uint64_t* s_empty = bars + 10;  // [2]  (4 arrivals: one per softmax warp)
-  uint64_t* p_full = bars + 12;   // [2]  (4 arrivals)
+  uint64_t* s_empty = bars + 10;  // [2]  (8 arrivals: one per softmax warp)
+  uint64_t* p_full = bars + 12;   // [2]  (8 arrivals)
   uint64_t* p_empty = bars + 14;  // [2]  P V of the tile that used this P buffer is done
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // [3][128 rows] row maxima of three consecutive tiles (order-preserving unsigned codes, joined by
+  // atomicMax from the two halves), then [2 halves][128] row sums at the end
+  uint32_t* exchange = reinterpret_cast<uint32_t*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = p.tile_req[blockIdx.x];
@@ -146,15 +170,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 4);
-      mbar_init(&p_full[i], 4);
+      mbar_init(&s_empty[i], 8);
+      mbar_init(&p_full[i], 8);
       mbar_init(&p_empty[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
+  }
+  for (int i = threadIdx.x; i < 3 * ROWS; i += THREADS) exchange[i] = 0u;
+  if (threadIdx.x == 0) {
     prefetch_tensormap(&map_kv);
   }
-  if (warp == 4) {
+  if (warp == 8) {
     tmem_alloc<512>(tmem_slot);
     tmem_relinquish();
   }
@@ -179,54 +206,51 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_o = tmem_base + 256;
 
-  if (warp == 5) {
+  if (warp == 9) {
     // ------------------------------------------------------------------ loader
-    if (lane == 0) {
-      const int pages_per_tile = KEYS / p.page_size;
-      for (int j = 0; j < num_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t phase = (j >> 1) & 1;
-        const int first_page = (tile_begin + j) * pages_per_tile;
-        int page_of[16];  // pages of this tile (page_size >= 8, so at most 16); beyond the table: page 0
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          const int index = first_page + i;
-          page_of[i] = (i < pages_per_tile && index < p.table_width) ? table[index] : 0;
-        }
-        mbar_wait(&k_empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
-        mbar_expect_tx(&k_full[s], TILE_BYTES);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          if (i < pages_per_tile) {
-            const int row = ((page_of[i] * 2 + 0) * p.nkv + kvh) * p.page_size;
-            uint8_t* dst = k_tiles + s * TILE_BYTES + i * p.page_size * 128;
-            tma_load_2d(dst, &map_kv, &k_full[s], 0, row);
-            tma_load_2d(dst + SLAB, &map_kv, &k_full[s], 64, row);
-          }
-        }
-        mbar_wait(&v_empty[s], phase ^ 1, abort_flag, &g_error_word, 2);
-        mbar_expect_tx(&v_full[s], TILE_BYTES);
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-          if (i < pages_per_tile) {
-            const int row = ((page_of[i] * 2 + 1) * p.nkv + kvh) * p.page_size;
-            uint8_t* dst = v_tiles + s * TILE_BYTES + i * p.page_size * 128;
-            tma_load_2d(dst, &map_kv, &v_full[s], 0, row);
-            tma_load_2d(dst + SLAB, &map_kv, &v_full[s], 64, row);
-          }
-        }
-      }
+    // Lane l copies half (l & 1) of page (l >> 1) of every tile: a box of page_size keys x 64
+    // elements (page_size >= 8, so a tile has at most 16 pages).
+    const int pages_per_tile = KEYS / p.page_size;
+    const int my_page = lane >> 1, my_half = lane & 1;
+    const bool active = my_page < pages_per_tile;
+    TIMING_BEGIN();
+    for (int j = 0; j < num_tiles; ++j) {
+      const int s = j & 1;
+      const uint32_t phase = (j >> 1) & 1;
+      const int index = (tile_begin + j) * pages_per_tile + my_page;
+      const int page = (active && index < p.table_width) ? table[index] : 0;  // beyond the table: page 0
+      const uint32_t offset = s * TILE_BYTES + my_half * SLAB + my_page * p.page_size * 128;
+      TICK(0);
+      mbar_wait(&k_empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
+      TICK(1);
+      if (lane == 0) mbar_expect_tx(&k_full[s], TILE_BYTES);
+      __syncwarp();
+      if (active)
+        tma_load_2d(k_tiles + offset, &map_kv, &k_full[s], my_half * 64, ((page * 2 + 0) * p.nkv + kvh) * p.page_size);
+      TICK(2);
+      mbar_wait(&v_empty[s], phase ^ 1, abort_flag, &g_error_word, 2);
+      TICK(3);
+      if (lane == 0) mbar_expect_tx(&v_full[s], TILE_BYTES);
+      __syncwarp();
+      if (active)
+        tma_load_2d(v_tiles + offset, &map_kv, &v_full[s], my_half * 64, ((page * 2 + 1) * p.nkv + kvh) * p.page_size);
+      TICK(4);
     }
-  } else if (warp == 4) {
+    TIMING_END(0);
+  } else if (warp == 8) {
     // --------------------------------------------------------------------- MMA
     if (lane == 0) {
       const uint32_t idesc_s = idesc_bf16_f32(ROWS, KEYS);
       const uint32_t idesc_o = idesc_pv();
       const uint32_t q_addr = smem_addr(q_tile);
+      TIMING_BEGIN();
       auto issue_pv = [&](int j) {  // O (+)= P_j V_j
         const int s = j & 1;
+        TICK(3);
         mbar_wait(&p_full[s], (j >> 1) & 1, abort_flag, &g_error_word, 5);
+        TICK(4);
         mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, &g_error_word, 6);
+        TICK(5);
         fence_after_sync();
         const uint32_t v_addr = smem_addr(v_tiles + s * TILE_BYTES);
         const uint32_t p_addr = smem_addr(p_tiles + s * TILE_BYTES);
@@ -238,12 +262,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         }
         mma_commit(&v_empty[s]);
         mma_commit(&p_empty[s]);
+        TICK(6);
       };
       for (int j = 0; j < num_tiles; ++j) {
         const int s = j & 1;
         const uint32_t phase = (j >> 1) & 1;
+        TICK(0);
         mbar_wait(&k_full[s], phase, abort_flag, &g_error_word, 3);
+        TICK(1);
         mbar_wait(&s_empty[s], phase ^ 1, abort_flag, &g_error_word, 4);
+        TICK(2);
         fence_after_sync();
         const uint32_t k_addr = smem_addr(k_tiles + s * TILE_BYTES);
 #pragma unroll
@@ -257,30 +285,37 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         if (j > 0) issue_pv(j - 1);  // one tile behind, so S of this tile overlaps the softmax of the last
       }
       if (num_tiles > 0) issue_pv(num_tiles - 1);
+      TIMING_END(8);
     }
   } else {
     // ----------------------------------------------------------------- softmax
-    const int r = warp * 32 + lane;  // row of the tile = lane of tensor memory
+    // Two threads a row: warps 0-3 take keys (and output columns) 0-63 of every tile, warps
+    // 4-7 take 64-127; the halves agree on the row's maximum through shared memory.
+    const int quarter = warp & 3, half = warp >> 2;
+    const int r = quarter * 32 + lane;  // row of the tile = lane of tensor memory
     const int row = row_start + r;
     const bool row_valid = r < p.rows_per_tile && row < row_end;
     const int pos = row_valid ? before + row / g : -1;
     const int lo = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
-    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
-    float m_ref = -INFINITY, l_sum = 0.f;  // m_ref in log2 units (already scaled)
+    const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+    constexpr int HALF = KEYS / 2;
+    float m_ref = -INFINITY, l_sum = 0.f;  // m_ref in log2 units (already scaled); l_sum of this half
+    TIMING_BEGIN();
     for (int j = 0; j < num_tiles; ++j) {
       const int s = j & 1;
-      const int key0 = (tile_begin + j) * KEYS;
+      TICK(0);
+      const int key0 = (tile_begin + j) * KEYS + half * HALF;  // first key of this thread's half
       mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, &g_error_word, 7);
+      TICK(1);
       fence_after_sync();
-      const uint32_t s_addr = tmem_base + s * KEYS + lane_base;
-      // A tile whose keys are all visible to every row of this warp needs no masking
-      // (all but the one or two tiles on the diagonal or at the window's edge).
-      const bool visible = key0 + KEYS - 1 <= pos && key0 >= lo;
+      const uint32_t s_addr = tmem_base + s * KEYS + half * HALF + lane_base;
+      // A half tile whose keys are all visible to every row of this warp needs no masking
+      const bool visible = key0 + HALF - 1 <= pos && key0 >= lo;
       const bool warp_visible = __all_sync(0xffffffffu, visible);
-      // pass 1: the row's maximum over the keys it may see (in raw score units)
+      // pass 1: the row's maximum over the keys of this half (in raw score units)
       float m_a = -INFINITY, m_b = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < KEYS; c += 32) {
+      for (int c = 0; c < HALF; c += 32) {
         uint32_t v[32];
         tmem_ld_32(s_addr + c, v);
         tmem_ld_wait();
@@ -298,7 +333,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
           }
         }
       }
-      const float m_tile = fmaxf(m_a, m_b) * p.scale_log2;  // the scale is positive: max commutes with it
+      TICK(2);
+      // Both halves join their maxima in the tile's slot; the slot of the tile after next was last
+      // read before the previous barrier and is written again only after the next one.
+      atomicMax(&exchange[(j % 3) * ROWS + r], ordered_code(fmaxf(m_a, m_b)));
+      asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps
+      const float m_tile = ordered_value(exchange[(j % 3) * ROWS + r]) * p.scale_log2;  // the scale is positive
+      if (half == 0) exchange[((j + 2) % 3) * ROWS + r] = 0u;
       // the reference max moves only when the row's max has grown past the threshold
       float factor = 1.f;
       bool rescale = false;
@@ -308,28 +349,31 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         m_ref = m_tile;
       }
       l_sum *= factor;
+      TICK(3);
       // this tile's P buffer is free once P V of the tile before last is done
       mbar_wait(&p_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, &g_error_word, 8);
+      TICK(4);
       if (__any_sync(0xffffffffu, rescale)) {
         // O may only be touched when no P V is in flight: wait for the previous tile's
         mbar_wait(&p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, &g_error_word, 10);
         fence_after_sync();
 #pragma unroll 1
-        for (int c = 0; c < D; c += 32) {
+        for (int c = 0; c < D / 2; c += 32) {  // this thread's half of the output columns
           uint32_t v[32];
-          tmem_ld_32(tmem_o + lane_base + c, v);
+          tmem_ld_32(tmem_o + lane_base + half * (D / 2) + c, v);
           tmem_ld_wait();
 #pragma unroll
           for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
-          tmem_st_32(tmem_o + lane_base + c, v);
+          tmem_st_32(tmem_o + lane_base + half * (D / 2) + c, v);
         }
         tmem_st_wait();
       }
+      TICK(5);
       // pass 2: P = exp2(S * scale - m_ref), row sum, P as bfloat16 into shared memory
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum_a = 0.f, sum_b = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < KEYS; c += 32) {
+      for (int c = 0; c < HALF; c += 32) {
         uint32_t v[32];
         tmem_ld_32(s_addr + c, v);
         tmem_ld_wait();
@@ -358,13 +402,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
           }
         }
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {  // four 16-byte chunks of 8 keys
-          const int c16 = (c >> 3) + q4;
-          uint8_t* dst = p_tiles + s * TILE_BYTES + (c16 >> 3) * SLAB + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
+        for (int q4 = 0; q4 < 4; ++q4) {  // four 16-byte chunks of 8 keys; a half is one slab
+          const int c8 = (c >> 3) + q4;
+          uint8_t* dst = p_tiles + s * TILE_BYTES + half * SLAB + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
           *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
         }
       }
       l_sum += sum_a + sum_b;
+      TICK(6);
       fence_proxy_async();   // P is read by the tensor core
       fence_before_sync();   // our tcgen05.ld/st of S and O are done
       __syncwarp();
@@ -372,18 +417,27 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         mbar_arrive(&s_empty[s]);
         mbar_arrive(&p_full[s]);
       }
+      TICK(7);
     }
-    // ---- output: O / l
+    if (warp == 0) TIMING_END(16);
+    if (warp == 4) TIMING_END(24);
+    // ---- output: O / l (the two halves add their sums)
+    float* sums = reinterpret_cast<float*>(exchange);
+    asm volatile("bar.sync 1, 256;" ::: "memory");  // the last tile's maxima have been read
+    sums[half * ROWS + r] = l_sum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    const float l_all = sums[r] + sums[ROWS + r];
     if (num_tiles > 0)
       mbar_wait(&p_empty[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1, abort_flag, &g_error_word, 9);
     fence_after_sync();
-    const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
     __nv_bfloat16* dst = nullptr;
-    if (row_valid) dst = p.out + (size_t)(tok0 + row / g) * p.out_stride + (size_t)(kvh * g + row % g) * D;
+    if (row_valid)
+      dst = p.out + (size_t)(tok0 + row / g) * p.out_stride + (size_t)(kvh * g + row % g) * D + half * (D / 2);
 #pragma unroll 1
-    for (int c = 0; c < D; c += 32) {
+    for (int c = 0; c < D / 2; c += 32) {
       uint32_t v[32];
-      tmem_ld_32(tmem_o + lane_base + c, v);
+      tmem_ld_32(tmem_o + lane_base + half * (D / 2) + c, v);
       tmem_ld_wait();
       if (row_valid && num_tiles > 0) {
         uint32_t packed[16];
@@ -402,7 +456,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   __syncwarp();
   fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     fence_after_sync();
     tmem_dealloc<512>(tmem_base);
   }
@@ -440,6 +494,14 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_
 }  // namespace
 
 extern "C" {
+
+#ifdef ATTN_TIMING
+int tl_attention_tc_timing(unsigned long long* out) {  // reads and clears the 32 counters
+  unsigned long long zero[32] = {};
+  if (cudaMemcpyFromSymbol(out, g_timing, sizeof(zero)) != cudaSuccess) return -1;
+  return (int)cudaMemcpyToSymbol(g_timing, zero, sizeof(zero));
+}
+#endif
 
 int tl_attention_tc_error() {
   int value = 0, zero = 0;
@@ -481,7 +543,8 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.window = window;
   p.rows_per_tile = tl_attention_tc_rows(nh / nkv);
   p.scale_log2 = scale * 1.4426950408889634f;
-  constexpr int SMEM = 7 * TILE_BYTES + 1024 + 256;
+  constexpr int SMEM = 7 * TILE_BYTES + 1024 + 256 + 3 * ROWS * 4;
+  static_assert(SMEM <= 232448, "shared memory of one CTA");
   static bool configured = false;
   if (!configured) {
     cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
