@@ -434,7 +434,7 @@ def test_attention_tc(case):
     scale = 0.37 / math.sqrt(d)
     want = plain_attention(x["dense"], before, nh, nkv, window, scale)
     rows = ops.attention_tc_rows(group)
-    assert rows == (128 // group) * group
+    assert rows == 2 * (128 // group) * group  # two row tiles of whole tokens a CTA
     tile_req, tile_row = [], []
     for r, q in enumerate(q_lens):
         for start in range(0, q * group, rows):

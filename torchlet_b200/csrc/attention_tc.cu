@@ -1,23 +1,30 @@
 // Paged causal grouped-query attention for PROMPT PORTIONS on the 5th-generation tensor
 // cores (tcgen05), bfloat16, head_dim 128.
 //
-// One CTA takes up to 128 PACKED ROWS of one (request, KV head): the pairs (token of the
-// step, query head of the KV head's group), token-major, so every key/value tile that is
-// loaded serves all query heads of the group.  It walks over the keys in tiles of 128
-// absolute positions:
+// One CTA takes two tiles of up to 128 PACKED ROWS of one (request, KV head): the pairs
+// (token of the step, query head of the KV head's group), token-major, so every key/value
+// tile that is loaded serves all query heads of the group and both row tiles.  It walks
+// over the keys in tiles of 128 absolute positions:
 //
-//   loader thread   TMA-loads the tile's pages of K and V (one box of page_size x 64
-//                   elements per page and half of the head, 128-byte swizzle) through the
-//                   block table into a two-stage ring;
-//   MMA thread      S = Q K^T   (tcgen05.mma 128 x 128 x 16, Q and K K-major in shared
-//                   memory, S in tensor memory, double-buffered) and, one tile behind,
-//                   O += P V    (P K-major from shared memory, V as the MN-major operand);
-//   softmax warps   eight warps, two threads per row (each half of a tile's keys): read S
-//                   from tensor memory, mask by
-//                   position, keep the running max and sum in float32, write P as bfloat16
-//                   into shared memory, and rescale O in tensor memory when the row's max
-//                   has grown by more than 2^8 since O was last scaled (a smaller growth is
-//                   carried in P, whose exponent range has room for it).
+//   loader warp     TMA-loads the tile's pages of K and V (one box of page_size x 64
+//                   elements per page and half of the head, 128-byte swizzle, one lane per
+//                   box) through the block table into a two-stage ring;
+//   MMA thread      for each row tile X in turn:  O_X += P_X V of the previous key tile
+//                   (P_X read from tensor memory, V as the MN-major operand from shared
+//                   memory), then S_X = Q_X K^T of this key tile (Q and K K-major in shared
+//                   memory).  S_X, P_X (in the first half of S_X's columns) and O_X live
+//                   in tensor memory: 2 x 128 + 2 x 128 columns, all 512;
+//   softmax warps   four warps per row tile, one thread per row: read the row of S from
+//                   tensor memory, mask by position, keep the running max and sum in
+//                   float32, write P as bfloat16 over S, and rescale O in tensor memory
+//                   when the row's max has grown by more than 2^8 since O was last scaled
+//                   (a smaller growth is carried in P, whose exponent range has room for
+//                   it).  While one row tile is in its softmax the tensor core works for
+//                   the other.
+//
+// The tensor core executes one thread's MMAs in the order of issue, so S_X of the next key
+// tile, issued after P_X V of this one, cannot overwrite P_X early, and O_X is at rest
+// whenever S_X has arrived (the arrival covers the P_X V before it).
 //
 // At the end the softmax warps divide O by the row sums and store bfloat16 output.
 // Numerics are those of attention_mma.cu and of the reference's Triton kernel
@@ -39,9 +46,10 @@ namespace {
 using namespace tc;
 
 constexpr int D = 128;          // head_dim
-constexpr int ROWS = 128;       // packed rows a CTA (UMMA M)
+constexpr int ROWS = 128;       // packed rows of a row tile (UMMA M)
+constexpr int QTILES = 2;       // row tiles a CTA
 constexpr int KEYS = 128;       // keys a tile (UMMA N of S, K of P V)
-constexpr int THREADS = 320;    // warps 0-7 softmax (two per TMEM lane quarter), 8 MMA, 9 loader
+constexpr int THREADS = 320;    // warps 0-3 softmax of row tile 0, 4-7 of row tile 1, 8 MMA, 9 loader
 constexpr int SLAB = ROWS * 128;  // bytes of a [128 rows][64 bf16] swizzled slab
 constexpr int TILE_BYTES = 2 * SLAB;  // a 128 x 128 bf16 operand tile = two slabs
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
@@ -50,8 +58,11 @@ __device__ int g_error_word = 0;
 
 #ifdef ATTN_TIMING
 __device__ unsigned long long g_timing[32];
-#define TIMING_BEGIN() long long t_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64();
-#define TICK(slot) { const long long t_now = clock64(); t_acc[slot] += t_now - t_last; t_last = t_now; }
+__device__ long long g_trace[5][256];  // MMA thread, warps 0-3, (others)
+#define TIMING_BEGIN() long long t_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64(); int t_count = 0; \
+    const int t_role = warp == 8 ? 0 : warp < 4 ? warp + 1 : 4;
+#define TICK(slot) { const long long t_now = clock64(); t_acc[slot] += t_now - t_last; t_last = t_now; \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && t_count < 256 && (warp == 8 || warp < 4)) { g_trace[t_role][t_count] = (t_now << 4) | (slot); ++t_count; } }
 #define TIMING_END(base) if (lane == 0) { for (int t_i = 0; t_i < 8; ++t_i) atomicAdd(&g_timing[(base) + t_i], (unsigned long long)t_acc[t_i]); }
 #else
 #define TIMING_BEGIN()
@@ -102,6 +113,17 @@ __device__ __forceinline__ uint64_t smem_desc_v(uint32_t saddr) {
   return desc;
 }
 
+// D (+)= A B with A read from tensor memory: row i of A in lane i, two bfloat16 of
+// consecutive k in each 32-bit column (16 k = 8 columns an instruction).
+__device__ __forceinline__ void mma_bf16_a_tmem(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc,
+                                                bool accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}\n" ::"r"(tmem_d),
+      "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"((uint32_t)accumulate)
+      : "memory");
+}
+
 __device__ __forceinline__ void tmem_st_32(uint32_t taddr, const uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -115,53 +137,54 @@ __device__ __forceinline__ void tmem_st_32(uint32_t taddr, const uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
-// float <-> unsigned code whose unsigned order is the floats' order (0 is below every float)
-__device__ __forceinline__ uint32_t ordered_code(float f) {
-  const uint32_t b = __float_as_uint(f);
-  return (b >> 31) ? ~b : (b | 0x80000000u);
-}
-__device__ __forceinline__ float ordered_value(uint32_t u) {
-  return __uint_as_float((u >> 31) ? (u & 0x7fffffffu) : ~u);
-}
+// Key tiles [begin, end) that row tile X of the CTA needs; rows [row_start, row_end).
+struct RowTile {
+  int row_start, row_end, begin, end;
+};
 
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_tile = smem;                       // 32 KB
-  uint8_t* p_tiles = smem + TILE_BYTES;         // 2 x 32 KB
-  uint8_t* k_tiles = smem + 3 * TILE_BYTES;     // 2 x 32 KB
-  uint8_t* v_tiles = smem + 5 * TILE_BYTES;     // 2 x 32 KB
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 7 * TILE_BYTES);
-  uint64_t* k_full = bars;        // [2]
-  uint64_t* v_full = bars + 2;    // [2]
-  uint64_t* k_empty = bars + 4;   // [2]
-  uint64_t* v_empty = bars + 6;   // [2]
-  uint64_t* s_full = bars + 8;    // [2]
-  uint64_t* s_empty = bars + 10;  // [2]  (8 arrivals: one per softmax warp)
-  uint64_t* p_full = bars + 12;   // [2]  (8 arrivals)
-  uint64_t* p_empty = bars + 14;  // [2]  P V of the tile that used this P buffer is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+  uint8_t* q_tiles = smem;                      // 2 x 32 KB
+  uint8_t* k_tiles = smem + 2 * TILE_BYTES;     // 2 x 32 KB
+  uint8_t* v_tiles = smem + 4 * TILE_BYTES;     // 2 x 32 KB
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
+  uint64_t* k_full = bars;        // [2 stages]
+  uint64_t* v_full = bars + 2;    // [2 stages]
+  uint64_t* k_empty = bars + 4;   // [2 stages]
+  uint64_t* v_empty = bars + 6;   // [2 stages]
+  uint64_t* s_full = bars + 8;    // [2 row tiles]  S_X of the next key tile is in tensor memory
+  uint64_t* p_full = bars + 10;   // [2 row tiles]  (4 arrivals: one per softmax warp) P_X is written
+  uint64_t* o_done = bars + 12;   // [2 row tiles]  the last P_X V is done
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  // [3][128 rows] row maxima of three consecutive tiles (order-preserving unsigned codes, joined by
-  // atomicMax from the two halves), then [2 halves][128] row sums at the end
-  uint32_t* exchange = reinterpret_cast<uint32_t*>(tmem_slot + 4);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = p.tile_req[blockIdx.x];
-  const int row_start = p.tile_row[blockIdx.x];
   const int kvh = blockIdx.y;
   const int g = p.nh / p.nkv;
   const int tok0 = p.req_indptr[req];
   const int q_len = p.req_indptr[req + 1] - tok0;
   const int before = p.kv_before[req];
-  const int row_end = min(q_len * g, row_start + p.rows_per_tile);
   const int* table = p.block_table + (size_t)req * p.table_width;
-  const int first_tok = row_start / g, last_tok = (max(row_end, row_start + 1) - 1) / g;
-  const int hi_key = before + last_tok;
-  const int lo_key = p.window > 0 ? max(0, before + first_tok - p.window + 1) : 0;
-  const int tile_begin = lo_key / KEYS, tile_end = hi_key / KEYS + 1;
-  const int num_tiles = tile_end - tile_begin;
+  RowTile tile[QTILES];
+#pragma unroll
+  for (int x = 0; x < QTILES; ++x) {
+    RowTile& t = tile[x];
+    t.row_start = p.tile_row[blockIdx.x] + x * p.rows_per_tile;
+    t.row_end = min(q_len * g, t.row_start + p.rows_per_tile);
+    t.begin = t.end = 0;
+    if (t.row_start < t.row_end) {
+      const int first_tok = t.row_start / g, last_tok = (t.row_end - 1) / g;
+      const int lo_key = p.window > 0 ? max(0, before + first_tok - p.window + 1) : 0;
+      t.begin = lo_key / KEYS;
+      t.end = (before + last_tok) / KEYS + 1;
+    }
+  }
+  // Later rows need later keys, so the CTA's key tiles are [first of tile 0, last of the last tile)
+  const int j_begin = tile[0].begin;
+  const int j_end = max(tile[0].end, tile[1].end);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -170,15 +193,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       mbar_init(&k_empty[i], 1);
       mbar_init(&v_empty[i], 1);
       mbar_init(&s_full[i], 1);
-      mbar_init(&s_empty[i], 8);
-      mbar_init(&p_full[i], 8);
-      mbar_init(&p_empty[i], 1);
+      mbar_init(&p_full[i], 4);
+      mbar_init(&o_done[i], 1);
     }
     *abort_flag = 0;
     mbar_fence_init();
-  }
-  for (int i = threadIdx.x; i < 3 * ROWS; i += THREADS) exchange[i] = 0u;
-  if (threadIdx.x == 0) {
     prefetch_tensormap(&map_kv);
   }
   if (warp == 8) {
@@ -189,13 +208,13 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   tl::pdl_wait();  // q and this step's keys and values come from the preceding kernels
 
   // ---- Q rows into shared memory in the K-major swizzled layout (all threads)
-  for (int i = threadIdx.x; i < ROWS * (D / 8); i += THREADS) {
-    const int r = i / (D / 8), c16 = i % (D / 8);
-    const int row = row_start + r;
-    const bool valid = r < p.rows_per_tile && row < row_end;
+  for (int i = threadIdx.x; i < QTILES * ROWS * (D / 8); i += THREADS) {
+    const int x = i / (ROWS * (D / 8)), r = (i / (D / 8)) % ROWS, c16 = i % (D / 8);
+    const int row = (x == 0 ? tile[0].row_start : tile[1].row_start) + r;
+    const bool valid = r < p.rows_per_tile && row < (x == 0 ? tile[0].row_end : tile[1].row_end);
     const __nv_bfloat16* src = p.q;
     if (valid) src = p.q + (size_t)(tok0 + row / g) * p.q_stride + (size_t)(kvh * g + row % g) * D + c16 * 8;
-    uint8_t* dst = q_tile + (c16 >> 3) * SLAB + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
+    uint8_t* dst = q_tiles + x * TILE_BYTES + (c16 >> 3) * SLAB + r * 128 + (((c16 & 7) ^ (r & 7)) << 4);
     cp_async_16(dst, src, valid);
   }
   asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;" ::: "memory");
@@ -204,20 +223,20 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   __syncthreads();
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_o = tmem_base + 256;
 
   if (warp == 9) {
     // ------------------------------------------------------------------ loader
     // Lane l copies half (l & 1) of page (l >> 1) of every tile: a box of page_size keys x 64
-    // elements (page_size >= 8, so a tile has at most 16 pages).
+    // elements (page_size >= 8, so a tile has at most 16 pages).  Thirty-two copies issued
+    // by one thread take longer than the tile's arithmetic.
     const int pages_per_tile = KEYS / p.page_size;
     const int my_page = lane >> 1, my_half = lane & 1;
     const bool active = my_page < pages_per_tile;
     TIMING_BEGIN();
-    for (int j = 0; j < num_tiles; ++j) {
-      const int s = j & 1;
-      const uint32_t phase = (j >> 1) & 1;
-      const int index = (tile_begin + j) * pages_per_tile + my_page;
+    for (int j = j_begin; j < j_end; ++j) {
+      const int jj = j - j_begin, s = jj & 1;
+      const uint32_t phase = (jj >> 1) & 1;
+      const int index = j * pages_per_tile + my_page;
       const int page = (active && index < p.table_width) ? table[index] : 0;  // beyond the table: page 0
       const uint32_t offset = s * TILE_BYTES + my_half * SLAB + my_page * p.page_size * 128;
       TICK(0);
@@ -242,104 +261,105 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     if (lane == 0) {
       const uint32_t idesc_s = idesc_bf16_f32(ROWS, KEYS);
       const uint32_t idesc_o = idesc_pv();
-      const uint32_t q_addr = smem_addr(q_tile);
+      // Descriptors of the operands' first 16-wide slices; a later slice adds its byte offset / 16
+      // to the address field (the tiles lie below 256 KB, so the field never carries).
+      const uint64_t q_desc[QTILES] = {smem_desc_sw128(smem_addr(q_tiles)), smem_desc_sw128(smem_addr(q_tiles + TILE_BYTES))};
+      const uint64_t k_desc[2] = {smem_desc_sw128(smem_addr(k_tiles)), smem_desc_sw128(smem_addr(k_tiles + TILE_BYTES))};
+      const uint64_t v_desc[2] = {smem_desc_v(smem_addr(v_tiles)), smem_desc_v(smem_addr(v_tiles + TILE_BYTES))};
       TIMING_BEGIN();
-      auto issue_pv = [&](int j) {  // O (+)= P_j V_j
-        const int s = j & 1;
-        TICK(3);
-        mbar_wait(&p_full[s], (j >> 1) & 1, abort_flag, &g_error_word, 5);
-        TICK(4);
-        mbar_wait(&v_full[s], (j >> 1) & 1, abort_flag, &g_error_word, 6);
-        TICK(5);
-        fence_after_sync();
-        const uint32_t v_addr = smem_addr(v_tiles + s * TILE_BYTES);
-        const uint32_t p_addr = smem_addr(p_tiles + s * TILE_BYTES);
+      // One step past the last key tile, for the P V that runs a tile behind
+      for (int j = j_begin; j <= j_end; ++j) {
+        const int jj = j - j_begin;
+        bool k_ready = false, v_ready = false;
 #pragma unroll
-        for (int k = 0; k < KEYS / 16; ++k) {
-          const uint64_t a_desc = smem_desc_sw128(p_addr + (k >> 2) * SLAB + (k & 3) * 32);
-          const uint64_t b_desc = smem_desc_v(v_addr + k * 2048);  // 16 keys = two 8-key atoms
-          mma_bf16(tmem_o, a_desc, b_desc, idesc_o, j > 0 || k > 0);
-        }
-        mma_commit(&v_empty[s]);
-        mma_commit(&p_empty[s]);
-        TICK(6);
-      };
-      for (int j = 0; j < num_tiles; ++j) {
-        const int s = j & 1;
-        const uint32_t phase = (j >> 1) & 1;
-        TICK(0);
-        mbar_wait(&k_full[s], phase, abort_flag, &g_error_word, 3);
-        TICK(1);
-        mbar_wait(&s_empty[s], phase ^ 1, abort_flag, &g_error_word, 4);
-        TICK(2);
-        fence_after_sync();
-        const uint32_t k_addr = smem_addr(k_tiles + s * TILE_BYTES);
+        for (int x = 0; x < QTILES; ++x) {
+          const uint32_t tmem_s = tmem_base + x * KEYS;         // S_x, and P_x in its first 64 columns
+          const uint32_t tmem_o = tmem_base + 256 + x * D;      // O_x
+          if (j - 1 >= tile[x].begin && j - 1 < tile[x].end) {  // O_x (+)= P_x V of key tile j - 1
+            const int t = j - 1 - tile[x].begin;
+            TICK(0);
+            mbar_wait(&p_full[x], t & 1, abort_flag, &g_error_word, 5);
+            TICK(1 + x);
+            if (!v_ready) mbar_wait(&v_full[(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort_flag, &g_error_word, 6);
+            v_ready = true;
+            TICK(3);
+            fence_after_sync();
+            const uint64_t b_desc = ((jj - 1) & 1) ? v_desc[1] : v_desc[0];
 #pragma unroll
-        for (int k = 0; k < D / 16; ++k) {
-          const uint64_t a_desc = smem_desc_sw128(q_addr + (k >> 2) * SLAB + (k & 3) * 32);
-          const uint64_t b_desc = smem_desc_sw128(k_addr + (k >> 2) * SLAB + (k & 3) * 32);
-          mma_bf16(tmem_base + s * KEYS, a_desc, b_desc, idesc_s, k > 0);
+            for (int k = 0; k < KEYS / 16; ++k)  // 16 keys: 8 columns of P, two 8-key atoms of V (2048 bytes)
+              mma_bf16_a_tmem(tmem_o, tmem_s + k * 8, b_desc + (uint64_t)(k * (2048 >> 4)), idesc_o, t > 0 || k > 0);
+            if (j == tile[x].end) mma_commit(&o_done[x]);
+            TICK(4);
+          }
+          if (j >= tile[x].begin && j < tile[x].end) {  // S_x = Q_x K^T of key tile j
+            TICK(0);
+            if (!k_ready) mbar_wait(&k_full[jj & 1], (jj >> 1) & 1, abort_flag, &g_error_word, 3);
+            k_ready = true;
+            TICK(5);
+            fence_after_sync();
+            const uint64_t a_desc = q_desc[x];
+            const uint64_t b_desc = (jj & 1) ? k_desc[1] : k_desc[0];
+#pragma unroll
+            for (int k = 0; k < D / 16; ++k) {  // slab k / 4, 32 bytes a slice within its 128-byte rows
+              const uint64_t offset = (uint64_t)(((k >> 2) * SLAB + (k & 3) * 32) >> 4);
+              mma_bf16(tmem_s, a_desc + offset, b_desc + offset, idesc_s, k > 0);
+            }
+            mma_commit(&s_full[x]);
+            TICK(6);
+          }
         }
-        mma_commit(&k_empty[s]);
-        mma_commit(&s_full[s]);
-        if (j > 0) issue_pv(j - 1);  // one tile behind, so S of this tile overlaps the softmax of the last
+        if (j < j_end) mma_commit(&k_empty[jj & 1]);
+        if (jj > 0) mma_commit(&v_empty[(jj - 1) & 1]);
       }
-      if (num_tiles > 0) issue_pv(num_tiles - 1);
       TIMING_END(8);
     }
   } else {
     // ----------------------------------------------------------------- softmax
-    // Two threads a row: warps 0-3 take keys (and output columns) 0-63 of every tile, warps
-    // 4-7 take 64-127; the halves agree on the row's maximum through shared memory.
-    const int quarter = warp & 3, half = warp >> 2;
+    const int x = warp >> 2, quarter = warp & 3;
+    const RowTile mine = x == 0 ? tile[0] : tile[1];
     const int r = quarter * 32 + lane;  // row of the tile = lane of tensor memory
-    const int row = row_start + r;
-    const bool row_valid = r < p.rows_per_tile && row < row_end;
+    const int row = mine.row_start + r;
+    const bool row_valid = r < p.rows_per_tile && row < mine.row_end;
     const int pos = row_valid ? before + row / g : -1;
     const int lo = (row_valid && p.window > 0) ? max(0, pos - p.window + 1) : 0;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-    constexpr int HALF = KEYS / 2;
-    float m_ref = -INFINITY, l_sum = 0.f;  // m_ref in log2 units (already scaled); l_sum of this half
+    const uint32_t tmem_s = tmem_base + x * KEYS + lane_base;
+    const uint32_t tmem_o = tmem_base + 256 + x * D + lane_base;
+    const int num_tiles = mine.end - mine.begin;
+    float m_ref = -INFINITY, l_sum = 0.f;  // m_ref in log2 units (already scaled)
     TIMING_BEGIN();
-    for (int j = 0; j < num_tiles; ++j) {
-      const int s = j & 1;
+    for (int t = 0; t < num_tiles; ++t) {
+      const int key0 = (mine.begin + t) * KEYS;
       TICK(0);
-      const int key0 = (tile_begin + j) * KEYS + half * HALF;  // first key of this thread's half
-      mbar_wait(&s_full[s], (j >> 1) & 1, abort_flag, &g_error_word, 7);
+      mbar_wait(&s_full[x], t & 1, abort_flag, &g_error_word, 7);
       TICK(1);
       fence_after_sync();
-      const uint32_t s_addr = tmem_base + s * KEYS + half * HALF + lane_base;
-      // A half tile whose keys are all visible to every row of this warp needs no masking
-      const bool visible = key0 + HALF - 1 <= pos && key0 >= lo;
-      const bool warp_visible = __all_sync(0xffffffffu, visible);
-      // pass 1: the row's maximum over the keys of this half (in raw score units)
-      float m_a = -INFINITY, m_b = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < HALF; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32(s_addr + c, v);
-        tmem_ld_wait();
-        if (warp_visible) {
+      uint32_t v[KEYS];  // the row of S, in registers
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            m_a = fmaxf(m_a, __uint_as_float(v[i]));
-            m_b = fmaxf(m_b, __uint_as_float(v[i + 1]));
-          }
-        } else {
+      for (int c = 0; c < KEYS; c += 32) tmem_ld_32(tmem_s + c, reinterpret_cast<uint32_t(&)[32]>(v[c]));
+      tmem_ld_wait();
+      // A tile whose keys are all visible to every row of this warp needs no masking; rows beyond
+      // the tile's last (zero queries, never stored) take whatever comes
+      const bool visible = !row_valid || (key0 + KEYS - 1 <= pos && key0 >= lo);
+      if (!__all_sync(0xffffffffu, visible)) {
+        const int first_rel = lo - key0;
+        const unsigned span = row_valid ? (unsigned)(pos - lo) : 0x7fffffffu;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            const int key = key0 + c + i;
-            if (key <= pos && key >= lo) m_a = fmaxf(m_a, __uint_as_float(v[i]));
-          }
+        for (int i = 0; i < KEYS; ++i) {
+          // key0 + i outside [lo, pos], as one unsigned comparison
+          if ((unsigned)(i - first_rel) > span) v[i] = __float_as_uint(-INFINITY);
         }
       }
+      float m_a = -INFINITY, m_b = -INFINITY, m_c = -INFINITY, m_d = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < KEYS; i += 4) {
+        m_a = fmaxf(m_a, __uint_as_float(v[i]));
+        m_b = fmaxf(m_b, __uint_as_float(v[i + 1]));
+        m_c = fmaxf(m_c, __uint_as_float(v[i + 2]));
+        m_d = fmaxf(m_d, __uint_as_float(v[i + 3]));
+      }
+      const float m_tile = fmaxf(fmaxf(m_a, m_b), fmaxf(m_c, m_d)) * p.scale_log2;  // the scale is positive
       TICK(2);
-      // Both halves join their maxima in the tile's slot; the slot of the tile after next was last
-      // read before the previous barrier and is written again only after the next one.
-      atomicMax(&exchange[(j % 3) * ROWS + r], ordered_code(fmaxf(m_a, m_b)));
-      asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight softmax warps
-      const float m_tile = ordered_value(exchange[(j % 3) * ROWS + r]) * p.scale_log2;  // the scale is positive
-      if (half == 0) exchange[((j + 2) % 3) * ROWS + r] = 0u;
       // the reference max moves only when the row's max has grown past the threshold
       float factor = 1.f;
       bool rescale = false;
@@ -349,109 +369,73 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         m_ref = m_tile;
       }
       l_sum *= factor;
-      TICK(3);
-      // this tile's P buffer is free once P V of the tile before last is done
-      mbar_wait(&p_empty[s], ((j >> 1) & 1) ^ 1, abort_flag, &g_error_word, 8);
-      TICK(4);
       if (__any_sync(0xffffffffu, rescale)) {
-        // O may only be touched when no P V is in flight: wait for the previous tile's
-        mbar_wait(&p_empty[(j - 1) & 1], ((j - 1) >> 1) & 1, abort_flag, &g_error_word, 10);
-        fence_after_sync();
+        // O_x is at rest: the arrival of S_x covered the P_x V issued before it
 #pragma unroll 1
-        for (int c = 0; c < D / 2; c += 32) {  // this thread's half of the output columns
-          uint32_t v[32];
-          tmem_ld_32(tmem_o + lane_base + half * (D / 2) + c, v);
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32(tmem_o + c, o);
           tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * factor);
-          tmem_st_32(tmem_o + lane_base + half * (D / 2) + c, v);
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * factor);
+          tmem_st_32(tmem_o + c, o);
         }
-        tmem_st_wait();
       }
-      TICK(5);
-      // pass 2: P = exp2(S * scale - m_ref), row sum, P as bfloat16 into shared memory
+      TICK(3);
+      // P = exp2(S * scale - m_ref) as bfloat16 pairs over the first half of S's columns; row sum
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum_a = 0.f, sum_b = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < HALF; c += 32) {
-        uint32_t v[32];
-        tmem_ld_32(s_addr + c, v);
-        tmem_ld_wait();
-        uint32_t packed[16];
-        if (warp_visible) {
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const float a = fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, neg_m));
-            const float b = fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, neg_m));
-            sum_a += a;
-            sum_b += b;
-            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-          }
-        } else {
+      for (int c = 0; c < KEYS; c += 64) {
+        uint32_t packed[32];
 #pragma unroll
-          for (int i = 0; i < 32; i += 2) {
-            const int key = key0 + c + i;
-            const float a = (key <= pos && key >= lo) ? fast_exp2(fmaf(__uint_as_float(v[i]), p.scale_log2, neg_m)) : 0.f;
-            const float b = (key + 1 <= pos && key + 1 >= lo)
-                                ? fast_exp2(fmaf(__uint_as_float(v[i + 1]), p.scale_log2, neg_m)) : 0.f;
-            sum_a += a;
-            sum_b += b;
-            __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-          }
+        for (int i = 0; i < 64; i += 2) {
+          const float a = fast_exp2(fmaf(__uint_as_float(v[c + i]), p.scale_log2, neg_m));
+          const float b = fast_exp2(fmaf(__uint_as_float(v[c + i + 1]), p.scale_log2, neg_m));
+          sum_a += a;
+          sum_b += b;
+          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
         }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4) {  // four 16-byte chunks of 8 keys; a half is one slab
-          const int c8 = (c >> 3) + q4;
-          uint8_t* dst = p_tiles + s * TILE_BYTES + half * SLAB + r * 128 + (((c8 & 7) ^ (r & 7)) << 4);
-          *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-        }
+        tmem_st_32(tmem_s + (c >> 1), packed);
       }
       l_sum += sum_a + sum_b;
-      TICK(6);
-      fence_proxy_async();   // P is read by the tensor core
-      fence_before_sync();   // our tcgen05.ld/st of S and O are done
+      tmem_st_wait();
+      TICK(4);
+      fence_before_sync();  // our tcgen05.ld/st of S, P and O are done
       __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(&s_empty[s]);
-        mbar_arrive(&p_full[s]);
+      if (lane == 0) mbar_arrive(&p_full[x]);
+      TICK(5);
+    }
+    // ---- output: O / l
+    if (num_tiles > 0) {
+      mbar_wait(&o_done[x], 0, abort_flag, &g_error_word, 9);
+      TICK(6);
+      fence_after_sync();
+      const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
+      __nv_bfloat16* dst = nullptr;
+      if (row_valid) dst = p.out + (size_t)(tok0 + row / g) * p.out_stride + (size_t)(kvh * g + row % g) * D;
+#pragma unroll 1
+      for (int c = 0; c < D; c += 32) {
+        uint32_t o[32];
+        tmem_ld_32(tmem_o + c, o);
+        tmem_ld_wait();
+        if (row_valid) {
+          uint32_t packed[16];
+#pragma unroll
+          for (int i = 0; i < 32; i += 2) {
+            __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(o[i]) * inv, __uint_as_float(o[i + 1]) * inv);
+            packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
+#pragma unroll
+          for (int q4 = 0; q4 < 4; ++q4)
+            *reinterpret_cast<uint4*>(dst + c + 8 * q4) =
+                make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
+        }
       }
       TICK(7);
     }
-    if (warp == 0) TIMING_END(16);
-    if (warp == 4) TIMING_END(24);
-    // ---- output: O / l (the two halves add their sums)
-    float* sums = reinterpret_cast<float*>(exchange);
-    asm volatile("bar.sync 1, 256;" ::: "memory");  // the last tile's maxima have been read
-    sums[half * ROWS + r] = l_sum;
-    asm volatile("bar.sync 1, 256;" ::: "memory");
-    const float l_all = sums[r] + sums[ROWS + r];
-    if (num_tiles > 0)
-      mbar_wait(&p_empty[(num_tiles - 1) & 1], ((num_tiles - 1) >> 1) & 1, abort_flag, &g_error_word, 9);
-    fence_after_sync();
-    const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-    __nv_bfloat16* dst = nullptr;
-    if (row_valid)
-      dst = p.out + (size_t)(tok0 + row / g) * p.out_stride + (size_t)(kvh * g + row % g) * D + half * (D / 2);
-#pragma unroll 1
-    for (int c = 0; c < D / 2; c += 32) {
-      uint32_t v[32];
-      tmem_ld_32(tmem_o + lane_base + half * (D / 2) + c, v);
-      tmem_ld_wait();
-      if (row_valid && num_tiles > 0) {
-        uint32_t packed[16];
-#pragma unroll
-        for (int i = 0; i < 32; i += 2) {
-          __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(v[i]) * inv, __uint_as_float(v[i + 1]) * inv);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-        }
-#pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
-          *reinterpret_cast<uint4*>(dst + c + 8 * q4) =
-              make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
-      }
-    }
+    if (quarter == 0) TIMING_END(16 + 8 * x);
   }
   __syncwarp();
   fence_before_sync();
@@ -496,6 +480,7 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_
 extern "C" {
 
 #ifdef ATTN_TIMING
+int tl_attention_tc_trace(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 5 * 256); }
 int tl_attention_tc_timing(unsigned long long* out) {  // reads and clears the 32 counters
   unsigned long long zero[32] = {};
   if (cudaMemcpyFromSymbol(out, g_timing, sizeof(zero)) != cudaSuccess) return -1;
@@ -510,11 +495,11 @@ int tl_attention_tc_error() {
   return value;
 }
 
-// Packed rows a tile holds for a group of ``group`` query heads (whole tokens only).
-int tl_attention_tc_rows(int group) { return group > 0 && group <= ROWS ? (ROWS / group) * group : 0; }
+// Packed rows a CTA takes for a group of ``group`` query heads: two row tiles of whole tokens.
+int tl_attention_tc_rows(int group) { return group > 0 && group <= ROWS ? QTILES * (ROWS / group) * group : 0; }
 
 // pages: one cache layer [num_pages][2][nkv][page_size][128] bf16.  tile_req / tile_row:
-// request and first packed row (a multiple of tl_attention_tc_rows(nh / nkv)) of each tile.
+// request and first packed row (a multiple of tl_attention_tc_rows(nh / nkv)) of each CTA.
 int tl_attention_tc(const void* q, long long q_stride, const void* pages, long long num_pages,
                     const int* block_table, int table_width, const int* req_indptr, const int* kv_before,
                     const int* tile_req, const int* tile_row, int tiles, void* out, long long out_stride, int nh,
@@ -541,9 +526,9 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.nkv = nkv;
   p.page_size = page_size;
   p.window = window;
-  p.rows_per_tile = tl_attention_tc_rows(nh / nkv);
+  p.rows_per_tile = tl_attention_tc_rows(nh / nkv) / QTILES;
   p.scale_log2 = scale * 1.4426950408889634f;
-  constexpr int SMEM = 7 * TILE_BYTES + 1024 + 256 + 3 * ROWS * 4;
+  constexpr int SMEM = 6 * TILE_BYTES + 1024 + 256;
   static_assert(SMEM <= 232448, "shared memory of one CTA");
   static bool configured = false;
   if (!configured) {
