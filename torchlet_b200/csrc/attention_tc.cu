@@ -6,10 +6,10 @@
 // tile that is loaded serves all query heads of the group and both row tiles.  It walks
 // over the keys in tiles of 128 absolute positions:
 //
-//   loader warp     TMA-loads the tile's pages of K and V (one box of page_size x 64
+//   loader warps    one for K, one for V: TMA-load the tile's pages (one box of page_size x 64
 //                   elements per page and half of the head, 128-byte swizzle, one lane per
 //                   box) through the block table into a two-stage ring;
-//   MMA thread      for each row tile X in turn:  O_X += P_X V of the previous key tile
+//   MMA warp        for each row tile X in turn:  O_X += P_X V of the previous key tile
 //                   (P_X read from tensor memory, V as the MN-major operand from shared
 //                   memory), then S_X = Q_X K^T of this key tile (Q and K K-major in shared
 //                   memory).  S_X, P_X (in the first half of S_X's columns) and O_X live
@@ -49,20 +49,19 @@ constexpr int D = 128;          // head_dim
 constexpr int ROWS = 128;       // packed rows of a row tile (UMMA M)
 constexpr int QTILES = 2;       // row tiles a CTA
 constexpr int KEYS = 128;       // keys a tile (UMMA N of S, K of P V)
-constexpr int THREADS = 320;    // warps 0-3 softmax of row tile 0, 4-7 of row tile 1, 8 MMA, 9 loader
+constexpr int THREADS = 352;    // warps 0-3 softmax of row tile 0, 4-7 of row tile 1, 8 MMA, 9 and 10 loaders
 constexpr int SLAB = ROWS * 128;  // bytes of a [128 rows][64 bf16] swizzled slab
 constexpr int TILE_BYTES = 2 * SLAB;  // a 128 x 128 bf16 operand tile = two slabs
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 __device__ int g_error_word = 0;
 
+// Built with -DATTN_TIMING every role adds up the cycles it spends between its TICK marks (eight
+// slots a role: loader K, MMA, softmax of row tile 0 and 1); tl_attention_tc_timing() reads the sums.
 #ifdef ATTN_TIMING
 __device__ unsigned long long g_timing[32];
-__device__ long long g_trace[5][256];  // MMA thread, warps 0-3, (others)
-#define TIMING_BEGIN() long long t_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64(); int t_count = 0; \
-    const int t_role = warp == 8 ? 0 : warp < 4 ? warp + 1 : 4;
-#define TICK(slot) { const long long t_now = clock64(); t_acc[slot] += t_now - t_last; t_last = t_now; \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && t_count < 256 && (warp == 8 || warp < 4)) { g_trace[t_role][t_count] = (t_now << 4) | (slot); ++t_count; } }
+#define TIMING_BEGIN() long long t_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64();
+#define TICK(slot) { const long long t_now = clock64(); t_acc[slot] += t_now - t_last; t_last = t_now; }
 #define TIMING_END(base) if (lane == 0) { for (int t_i = 0; t_i < 8; ++t_i) atomicAdd(&g_timing[(base) + t_i], (unsigned long long)t_acc[t_i]); }
 #else
 #define TIMING_BEGIN()
@@ -94,6 +93,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
@@ -137,6 +141,27 @@ __device__ __forceinline__ void tmem_st_32(uint32_t taddr, const uint32_t (&r)[3
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// P = exp2(S * scale - m) of one row as bfloat16 pairs into tensor memory at ``tmem_p`` (64
+// columns).  The row's sum of the unrounded P goes to sum_a + sum_b.
+__device__ __forceinline__ void exp_and_store(const uint32_t (&v)[KEYS], float scale_log2, float neg_m, uint32_t tmem_p,
+                                              float& sum_a, float& sum_b) {
+#pragma unroll
+  for (int c = 0; c < KEYS; c += 64) {
+    uint32_t packed[32];
+#pragma unroll
+    for (int i = 0; i < 64; i += 2) {
+      const float xa = fmaf(__uint_as_float(v[c + i]), scale_log2, neg_m);
+      const float xb = fmaf(__uint_as_float(v[c + i + 1]), scale_log2, neg_m);
+      const float a = fast_exp2(xa), b = fast_exp2(xb);
+      sum_a += a;
+      sum_b += b;
+      __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+      packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    tmem_st_32(tmem_p + (c >> 1), packed);
+  }
+}
+
 // Key tiles [begin, end) that row tile X of the CTA needs; rows [row_start, row_end).
 struct RowTile {
   int row_start, row_end, begin, end;
@@ -157,7 +182,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   uint64_t* s_full = bars + 8;    // [2 row tiles]  S_X of the next key tile is in tensor memory
   uint64_t* p_full = bars + 10;   // [2 row tiles]  (4 arrivals: one per softmax warp) P_X is written
   uint64_t* o_done = bars + 12;   // [2 row tiles]  the last P_X V is done
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -224,11 +249,16 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   fence_after_sync();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 9) {
-    // ------------------------------------------------------------------ loader
-    // Lane l copies half (l & 1) of page (l >> 1) of every tile: a box of page_size keys x 64
-    // elements (page_size >= 8, so a tile has at most 16 pages).  Thirty-two copies issued
-    // by one thread take longer than the tile's arithmetic.
+  if (warp >= 9) {
+    // ----------------------------------------------------------------- loaders
+    // Warp 9 copies K, warp 10 copies V.  Lane l copies half (l & 1) of page (l >> 1) of every
+    // tile: a box of page_size keys x 64 elements (page_size >= 8, so a tile has at most 16
+    // pages).  The copies of a tile cost their issue, not their bytes: thirty-two issued by
+    // one thread take longer than the tile's arithmetic.
+    const int is_v = warp - 9;
+    uint8_t* tiles = is_v ? v_tiles : k_tiles;
+    uint64_t* full = is_v ? v_full : k_full;
+    uint64_t* empty = is_v ? v_empty : k_empty;
     const int pages_per_tile = KEYS / p.page_size;
     const int my_page = lane >> 1, my_half = lane & 1;
     const bool active = my_page < pages_per_tile;
@@ -240,79 +270,83 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       const int page = (active && index < p.table_width) ? table[index] : 0;  // beyond the table: page 0
       const uint32_t offset = s * TILE_BYTES + my_half * SLAB + my_page * p.page_size * 128;
       TICK(0);
-      mbar_wait(&k_empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
+      mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1 + is_v);
       TICK(1);
-      if (lane == 0) mbar_expect_tx(&k_full[s], TILE_BYTES);
+      if (lane == 0) mbar_expect_tx(&full[s], TILE_BYTES);
       __syncwarp();
       if (active)
-        tma_load_2d(k_tiles + offset, &map_kv, &k_full[s], my_half * 64, ((page * 2 + 0) * p.nkv + kvh) * p.page_size);
+        tma_load_2d(tiles + offset, &map_kv, &full[s], my_half * 64, ((page * 2 + is_v) * p.nkv + kvh) * p.page_size);
       TICK(2);
-      mbar_wait(&v_empty[s], phase ^ 1, abort_flag, &g_error_word, 2);
-      TICK(3);
-      if (lane == 0) mbar_expect_tx(&v_full[s], TILE_BYTES);
-      __syncwarp();
-      if (active)
-        tma_load_2d(v_tiles + offset, &map_kv, &v_full[s], my_half * 64, ((page * 2 + 1) * p.nkv + kvh) * p.page_size);
-      TICK(4);
     }
-    TIMING_END(0);
+    if (is_v == 0) TIMING_END(0);
   } else if (warp == 8) {
     // --------------------------------------------------------------------- MMA
-    if (lane == 0) {
-      const uint32_t idesc_s = idesc_bf16_f32(ROWS, KEYS);
-      const uint32_t idesc_o = idesc_pv();
-      // Descriptors of the operands' first 16-wide slices; a later slice adds its byte offset / 16
-      // to the address field (the tiles lie below 256 KB, so the field never carries).
-      const uint64_t q_desc[QTILES] = {smem_desc_sw128(smem_addr(q_tiles)), smem_desc_sw128(smem_addr(q_tiles + TILE_BYTES))};
-      const uint64_t k_desc[2] = {smem_desc_sw128(smem_addr(k_tiles)), smem_desc_sw128(smem_addr(k_tiles + TILE_BYTES))};
-      const uint64_t v_desc[2] = {smem_desc_v(smem_addr(v_tiles)), smem_desc_v(smem_addr(v_tiles + TILE_BYTES))};
-      TIMING_BEGIN();
-      // One step past the last key tile, for the P V that runs a tile behind
-      for (int j = j_begin; j <= j_end; ++j) {
-        const int jj = j - j_begin;
-        bool k_ready = false, v_ready = false;
+    // The whole warp walks the loop and waits; one elected lane issues (with the loop inside a
+    // one-lane branch the operands of every MMA went through per-lane registers, and issuing
+    // took longer than the MMAs run).  The tensor core's queue is short, and every wait, fence
+    // and election costs the warp tens of nanoseconds in which it issues nothing, while eight
+    // of these MMAs run for 280 ns: so a row tile's P V and next S go out together, behind one
+    // wait for its P.  The tiles take turns, which keeps one in its softmax while the other's
+    // MMAs run.
+    const uint32_t idesc_s = idesc_bf16_f32(ROWS, KEYS);
+    const uint32_t idesc_o = idesc_pv();
+    // Descriptors of the operands' first 16-wide slices; a later slice adds its byte offset / 16
+    // to the address field (the tiles lie below 256 KB, so the field never carries).
+    const uint64_t q_desc[QTILES] = {smem_desc_sw128(smem_addr(q_tiles)), smem_desc_sw128(smem_addr(q_tiles + TILE_BYTES))};
+    const uint64_t k_desc[2] = {smem_desc_sw128(smem_addr(k_tiles)), smem_desc_sw128(smem_addr(k_tiles + TILE_BYTES))};
+    const uint64_t v_desc[2] = {smem_desc_v(smem_addr(v_tiles)), smem_desc_v(smem_addr(v_tiles + TILE_BYTES))};
+    TIMING_BEGIN();
+    // One step past the last key tile, for the P V that runs a tile behind
+    for (int j = j_begin; j <= j_end; ++j) {
+      const int jj = j - j_begin;
+      TICK(0);
+      // V of the previous key tile has long arrived, K of this one nearly always
+      if (jj > 0) mbar_wait(&v_full[(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort_flag, &g_error_word, 6);
+      TICK(1);
+      if (j < j_end) mbar_wait(&k_full[jj & 1], (jj >> 1) & 1, abort_flag, &g_error_word, 3);
+      TICK(2);
+      // the last row tile with work at this step (row tile 0 always has some)
+      const bool work_1 = (j - 1 >= tile[1].begin && j - 1 < tile[1].end) || (j >= tile[1].begin && j < tile[1].end);
 #pragma unroll
-        for (int x = 0; x < QTILES; ++x) {
-          const uint32_t tmem_s = tmem_base + x * KEYS;         // S_x, and P_x in its first 64 columns
-          const uint32_t tmem_o = tmem_base + 256 + x * D;      // O_x
-          if (j - 1 >= tile[x].begin && j - 1 < tile[x].end) {  // O_x (+)= P_x V of key tile j - 1
-            const int t = j - 1 - tile[x].begin;
-            TICK(0);
-            mbar_wait(&p_full[x], t & 1, abort_flag, &g_error_word, 5);
-            TICK(1 + x);
-            if (!v_ready) mbar_wait(&v_full[(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort_flag, &g_error_word, 6);
-            v_ready = true;
-            TICK(3);
-            fence_after_sync();
+      for (int x = 0; x < QTILES; ++x) {
+        const uint32_t tmem_s = tmem_base + x * KEYS;     // S_x, and P_x in its first 64 columns
+        const uint32_t tmem_o = tmem_base + 256 + x * D;  // O_x
+        const bool do_pv = j - 1 >= tile[x].begin && j - 1 < tile[x].end;  // O_x (+)= P_x V of key tile j - 1
+        const bool do_s = j >= tile[x].begin && j < tile[x].end;           // S_x = Q_x K^T of key tile j
+        if (!do_pv && !do_s) continue;
+        const int t = j - 1 - tile[x].begin;
+        if (do_pv) mbar_wait(&p_full[x], t & 1, abort_flag, &g_error_word, 5);
+        TICK(3);
+        fence_after_sync();
+        if (elect_one()) {
+          if (do_pv) {
             const uint64_t b_desc = ((jj - 1) & 1) ? v_desc[1] : v_desc[0];
 #pragma unroll
             for (int k = 0; k < KEYS / 16; ++k)  // 16 keys: 8 columns of P, two 8-key atoms of V (2048 bytes)
               mma_bf16_a_tmem(tmem_o, tmem_s + k * 8, b_desc + (uint64_t)(k * (2048 >> 4)), idesc_o, t > 0 || k > 0);
             if (j == tile[x].end) mma_commit(&o_done[x]);
-            TICK(4);
           }
-          if (j >= tile[x].begin && j < tile[x].end) {  // S_x = Q_x K^T of key tile j
-            TICK(0);
-            if (!k_ready) mbar_wait(&k_full[jj & 1], (jj >> 1) & 1, abort_flag, &g_error_word, 3);
-            k_ready = true;
-            TICK(5);
-            fence_after_sync();
-            const uint64_t a_desc = q_desc[x];
+          if (do_s) {
             const uint64_t b_desc = (jj & 1) ? k_desc[1] : k_desc[0];
 #pragma unroll
             for (int k = 0; k < D / 16; ++k) {  // slab k / 4, 32 bytes a slice within its 128-byte rows
               const uint64_t offset = (uint64_t)(((k >> 2) * SLAB + (k & 3) * 32) >> 4);
-              mma_bf16(tmem_s, a_desc + offset, b_desc + offset, idesc_s, k > 0);
+              mma_bf16(tmem_s, q_desc[x] + offset, b_desc + offset, idesc_s, k > 0);
             }
             mma_commit(&s_full[x]);
-            TICK(6);
+          }
+          // The warp's MMAs are all issued by the lane that elect.sync names, the same every
+          // time, so its commits cover them
+          if (x == 1 || !work_1) {
+            if (j < j_end) mma_commit(&k_empty[jj & 1]);
+            if (jj > 0) mma_commit(&v_empty[(jj - 1) & 1]);
           }
         }
-        if (j < j_end) mma_commit(&k_empty[jj & 1]);
-        if (jj > 0) mma_commit(&v_empty[(jj - 1) & 1]);
+        __syncwarp();
+        TICK(4);
       }
-      TIMING_END(8);
     }
+    TIMING_END(8);
   } else {
     // ----------------------------------------------------------------- softmax
     const int x = warp >> 2, quarter = warp & 3;
@@ -341,7 +375,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       // A tile whose keys are all visible to every row of this warp needs no masking; rows beyond
       // the tile's last (zero queries, never stored) take whatever comes
       const bool visible = !row_valid || (key0 + KEYS - 1 <= pos && key0 >= lo);
-      if (!__all_sync(0xffffffffu, visible)) {
+      const bool all_visible = __all_sync(0xffffffffu, visible);
+      if (!all_visible) {
         const int first_rel = lo - key0;
         const unsigned span = row_valid ? (unsigned)(pos - lo) : 0x7fffffffu;
 #pragma unroll
@@ -352,11 +387,11 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       }
       float m_a = -INFINITY, m_b = -INFINITY, m_c = -INFINITY, m_d = -INFINITY;
 #pragma unroll
-      for (int i = 0; i < KEYS; i += 4) {
-        m_a = fmaxf(m_a, __uint_as_float(v[i]));
-        m_b = fmaxf(m_b, __uint_as_float(v[i + 1]));
-        m_c = fmaxf(m_c, __uint_as_float(v[i + 2]));
-        m_d = fmaxf(m_d, __uint_as_float(v[i + 3]));
+      for (int i = 0; i < KEYS; i += 8) {
+        m_a = max3(m_a, __uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+        m_b = max3(m_b, __uint_as_float(v[i + 2]), __uint_as_float(v[i + 3]));
+        m_c = max3(m_c, __uint_as_float(v[i + 4]), __uint_as_float(v[i + 5]));
+        m_d = max3(m_d, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
       }
       const float m_tile = fmaxf(fmaxf(m_a, m_b), fmaxf(m_c, m_d)) * p.scale_log2;  // the scale is positive
       TICK(2);
@@ -364,7 +399,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       float factor = 1.f;
       bool rescale = false;
       if (m_tile > m_ref + RESCALE_THRESHOLD || (m_ref == -INFINITY && m_tile > -INFINITY)) {
-        factor = m_ref == -INFINITY ? 0.f : exp2f(m_ref - m_tile);
+        factor = m_ref == -INFINITY ? 0.f : fast_exp2(m_ref - m_tile);
         rescale = m_ref != -INFINITY;
         m_ref = m_tile;
       }
@@ -385,20 +420,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       // P = exp2(S * scale - m_ref) as bfloat16 pairs over the first half of S's columns; row sum
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum_a = 0.f, sum_b = 0.f;
-#pragma unroll
-      for (int c = 0; c < KEYS; c += 64) {
-        uint32_t packed[32];
-#pragma unroll
-        for (int i = 0; i < 64; i += 2) {
-          const float a = fast_exp2(fmaf(__uint_as_float(v[c + i]), p.scale_log2, neg_m));
-          const float b = fast_exp2(fmaf(__uint_as_float(v[c + i + 1]), p.scale_log2, neg_m));
-          sum_a += a;
-          sum_b += b;
-          __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
-          packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        tmem_st_32(tmem_s + (c >> 1), packed);
-      }
+      exp_and_store(v, p.scale_log2, neg_m, tmem_s, sum_a, sum_b);
       l_sum += sum_a + sum_b;
       tmem_st_wait();
       TICK(4);
@@ -480,7 +502,6 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_
 extern "C" {
 
 #ifdef ATTN_TIMING
-int tl_attention_tc_trace(long long* out) { return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 5 * 256); }
 int tl_attention_tc_timing(unsigned long long* out) {  // reads and clears the 32 counters
   unsigned long long zero[32] = {};
   if (cudaMemcpyFromSymbol(out, g_timing, sizeof(zero)) != cudaSuccess) return -1;
