@@ -334,42 +334,57 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
   const int num_kb = p.k_blocks;
   if (warp == 0) {
     if (lane == 0) {
-      int it = 0;
+      int s = 0;
+      uint32_t phase = 0;
       for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x) {
         const int row0 = (tile % p.row_tiles) * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t phase = (it / p.stages) & 1;
+        for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
           mbar_expect_tx(&full[s], stage_bytes);
           uint8_t* stage = smem + s * stage_bytes;
           tma_load_2d(stage, &map_row, &full[s], kb * BLOCK_K, row0);
           tma_load_2d(stage + ROW_TILE_BYTES, &map_col, &full[s], kb * BLOCK_K, col0);
+          if (++s == p.stages) {
+            s = 0;
+            phase ^= 1;
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = idesc_bf16_f32(BLOCK_P, p.block_q);
-      int it = 0, local = 0;
-      for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local) {
-        const int a = local & 1;
-        mbar_wait(&tmem_empty[a], ((local >> 1) & 1) ^ 1, abort_flag, &g_error_word, 4);
+    // The whole warp walks the loop and waits; one elected lane issues.  (Inside a one-lane
+    // branch the operands of every MMA go through per-lane registers, which makes the issue
+    // slower; the tensor core's queue is short, so what this warp spends between two MMAs
+    // shows.)
+    const uint32_t idesc = idesc_bf16_f32(BLOCK_P, p.block_q);
+    const uint64_t a_desc0 = smem_desc_sw128(smem_addr(smem));
+    const uint64_t b_desc0 = smem_desc_sw128(smem_addr(smem + ROW_TILE_BYTES));
+    const uint64_t stage_step = (uint64_t)(stage_bytes >> 4);  // in the descriptors' address field
+    int s = 0, local = 0;
+    uint32_t phase = 0;
+    uint64_t a_desc = a_desc0, b_desc = b_desc0;
+    for (int tile = blockIdx.x; tile < p.num_tiles; tile += gridDim.x, ++local) {
+      const int a = local & 1;
+      mbar_wait(&tmem_empty[a], ((local >> 1) & 1) ^ 1, abort_flag, &g_error_word, 4);
+      const uint32_t acc = tmem_base + a * ACC_COLS;
+      for (int kb = 0; kb < num_kb; ++kb) {
+        mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
         fence_after_sync();
-        const uint32_t acc = tmem_base + a * ACC_COLS;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t phase = (it / p.stages) & 1;
-          mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
-          fence_after_sync();
-          const uint32_t a_addr = smem_addr(smem + s * stage_bytes);
-          const uint64_t a_desc = smem_desc_sw128(a_addr);
-          const uint64_t b_desc = smem_desc_sw128(a_addr + ROW_TILE_BYTES);
+        if (elect_one()) {
 #pragma unroll
           for (int k = 0; k < BLOCK_K / UMMA_K; ++k) mma_bf16(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
           mma_commit(&empty[s]);
+          if (kb == num_kb - 1) mma_commit(&tmem_full[a]);
         }
-        mma_commit(&tmem_full[a]);
+        __syncwarp();
+        a_desc += stage_step;
+        b_desc += stage_step;
+        if (++s == p.stages) {
+          s = 0;
+          phase ^= 1;
+          a_desc = a_desc0;
+          b_desc = b_desc0;
+        }
       }
     }
   } else {
