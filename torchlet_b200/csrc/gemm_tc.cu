@@ -194,24 +194,33 @@ gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid
     }
   } else if (warp == 1) {
     tl::pdl_wait();
-    if (lane == 0) {
-      for (int it = 0; it < num_kb; ++it) {
-        const int s = it % STAGES;
-        const uint32_t phase = (it / STAGES) & 1;
-        mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
-        fence_after_sync();
-        const uint32_t a_addr = smem_addr(smem + s * STAGE_BYTES);
-        const uint64_t a_desc = smem_desc_sw128(a_addr);
-        const uint64_t b_desc = smem_desc_sw128(a_addr + ROW_TILE_BYTES);
+    // The whole warp walks the loop and waits; one elected lane issues (see the persistent kernel)
+    const uint64_t a_desc0 = smem_desc_sw128(smem_addr(smem));
+    const uint64_t b_desc0 = smem_desc_sw128(smem_addr(smem + ROW_TILE_BYTES));
+    int s = 0;
+    uint32_t phase = 0;
+    for (int it = 0; it < num_kb; ++it) {
+      mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
+      fence_after_sync();
+      const uint64_t a_desc = a_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+      const uint64_t b_desc = b_desc0 + (uint64_t)(s * (STAGE_BYTES >> 4));
+      if (elect_one()) {
 #pragma unroll
         for (int k = 0; k < BLOCK_K / UMMA_K; ++k) {
           // 16 bf16 = 32 bytes further along K inside the swizzled row: +2 in 16-byte units
           mma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, IDESC, it > 0 || k > 0);
         }
         mma_commit(&empty[s]);
+        if (it == num_kb - 1) mma_commit(tmem_full);
       }
-      mma_commit(tmem_full);
+      __syncwarp();
+      if (++s == STAGES) {
+        s = 0;
+        phase ^= 1;
+      }
     }
+    if (num_kb == 0 && elect_one()) mma_commit(tmem_full);
+    __syncwarp();
   } else {
     tl::pdl_wait();  // the epilogue writes buffers that earlier kernels may still read
     mbar_wait(tmem_full, 0, abort_flag, &g_error_word, 3);
