@@ -80,6 +80,28 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, c
     dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
     return;
   }
+  if (p.epilogue == EPI_ACCUM_F32 && cols == 32 && n0 + 32 <= N) {
+    float* o = (float*)p.out + (size_t)m * p.ldo + n0;
+    if ((reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+      // all of the chunk's old values are requested before the first is used: one trip to
+      // memory a chunk instead of one for every eight columns
+      float4* o4 = reinterpret_cast<float4*>(o);
+      float4 old[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) old[j] = o4[j];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int n = n0 + 4 * j;
+        old[j].x += v[4 * j] + (p.bias ? p.bias[n] : 0.f);
+        old[j].y += v[4 * j + 1] + (p.bias ? p.bias[n + 1] : 0.f);
+        old[j].z += v[4 * j + 2] + (p.bias ? p.bias[n + 2] : 0.f);
+        old[j].w += v[4 * j + 3] + (p.bias ? p.bias[n + 3] : 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o4[j] = old[j];
+      return;
+    }
+  }
 #pragma unroll
   for (int c = 0; c < 32; c += 8) {
     const int n = n0 + c;
