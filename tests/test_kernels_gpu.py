@@ -133,9 +133,11 @@ def test_gemm_tc_refuses_what_it_cannot_do():
 
 
 # ----------------------------------------------------------------- attention
-def paged_inputs(lens_before, q_lens, nh, nkv, d, page, dtype, seed=0, num_pages=None, shuffle=True):
+def paged_inputs(lens_before, q_lens, nh, nkv, d, page, dtype, seed=0, num_pages=None, shuffle=True, spike=None):
     """Random q/k/v for requests with ``lens_before`` cached tokens and ``q_lens`` new ones;
-    returns the kernel's inputs and per-request dense (q, k, v) for the plain reference."""
+    returns the kernel's inputs and per-request dense (q, k, v) for the plain reference.
+    ``spike`` = (request, new token, key position): that key is set along the token's queries
+    (the first head of every group), so that one far score stands out."""
     g = torch.Generator().manual_seed(seed)
     n = len(q_lens)
     totals = [b + q for b, q in zip(lens_before, q_lens)]
@@ -154,6 +156,8 @@ def paged_inputs(lens_before, q_lens, nh, nkv, d, page, dtype, seed=0, num_pages
         k = torch.randn(total, nkv, d, generator=g).to(dtype)
         v = torch.randn(total, nkv, d, generator=g).to(dtype)
         q = torch.randn(q_len, nh, d, generator=g).to(dtype)
+        if spike is not None and spike[0] == i:
+            k[spike[2]] = 4 * q[spike[1], :: nh // nkv]
         count = -(-total // page)
         mine = order[cursor:cursor + count]
         cursor += count
@@ -423,14 +427,19 @@ def test_sampling_over_a_vocabulary_scanned_by_several_blocks():
     ([5, 1000], [333, 40], 8, 8, 32, None),
     ([64, 0], [200, 129], 4, 2, 8, 100),
     ([0], [130], 16, 1, 128, None),
+    ([0, 2500], [2, 3], 28, 4, 16, None),        # the second row tile of a CTA is empty
+    ([3000], [200], 14, 2, 16, 512),            # the row tiles start at different key tiles
+    ([4000], [300], 28, 4, 64, None, (0, 299, 7)),   # a far key that decides the last token
+    ([1100], [150], 12, 4, 16, 300, (0, 20, 830)),   # a key just inside the window of token 1120: 821 and later
 ])
 def test_attention_tc(case):
     """Prompt-portion attention on tcgen05 (head_dim 128) against the plain formula."""
     ops = _ops()
-    before, q_lens, nh, nkv, page, window = case
+    before, q_lens, nh, nkv, page, window = case[:6]
+    spike = case[6] if len(case) > 6 else None
     d, group = 128, nh // nkv
     assert ops.attention_tc_supported(d, group, page)
-    x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=5)
+    x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=5, spike=spike)
     scale = 0.37 / math.sqrt(d)
     want = plain_attention(x["dense"], before, nh, nkv, window, scale)
     rows = ops.attention_tc_rows(group)
@@ -447,3 +456,8 @@ def test_attention_tc(case):
     torch.cuda.synchronize()
     assert ops.attention_tc_error() == 0
     assert (out.float().cpu() - want).abs().max() <= 1.5e-2 * want.abs().max()
+    if spike is not None:  # the spiked head's output is that key's value, in the kernel as in the formula
+        token = sum(q_lens[:spike[0]]) + spike[1]
+        v_spike = x["dense"][spike[0]][2][spike[2], 0].float()
+        assert (want[token, :d] - v_spike).abs().max() < 0.05 * v_spike.abs().max()
+        assert (out[token, :d].float().cpu() - v_spike).abs().max() < 0.05 * v_spike.abs().max()

@@ -10,6 +10,7 @@ from __future__ import annotations
 
 from typing import Optional
 
+from .. import ops
 from ..config.engine import EngineConfig
 from ..logger import logger
 from ..parts.model import LayeredModel
@@ -51,6 +52,8 @@ class Engine:
             result = self.runner.run(entries)
             sampled = result.tokens.tolist() if result.tokens is not None else []
             done += scheduler.update(plan, sampled)
+            if done:  # nothing is handed back before the kernels' own error words have been read
+                ops.raise_on_wait_errors()
         scheduler.drain_finished()
         return done
 

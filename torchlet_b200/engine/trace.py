@@ -43,6 +43,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
 
     import numpy as np
 
+    from .. import ops
     from ..config import EngineConfig
     from .loading import load_model
     from .runner import ModelRunner, StepEntry
@@ -77,6 +78,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
         logits = runner.step(entries)
         if logits is not None:
             array = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
+            ops.raise_on_wait_errors()  # before anything of this step is written
             array.tofile(out_dir / f"{step}.f32")
         for request_id in record.get("end", []):
             if runner.cache.has(request_id):

@@ -360,3 +360,16 @@ def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_
 def attention_tc_error() -> int:
     """0, or the code a bounded wait in the tcgen05 attention kernel left when it gave up."""
     return _fn("attention_tc", "tl_attention_tc_error")()
+
+
+def raise_on_wait_errors() -> None:
+    """Raises if a bounded wait inside a tensor-core kernel has given up since the last call
+    (the kernel then ran to its end with whatever it had, so its output is not to be used).
+    Only libraries that are loaded are asked.  The read is a blocking copy on the default
+    stream, so it sees every kernel launched before it."""
+    for library, read in (("gemm_tc", gemm_tc_error), ("attention_tc", attention_tc_error)):
+        if any(name in _functions for name in _SIGNATURES[library]):
+            code = read()
+            if code:
+                raise KernelError(f"{library}: a bounded wait gave up inside a kernel (code {code}); "
+                                  "the results of this step are invalid")
