@@ -20,15 +20,29 @@ EPILOGUES = {"bf16": ops.EPI_STORE_BF16, "accum": ops.EPI_ACCUM_F32, "swiglu": o
              "f32": ops.EPI_STORE_F32}
 
 
+USE_GRAPH = False  # --graph: the timed launches are replayed from one CUDA graph (no host time between them)
+
+
 def _time(fn, iters: int, warmup: int) -> float:
     for i in range(warmup):
         fn(i)
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    begin.record()
-    for i in range(iters):
-        fn(warmup + i)
-    end.record()
+    if USE_GRAPH:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                fn(warmup + i)
+        graph.replay()
+        torch.cuda.synchronize()
+        begin.record()
+        graph.replay()
+        end.record()
+    else:
+        begin.record()
+        for i in range(iters):
+            fn(warmup + i)
+        end.record()
     torch.cuda.synchronize()
     return begin.elapsed_time(end) / iters
 
@@ -113,7 +127,11 @@ def main(argv=None) -> int:
     for p in (gemm, attention):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
+        p.add_argument("--graph", action="store_true",
+                       help="replay the timed launches from one CUDA graph (for kernels shorter than a launch costs the host)")
     args = parser.parse_args(argv)
+    global USE_GRAPH
+    USE_GRAPH = args.graph
     {"gemm": bench_gemm, "attention": bench_attention}[args.what](args)
     return 0
 
