@@ -676,7 +676,17 @@ int sm_count() {
   return count;
 }
 
-constexpr int SWAP_MAX_TOKENS = 256;
+// The swapped orientation is considered up to this many tokens (TORCHLET_B200_SWAP_MAX forces
+// another bound, for measurements).
+int swap_max_tokens() {
+  static int value = -1;
+  if (value < 0) {
+    const char* v = getenv("TORCHLET_B200_SWAP_MAX");
+    value = v ? atoi(v) : 256;
+    if (value < 0 || value > 256) value = 256;
+  }
+  return value;
+}
 
 int pick_block_q_swapped(int M) {
   if (M <= 16) return 16;
@@ -694,7 +704,17 @@ struct Plan {
 Plan make_plan(int M, int N, int K) {
   Plan plan;
   const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
-  plan.swap = M <= SWAP_MAX_TOKENS;
+  // Which orientation.  Up to 64 tokens the swapped kernel streams the weights at 5.5-6.2 TB/s.
+  // Beyond that its wide column tiles lose (4.7 TB/s at 128 columns, 2.5 at 256), and the
+  // persistent kernel takes over where it has a tile for every SM, or, past 128 tokens, where
+  // one CTA's pass over K (about 200 GB/s a CTA) is shorter than the swapped kernel's time.
+  plan.swap = M <= swap_max_tokens();
+  if (plan.swap && M > 64 && swap_max_tokens() == 256) {
+    const long long normal_tiles = (long long)((M + BLOCK_P - 1) / BLOCK_P) * ((N + 255) / 256);
+    const double pass_us = (double)K * (BLOCK_P + 256) * 2 / 200e3;
+    const double swapped_us = (double)N * K * 2 / 2.5e6 + 8.0;
+    if (normal_tiles >= sm_count() || (M > 128 && pass_us < swapped_us)) plan.swap = false;
+  }
   if (plan.swap) {
     plan.block_q = pick_block_q_swapped(M);
     const int tiles = ((N + BLOCK_P - 1) / BLOCK_P) * ((M + plan.block_q - 1) / plan.block_q);
