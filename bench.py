@@ -465,6 +465,9 @@ def main() -> int:
         record["prefill"] = {"value": round(2048 / (prefill_ms / 1e3), 1), "tokens": 2048, "ms": round(prefill_ms, 3),
                              "frac": round(flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4),
                              "tflops": round(flops / (prefill_ms / 1e3) / 1e12, 1), "peak_tflops": peaks["bf16_tflops"]}
+        if peaks.get("bf16_tflops_sustained"):  # the same against the seconds-long cuBLAS figure under the power cap
+            record["prefill"]["frac_of_sustained"] = round(
+                flops / (prefill_ms / 1e3) / 1e12 / peaks["bf16_tflops_sustained"], 4)
         points = {}
         for batch in (1, 64):
             run = time_decode(model, batch, args.context, min(args.steps, 64), args.warmup)

@@ -56,7 +56,8 @@ def bench_gemm(args) -> None:
     x = (torch.randn(M, K, device="cuda", generator=generator)).bfloat16()
     out_cols = N // 2 if args.epilogue == "swiglu" else N
     out = torch.zeros(M, out_cols, device="cuda", dtype=torch.bfloat16 if args.epilogue in ("bf16", "swiglu") else torch.float32)
-    ms = _time(lambda i: ops.gemm_tc(x, weights[i % copies], out, None, epilogue), args.iters, args.warmup)
+    ms = _time(lambda i: ops.gemm_tc(x, weights[i % copies], out, None, epilogue, cta_pairs={"auto": None, "on": True, "off": False}[args.pairs]), args.iters,
+               args.warmup)
     flops, weight_bytes = 2.0 * M * N * K, N * K * 2
     print(f"gemm M={M} N={N} K={K} epilogue={args.epilogue}: {ms * 1e3:.1f} us, {flops / ms / 1e9:.1f} TFLOP/s, "
           f"weights {weight_bytes / ms / 1e6:.0f} GB/s, wait-error {ops.gemm_tc_error()}")
@@ -114,6 +115,8 @@ def main(argv=None) -> int:
     gemm.add_argument("--n", type=int, default=37888)
     gemm.add_argument("--k", type=int, default=3584)
     gemm.add_argument("--epilogue", choices=sorted(EPILOGUES), default="swiglu")
+    gemm.add_argument("--pairs", choices=["auto", "on", "off"], default="auto",
+                      help="many tokens: the CTA-pair kernel (cta_group::2), the single-CTA kernel, or the library's choice")
     attention = sub.add_parser("attention")
     attention.add_argument("--batch", type=int, default=8)
     attention.add_argument("--context", type=int, default=4096)

@@ -522,45 +522,58 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
   const int num_kb = p.k_blocks;
   if (warp == 0) {
     if (lane == 0) {
-      int it = 0;
+      int s = 0;
+      uint32_t phase = 0;
       for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
         const int row0 = (tile % p.row_tiles) * 256 + (int)rank * BLOCK_P;
         const int col0 = (tile / p.row_tiles) * p.block_q + (int)rank * half_q;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t phase = (it / p.stages) & 1;
+        for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
           if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);  // the bytes of both CTAs
           const uint32_t bar = peer_addr(&full[s], 0);
           uint8_t* stage = smem + s * stage_bytes;
           tma_load_2d_pair(stage, &map_row, bar, kb * BLOCK_K, row0);
           tma_load_2d_pair(stage + ROW_TILE_BYTES, &map_col, bar, kb * BLOCK_K, col0);
+          if (++s == p.stages) {
+            s = 0;
+            phase ^= 1;
+          }
         }
       }
     }
   } else if (warp == 1) {
-    if (lane == 0 && rank == 0) {
+    if (rank == 0) {  // the whole warp walks the loop and waits; one elected lane issues
       const uint32_t idesc = idesc_bf16_f32(256, p.block_q);
-      int it = 0, local = 0;
+      const uint64_t a_desc0 = smem_desc_sw128(smem_addr(smem));
+      const uint64_t b_desc0 = smem_desc_sw128(smem_addr(smem + ROW_TILE_BYTES));
+      const uint64_t stage_step = (uint64_t)(stage_bytes >> 4);  // in the descriptors' address field
+      int s = 0, local = 0;
+      uint32_t phase = 0;
+      uint64_t a_desc = a_desc0, b_desc = b_desc0;
       for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++local) {
         const int a = local & 1;
         mbar_wait(&tmem_empty[a], ((local >> 1) & 1) ^ 1, abort_flag, &g_error_word, 4);
-        fence_after_sync();
         const uint32_t acc = tmem_base + a * ACC_COLS;
-        for (int kb = 0; kb < num_kb; ++kb, ++it) {
-          const int s = it % p.stages;
-          const uint32_t phase = (it / p.stages) & 1;
+        for (int kb = 0; kb < num_kb; ++kb) {
           mbar_wait(&full[s], phase, abort_flag, &g_error_word, 2);
           fence_after_sync();
-          const uint32_t a_addr = smem_addr(smem + s * stage_bytes);
-          const uint64_t a_desc = smem_desc_sw128(a_addr);
-          const uint64_t b_desc = smem_desc_sw128(a_addr + ROW_TILE_BYTES);
+          if (elect_one()) {
 #pragma unroll
-          for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
-            mma_bf16_pair(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
-          mma_commit_pair(&empty[s]);
+            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+              mma_bf16_pair(acc, a_desc + 2 * k, b_desc + 2 * k, idesc, kb > 0 || k > 0);
+            mma_commit_pair(&empty[s]);
+            if (kb == num_kb - 1) mma_commit_pair(&tmem_full[a]);
+          }
+          __syncwarp();
+          a_desc += stage_step;
+          b_desc += stage_step;
+          if (++s == p.stages) {
+            s = 0;
+            phase ^= 1;
+            a_desc = a_desc0;
+            b_desc = b_desc0;
+          }
         }
-        mma_commit_pair(&tmem_full[a]);
       }
     }
   } else {
@@ -782,8 +795,10 @@ int tl_gemm_tc_error() {
 
 // defer == 1 (swapped orientation only): leave the float32 partials [splits][M][N] in the
 // workspace for a fused finishing kernel of the caller; *splits_out gets their number.
-// defer == 2: with many tokens, use the CTA-pair kernel (cta_group::2) instead of the
-// single-CTA persistent kernel; it measures the same speed here and is kept selectable.
+// With many tokens the CTA-pair kernel (cta_group::2) runs from 512 tokens on (it is 5-9 %
+// faster there: 1,585 against 1,445 TFLOP/s on the gate/up product at 2,048 tokens), the
+// single-CTA persistent kernel below that; defer == 2 forces the pair kernel, defer == 3 the
+// single-CTA kernel.
 // out (+)= x[M, K] . w[N, K]^T.  x and w bfloat16 with K contiguous, ldx/ldw elements
 // between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
 // 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
@@ -808,7 +823,8 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   CUtensorMap map_row, map_col;
   int rc;
   if (!plan.swap && defer == 1) return TL_ERR_UNSUPPORTED;
-  if (plan.swap && defer == 2) defer = 0;
+  if (plan.swap && defer >= 2) defer = 0;
+  if (!plan.swap && defer == 0 && M >= 512) defer = 2;
   if (plan.swap) {
     // one split writes its output directly; several (or a deferred finish) go through partials
     const bool partials = plan.splits > 1 || defer;
@@ -845,12 +861,12 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   p.cols = N;
   constexpr int SMEM_LIMIT = 227 * 1024;
   if (defer == 2 && sm_count() % 2 == 0) {
-    // CTA pairs: 256-row tiles, tile width a multiple of 64 chosen for whole waves of pairs
+    // CTA pairs: 256-row tiles, tile width a multiple of 32 chosen for whole waves of pairs
     const int pairs = sm_count() / 2;
     const int row_tiles = (M + 255) / 256;
     long long best_cost = -1;
     int block_q = 256;
-    for (int q = 256; q >= 128; q -= 64) {
+    for (int q = 256; q >= 128; q -= 32) {
       const long long tiles = (long long)row_tiles * ((N + q - 1) / q);
       const long long cost = ((tiles + pairs - 1) / pairs) * (q + 24);
       if (best_cost < 0 || cost < best_cost) {

@@ -247,9 +247,10 @@ def _release_workspace() -> None:
         workspace_holder.flush_pending()
 
 
-def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs: bool = False) -> None:
+def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs=None) -> None:
     """out (+)= x @ w.T (+ bias) on the tcgen05 tensor cores; see csrc/gemm_tc.cu.
-    ``cta_pairs``: for many tokens use the kernel in which two CTAs share one 256-row MMA."""
+    ``cta_pairs``: for many tokens, True forces the kernel in which two CTAs share one 256-row
+    MMA, False the single-CTA kernel; None lets the library choose (pairs from 512 tokens on)."""
     _need_cuda(x, w, out, bias)
     _release_workspace()
     M, K = x.shape
@@ -264,7 +265,8 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs: bool = Fal
     kernels = 2 if need and splits.value > 1 else 1  # several splits: product + finishing pass
     code = _fn("gemm_tc", "tl_gemm_tc")(
         x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), epilogue, M, N, K, x.stride(0),
-        w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, 2 if cta_pairs else 0, None, _stream())
+        w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, {None: 0, True: 2, False: 3}[cta_pairs], None,
+        _stream())
     _check(code, "gemm_tc", kernels)
 
 
