@@ -714,6 +714,25 @@ struct Plan {
   int block_q, splits, k_blocks_per_split;
 };
 
+// The tile width that gives the shortest schedule of the persistent kernels, and its cost:
+// waves of one tile per SM (per SM pair), a tile's time in proportion to its width plus a
+// fixed part.  Single CTAs take 128 rows and widths 64..256 in steps of 16, pairs 256 rows and
+// widths 128..256 in steps of 32.
+long long best_width(int M, int N, bool pairs, int* width) {
+  const int units = pairs ? sm_count() / 2 : sm_count();
+  const int row_tiles = (M + (pairs ? 255 : BLOCK_P - 1)) / (pairs ? 256 : BLOCK_P);
+  long long best_cost = -1;
+  for (int q = 256; q >= (pairs ? 128 : 64); q -= (pairs ? 32 : 16)) {
+    const long long tiles = (long long)row_tiles * ((N + q - 1) / q);
+    const long long cost = ((tiles + units - 1) / units) * (q + 24);
+    if (best_cost < 0 || cost < best_cost) {
+      best_cost = cost;
+      *width = q;
+    }
+  }
+  return best_cost;
+}
+
 Plan make_plan(int M, int N, int K) {
   Plan plan;
   const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
@@ -738,20 +757,7 @@ Plan make_plan(int M, int N, int K) {
     plan.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     plan.splits = (k_blocks + plan.k_blocks_per_split - 1) / plan.k_blocks_per_split;
   } else {
-    // persistent kernel: the tile width that gives the shortest schedule
-    // (waves of one tile per SM, a tile's time in proportion to its width)
-    const int row_tiles = (M + BLOCK_P - 1) / BLOCK_P;
-    long long best_cost = -1;
-    plan.block_q = 256;
-    for (int q = 256; q >= 64; q -= 16) {
-      const long long tiles = (long long)row_tiles * ((N + q - 1) / q);
-      const long long waves = (tiles + sm_count() - 1) / sm_count();
-      const long long cost = waves * (q + 24);  // + a fixed part of a tile's time
-      if (best_cost < 0 || cost < best_cost) {
-        best_cost = cost;
-        plan.block_q = q;
-      }
-    }
+    best_width(M, N, false, &plan.block_q);
     plan.splits = 1;
     plan.k_blocks_per_split = k_blocks;
   }
@@ -795,10 +801,10 @@ int tl_gemm_tc_error() {
 
 // defer == 1 (swapped orientation only): leave the float32 partials [splits][M][N] in the
 // workspace for a fused finishing kernel of the caller; *splits_out gets their number.
-// With many tokens the CTA-pair kernel (cta_group::2) runs from 512 tokens on (it is 5-9 %
-// faster there: 1,585 against 1,445 TFLOP/s on the gate/up product at 2,048 tokens), the
-// single-CTA persistent kernel below that; defer == 2 forces the pair kernel, defer == 3 the
-// single-CTA kernel.
+// With many tokens the CTA-pair kernel (cta_group::2) runs from 512 tokens on (measured faster
+// there on every product of the model, by 3-9 %: 1,585 against 1,445 TFLOP/s on the gate/up
+// product at 2,048 tokens), the single-CTA persistent kernel below that; defer == 2 forces the
+// pair kernel, defer == 3 the single-CTA kernel.
 // out (+)= x[M, K] . w[N, K]^T.  x and w bfloat16 with K contiguous, ldx/ldw elements
 // between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
 // 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
@@ -864,16 +870,8 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
     // CTA pairs: 256-row tiles, tile width a multiple of 32 chosen for whole waves of pairs
     const int pairs = sm_count() / 2;
     const int row_tiles = (M + 255) / 256;
-    long long best_cost = -1;
     int block_q = 256;
-    for (int q = 256; q >= 128; q -= 32) {
-      const long long tiles = (long long)row_tiles * ((N + q - 1) / q);
-      const long long cost = ((tiles + pairs - 1) / pairs) * (q + 24);
-      if (best_cost < 0 || cost < best_cost) {
-        best_cost = cost;
-        block_q = q;
-      }
-    }
+    best_width(M, N, true, &block_q);
     if (!cached_map(&map_row, x, M, K, ldx, BLOCK_P) || !cached_map(&map_col, w, N, K, ldw, block_q / 2))
       return TL_ERR_UNSUPPORTED;
     p.block_q = block_q;
