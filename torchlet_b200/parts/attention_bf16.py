@@ -1,12 +1,14 @@
-"""Choice and planning of the bfloat16 tensor-core attention kernel
-(csrc/attention_mma.cu).  Returns False when it does not take the sizes (head_dim other
-than 64 or 128, more than 16 query heads per KV head); the caller then uses the any-size
-kernel.
+"""Choice and planning of the bfloat16 tensor-core attention kernels.  Returns False when
+they do not take the sizes (head_dim other than 64 or 128, more than 16 query heads per KV
+head); the caller then uses the any-size kernel.
 
-Requests that bring a single token (decode) run in tiles of 16 packed rows with their
-keys split over several CTAs, so that a few long requests still fill the GPU; requests
-that bring a portion of a prompt run in tiles of 64 packed rows planned here on the host,
-as the reference plans its prefill tiles (v10_triton_paged_gqa/layer/gqa.py:163-216).
+Requests that bring a single token (decode) run in tiles of 16 packed rows with their keys
+split over several CTAs, so that a few long requests still fill the GPU
+(csrc/attention_mma.cu).  Requests that bring a portion of a prompt run in row tiles planned
+here on the host, as the reference plans its prefill tiles
+(v10_triton_paged_gqa/layer/gqa.py:163-216): for head_dim 128 on the tcgen05 kernel
+(csrc/attention_tc.cu, two row tiles of whole tokens a CTA), else in tiles of 64 packed rows
+on the mma.sync kernel.
 """
 from __future__ import annotations
 
