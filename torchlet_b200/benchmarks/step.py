@@ -1,0 +1,98 @@
+"""What each kernel class costs inside the running decode step.
+
+    python -m torchlet_b200.benchmarks.step [--batch 8] [--context 4096] [--steps 64] [--layers 28]
+
+Builds a model of Qwen2.5-7B layer sizes with random bfloat16 weights, gives ``batch``
+requests a cached context of random keys and values, and times the decode step (CUDA events
+around replays of its CUDA graph) once as it is and once with each kernel class replaced by
+nothing.  The difference is that class's cost in place, overlap with its neighbours included.
+The steps with something left out compute garbage; only their time is used.
+"""
+from __future__ import annotations
+
+import argparse
+
+import torch
+
+from .. import ops
+from ..config import EngineConfig, Qwen2Config
+from ..engine import ModelRunner, StepEntry
+from ..engine.loading import build_model
+from ..sampling import SampleSpec
+from ..weights import random_tensors
+
+SIZES = {
+    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 152064, "hidden_size": 3584, "intermediate_size": 18944,
+    "num_attention_heads": 28, "num_key_value_heads": 4, "max_position_embeddings": 32768,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
+}
+CLASSES = ("attention_mma", "finish_accum_norm", "finish_qkv_rope")
+
+
+def time_step(model, batch: int, context: int, steps: int, warmup: int = 4) -> float:
+    """Microseconds of one decode step of ``batch`` requests near ``context`` cached tokens."""
+    page = 16
+    config = EngineConfig(dtype="bfloat16", max_decode_slots=batch, kv_block_size=page, max_seq_len=context,
+                          max_num_blocks=batch * (-(-context // page)) + 1, max_num_batched_tokens=2048)
+    runner = ModelRunner(model, config)
+    generator = torch.Generator(device="cuda:0").manual_seed(17)
+    for pages in runner.storage.pages:
+        flat = pages.view(-1)
+        for start in range(0, flat.numel(), 1 << 27):
+            chunk = flat[start:start + (1 << 27)]
+            chunk.copy_(torch.randn(chunk.shape, generator=generator, device=pages.device).mul_(0.5))
+    ids = [f"d{i}" for i in range(batch)]
+    for rid in ids:
+        runner.admit(rid)
+        if not runner.cache.extend(rid, context - steps - warmup):
+            raise RuntimeError("the page pool is too small")
+        runner.cache.advance(rid, context - steps - warmup)
+    tokens = torch.randint(0, model.spec.vocab_size, (steps + warmup, batch)).tolist()
+
+    def step(k):
+        runner.run([StepEntry(rid, [tokens[k][i]], sample=SampleSpec(0.0, i, k)) for i, rid in enumerate(ids)])
+
+    for k in range(warmup):
+        step(k)
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record()
+    for k in range(warmup, warmup + steps):
+        step(k)
+    end.record()
+    torch.cuda.synchronize()
+    for rid in ids:
+        runner.finish(rid)
+    del runner
+    torch.cuda.empty_cache()
+    return begin.elapsed_time(end) / steps * 1e3
+
+
+def main(argv=None) -> int:
+    parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    parser.add_argument("--batch", type=int, default=8)
+    parser.add_argument("--context", type=int, default=4096)
+    parser.add_argument("--steps", type=int, default=64)
+    parser.add_argument("--layers", type=int, default=28)
+    args = parser.parse_args(argv)
+    config = Qwen2Config.from_dict(dict(SIZES, num_hidden_layers=args.layers))
+    tensors = random_tensors(config, 4, std=0.02, norm_std=0.0, dtype="bfloat16", device="cuda:0")
+    model = build_model(config, tensors, "bfloat16")
+    del tensors
+    full = time_step(model, args.batch, args.context, args.steps)
+    print(f"batch {args.batch}, context {args.context}, {args.layers} layers")
+    print(f"{'full step':32s} {full:9.1f} us")
+    for name in CLASSES:
+        original = getattr(ops, name)
+        setattr(ops, name, lambda *a, **k: None)
+        try:
+            without = time_step(model, args.batch, args.context, args.steps)
+        finally:
+            setattr(ops, name, original)
+        print(f"{'without ' + name:32s} {without:9.1f} us   {name} costs {full - without:7.1f} us a step, "
+              f"{(full - without) / args.layers:6.2f} us a layer")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
