@@ -116,3 +116,50 @@ def test_random_orders_keep_the_invariants(seed):
                     assert table[pos // m.page_size] != 0
     m.reset(); m.check()
     assert all(pool.num_free == pool.num_pages - 1 for pool in m.pools)
+
+
+def test_decode_pass_matches_single_calls():
+    """begin_decode / end_decode do for a batch what extend / advance do one by one,
+    the length limit included."""
+    from torchlet_b200.cache.manager import CacheError, CacheManager, GroupSpec
+
+    def fresh():
+        manager = CacheManager([GroupSpec(2, 16, None, (0,), 40), GroupSpec(2, 16, 20, (1,), 40)], page_size=8, max_slots=4,
+                               max_seq_len=50)
+        for rid, length in (("a", 7), ("b", 16), ("c", 30)):
+            manager.admit(rid)
+            assert manager.extend(rid, length)
+            manager.advance(rid, length)
+        return manager
+
+    one, batch = fresh(), fresh()
+    ids = ["a", "b", "c"]
+    for _ in range(20):
+        for rid in ids:
+            length = one.num_tokens(rid)
+            assert one.extend(rid, length + 1)
+            one.advance(rid, length + 1)
+        before, slots = batch.begin_decode(ids)
+        batch.end_decode(ids)
+        assert [batch.num_tokens(r) for r in ids] == [one.num_tokens(r) for r in ids]
+        assert before.tolist() == [n - 1 for n in (batch.num_tokens(r) for r in ids)]
+        assert slots.tolist() == [batch.slot_of(r) for r in ids]
+        for g in range(2):
+            # the same logical pages are held (which physical ones depends on the order of the calls)
+            assert all([p != 0 for p in batch.table(r, g)] == [p != 0 for p in one.table(r, g)] for r in ids)
+        batch.check()
+    # request "c" is at the limit of 50 tokens now
+    assert batch.num_tokens("c") == 50
+    try:
+        batch.begin_decode(["c"])
+    except CacheError:
+        pass
+    else:
+        raise AssertionError("the length limit was not enforced")
+    # a pool that runs dry is reported by index
+    small = CacheManager([GroupSpec(2, 16, None, (0,), 3)], page_size=8, max_slots=2, max_seq_len=64)
+    for rid in ("x", "y"):
+        small.admit(rid)
+        assert small.extend(rid, 8)
+        small.advance(rid, 8)
+    assert small.begin_decode(["x", "y"]) == 0  # two pages, both taken

@@ -77,6 +77,7 @@ class _RequestPages:
     num_tokens: int = 0  # tokens whose keys and values are in pages (steps done so far)
     tables: list = field(default_factory=list)  # per group: logical page -> physical page
     first_live: list = field(default_factory=list)  # per group: first logical page still held
+    capacity: int = 0  # tokens that fit the pages reserved so far, at most the length limit
 
 
 class CacheManager:
@@ -133,6 +134,8 @@ class CacheManager:
 
     def can_extend(self, request_id: Hashable, new_len: int) -> bool:
         record = self._requests[request_id]
+        if new_len <= record.capacity:
+            return True
         need = self._pages_needed(record, new_len)
         return all(n <= pool.num_free for n, pool in zip(need, self.pools))
 
@@ -143,6 +146,8 @@ class CacheManager:
         if new_len > self.max_seq_len:
             raise CacheError(f"request {request_id!r} would hold {new_len} tokens, the limit is {self.max_seq_len}")
         record = self._requests[request_id]
+        if new_len <= record.capacity:
+            return True
         need = self._pages_needed(record, new_len)
         if any(n > pool.num_free for n, pool in zip(need, self.pools)):
             return False
@@ -151,7 +156,36 @@ class CacheManager:
                 start = len(table)
                 table.extend(pool.take(n))
                 self.table_arrays[g][record.slot, start:start + n] = table[start:]
+        record.capacity = min(min(len(table) for table in record.tables) * self.page_size, self.max_seq_len)
         return True
+
+    def begin_decode(self, request_ids) -> tuple:
+        """One more token for each request of a decode step, in one pass: makes room for it
+        and returns (lengths so far, slots) as int32 arrays, or the index of the first
+        request that gets no page (the requests before it keep what they reserved)."""
+        n = len(request_ids)
+        before = np.empty(n, dtype=np.int32)
+        slots = np.empty(n, dtype=np.int32)
+        requests = self._requests
+        for i, request_id in enumerate(request_ids):
+            record = requests[request_id]
+            length = record.num_tokens
+            before[i] = length
+            slots[i] = record.slot
+            if length + 1 > record.capacity and not self.extend(request_id, length + 1):
+                return i
+        return before, slots
+
+    def end_decode(self, request_ids) -> None:
+        """The step wrote one more token of each request (``advance`` by one, in one pass)."""
+        windowed = any(group.window is not None for group in self.groups)
+        requests = self._requests
+        for request_id in request_ids:
+            record = requests[request_id]
+            if windowed or record.num_tokens + 1 > record.capacity:
+                self.advance(request_id, record.num_tokens + 1)
+            else:
+                record.num_tokens += 1
 
     def advance(self, request_id: Hashable, new_len: int) -> int:
         """After a step wrote the request's tokens up to ``new_len``: record the length

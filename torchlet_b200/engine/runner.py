@@ -317,16 +317,16 @@ class ModelRunner:
         state = self._graphs.get(b) or self._capture_decode_graph(b)
         layout, words = state["layout"], state["words"]
         W = cache.max_pages_per_request
-        before = np.fromiter((cache.num_tokens(e.request_id) for e in entries), dtype=np.int32, count=n)
-        slots = np.fromiter((cache.slot_of(e.request_id) for e in entries), dtype=np.int32, count=n)
+        ids = [e.request_id for e in entries]
+        if len(set(ids)) != n:
+            raise ValueError("a request appears twice in one step")
         toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
         if n and (toks.min() < 0 or toks.max() >= self.vocab_size):
             raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
-        if len(set(slots.tolist())) != n:
-            raise ValueError("a request appears twice in one step")
-        for e, length in zip(entries, before):
-            if not cache.extend(e.request_id, int(length) + 1):
-                raise OutOfPages(f"no pages left for request {e.request_id!r}")
+        room = cache.begin_decode(ids)
+        if not isinstance(room, tuple):
+            raise OutOfPages(f"no pages left for request {ids[room]!r}")
+        before, slots = room
         host, _ = self._meta(words)
         host[:words] = state["template"]
         put = lambda name, values: host.__setitem__(slice(layout[name][0], layout[name][0] + n), values)
@@ -348,8 +348,7 @@ class ModelRunner:
         self._meta_event[turn].record()
         state["graph"].replay()
         ops.launch_count += state["kernels"]
-        for e, length in zip(entries, before):
-            cache.advance(e.request_id, int(length) + 1)
+        cache.end_decode(ids)
         self.steps_run += 1
         self.graph_steps += 1
         return StepResult(state["logits"][:n], state["tokens"][:n])
