@@ -88,6 +88,52 @@ def test_sampling_does_not_depend_on_the_batch(tmp_path):
     assert scores[alone[2][0]] >= max(scores) - 1e-3
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_running_one_step_ahead_equals_stepping(tmp_path, dtype):
+    """``Engine.run`` launches a decode step before it has read the tokens of the one before;
+    it must give what synchronous ``step()`` calls give, also when requests end by a stop
+    token (one lane of the step under way is void then), by their token limit, and when new
+    requests join as slots come free."""
+    from torchlet_b200 import LLM, SamplingParams
+    from torchlet_b200.engine.scheduler import Request
+
+    folder = model_dir(tmp_path, "B")
+    cfg = tiny_configs.ALL["B"][0]
+    prompts = [tiny_configs.make_ids(cfg, n, seed=80 + i) for i, n in enumerate((3, 21, 9, 30, 14, 6))]
+
+    def requests(stops):
+        limits = (25, 9, 31, 16, 12, 40)
+        return [Request(list(p), SamplingParams(max_new_tokens=m, temperature=t, seed=7 + i, stop_token_ids=stops))
+                for i, (p, m, t) in enumerate(zip(prompts, limits, (0.0, 0.9, 0.0, 0.7, 0.0, 1.2)))]
+
+    def stepping(stops):
+        llm = LLM(folder, max_decode_slots=3, kv_block_size=8, dtype=dtype, max_seq_len=128)
+        reqs = requests(stops)
+        llm.engine.add_requests(reqs)
+        while llm.engine.scheduler.has_work():
+            llm.engine.step()
+        llm.engine.runner.cache.check()
+        return [r.output_tokens for r in reqs]
+
+    def running(stops):
+        llm = LLM(folder, max_decode_slots=3, kv_block_size=8, dtype=dtype, max_seq_len=128)
+        reqs = requests(stops)
+        llm.engine.generate(reqs)
+        llm.engine.runner.cache.check()
+        assert llm.engine.runner.cache.live_requests() == []
+        assert llm.engine.runner.graph_steps > 0 and llm.engine.steps_ahead > 0
+        return [r.output_tokens for r in reqs]
+
+    free = stepping(())
+    assert [len(x) for x in free] == [25, 9, 31, 16, 12, 40]
+    assert running(()) == free
+    # tokens that really occur, some of them early, as stop tokens
+    stops = tuple({free[0][6], free[2][3], free[5][20], free[3][15]})
+    cut = stepping(stops)
+    assert any(len(a) < len(b) for a, b in zip(cut, free))
+    assert running(stops) == cut
+
+
 def test_small_pool_preempts_and_gives_the_same_tokens(tmp_path):
     from torchlet_b200 import LLM
 

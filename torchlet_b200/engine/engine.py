@@ -1,8 +1,9 @@
 """The engine: scheduler above, step function below, one loop.
 
 One ``step()`` = schedule -> run the mixed batch -> sample -> apply tokens -> free what
-finished (the reference's loop: v10_triton_paged_gqa/engine.py:101-135, 204-217).  The
-loop is synchronous; a failure inside a step ends every live request with that error
+finished (the reference's loop: v10_triton_paged_gqa/engine.py:101-135, 204-217).
+``step()`` is synchronous; ``run()`` keeps one decode step ahead of the tokens it has seen
+(see ``_next_decode``).  A failure inside a step ends every live request with that error
 and gives all pages and slots back, as the reference's ``fail_all`` does
 (engine.py:215-217).
 """
@@ -14,8 +15,9 @@ from .. import ops
 from ..config.engine import EngineConfig
 from ..logger import logger
 from ..parts.model import LayeredModel
-from .runner import ModelRunner, StepEntry
-from .scheduler import Request, Scheduler
+from ..sampling import SampleSpec
+from .runner import ModelRunner, OutOfPages, StepEntry
+from .scheduler import Request, RequestState, ScheduledPortion, Scheduler, StepPlan
 
 
 class Engine:
@@ -23,6 +25,7 @@ class Engine:
         self.config = config or EngineConfig()
         self.runner = ModelRunner(model, self.config)
         self.scheduler = Scheduler(self.runner, self.config.max_num_batched_tokens, self.config.max_seq_len)
+        self.steps_ahead = 0  # decode steps launched before the tokens of the step before were read
 
     def add_requests(self, requests: list) -> None:
         for request in requests:
@@ -30,26 +33,30 @@ class Engine:
         for request in requests:
             self.scheduler.add_request(request)
 
+    def _entries(self, plan) -> list:
+        scheduler = self.scheduler
+        entries = []
+        for portion in plan.portions:
+            request = portion.request
+            prompt_len = len(request.prompt_tokens)
+            if portion.start >= prompt_len:  # decoding (or recomputing produced tokens)
+                first = portion.start - prompt_len
+                tokens = request.output_tokens[first:first + portion.length]
+            elif portion.start + portion.length <= prompt_len:
+                tokens = request.prompt_tokens[portion.start:portion.start + portion.length]
+            else:
+                tokens = request.all_tokens[portion.start:portion.start + portion.length]
+            entries.append(StepEntry(request.request_id, tokens,
+                                     sample=scheduler.sample_spec(request) if portion.samples else None))
+        return entries
+
     def step(self) -> list:
         """One engine step; returns the requests that finished (or failed) in it."""
         scheduler = self.scheduler
         plan = scheduler.schedule()
         done = list(plan.failed)
         if plan.portions:
-            entries = []
-            for portion in plan.portions:
-                request = portion.request
-                prompt_len = len(request.prompt_tokens)
-                if portion.start >= prompt_len:  # decoding (or recomputing produced tokens)
-                    first = portion.start - prompt_len
-                    tokens = request.output_tokens[first:first + portion.length]
-                elif portion.start + portion.length <= prompt_len:
-                    tokens = request.prompt_tokens[portion.start:portion.start + portion.length]
-                else:
-                    tokens = request.all_tokens[portion.start:portion.start + portion.length]
-                entries.append(StepEntry(request.request_id, tokens,
-                                         sample=scheduler.sample_spec(request) if portion.samples else None))
-            result = self.runner.run(entries)
+            result = self.runner.run(self._entries(plan))
             sampled = result.tokens.tolist() if result.tokens is not None else []
             done += scheduler.update(plan, sampled)
             if done:  # nothing is handed back before the kernels' own error words have been read
@@ -57,12 +64,80 @@ class Engine:
         scheduler.drain_finished()
         return done
 
+    # ----------------------------------------------------- decode, one step ahead
+    # While every running request decodes, the next step's inputs are known before this
+    # step's tokens are: positions and pages follow from the lengths, and the token itself
+    # can be handed over on the device.  ``run`` therefore launches step k + 1 before it
+    # reads step k's tokens, so that the host's share of a step (scheduling, metadata, the
+    # copy of the tokens) runs beside the GPU and not between two of its steps.  A request
+    # that ends at step k for a reason the host could not foresee (a stop token) has run one
+    # step too many by then; its lane of step k + 1 is dropped, and its pages, given back
+    # at step k, are reused only by steps launched later on the same stream.
+    def _next_decode(self, plan):
+        """The plan and entries of the step after ``plan`` if that can be told without its
+        tokens: every running request is in ``plan`` with one decoded token and stays under
+        its token limit, and nothing waits for a free slot.  Else None."""
+        scheduler = self.scheduler
+        if not self.config.cuda_graph or len(plan.portions) != len(scheduler.running):
+            return None
+        if scheduler.waiting and self.runner.cache.num_free_slots > 0:
+            return None
+        portions, entries = [], []
+        for portion in plan.portions:
+            request = portion.request
+            produced = len(request.output_tokens)
+            if (portion.length != 1 or not portion.samples or portion.start < len(request.prompt_tokens)
+                    or produced + 2 > request.params.max_new_tokens
+                    or request.num_tokens + 2 > self.runner.cache.max_seq_len):
+                return None
+            portions.append(ScheduledPortion(request, portion.start + 1, 1, True))
+            entries.append(StepEntry(request.request_id, [0],
+                                     sample=SampleSpec(request.params.temperature, request.seed, produced + 1)))
+        if not self.runner.can_feed_previous(entries):
+            return None
+        return StepPlan(portions, [], []), entries
+
     def run(self) -> list:
         """Step until no request is waiting or running; returns all that ended."""
+        scheduler, runner = self.scheduler, self.runner
         ended = []
+        ahead = None  # (plan, pinned tokens, event) of a step that is launched but not yet applied
         try:
-            while self.scheduler.has_work():
-                ended += self.step()
+            while ahead is not None or scheduler.has_work():
+                if ahead is None:
+                    plan = scheduler.schedule()
+                    ended += plan.failed
+                    if not plan.portions:
+                        scheduler.drain_finished()
+                        continue
+                    result = runner.run(self._entries(plan))
+                    if result.tokens is None:  # portions of prompts that sample nothing
+                        scheduler.update(plan, [])
+                        scheduler.drain_finished()
+                        continue
+                    ahead = (plan, *runner.tokens_to_host(result))
+                plan, tokens, event = ahead
+                ahead = None
+                following = self._next_decode(plan)
+                if following is not None:
+                    try:
+                        result = runner.run(following[1], feed_previous=True)
+                        ahead = (following[0], *runner.tokens_to_host(result))
+                        self.steps_ahead += 1
+                    except OutOfPages:  # the scheduler decides who gives way, with this step's tokens in hand
+                        ahead = None
+                event.synchronize()
+                values = tokens.tolist()
+                if any(p.request.state is not RequestState.RUNNING for p in plan.portions):
+                    # lanes of requests that ended one step earlier: that step was launched before the host knew
+                    live = [(p, v) for p, v in zip(plan.portions, values) if p.request.state is RequestState.RUNNING]
+                    plan = StepPlan([p for p, _ in live], [], [])
+                    values = [v for _, v in live]
+                done = scheduler.update(plan, values)
+                if done:
+                    ops.raise_on_wait_errors()  # nothing is handed back before the kernels' error words are read
+                    ended += done
+                scheduler.drain_finished()
         except Exception as exc:  # a failed step fails every live request
             logger.error("engine step failed: %s", exc)
             ended += self.scheduler.fail_all(exc)

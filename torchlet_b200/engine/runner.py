@@ -125,6 +125,10 @@ class ModelRunner:
         self._meta_turn = 0
         self._aux_offset = 0
         self._graphs: dict = {}
+        self._last_graph_ids: Optional[list] = None  # requests of the last step, if it was a graph decode step
+        self._tokens_host = [None, None]
+        self._tokens_event = [None, None]
+        self._tokens_turn = 0
         self._graph_safe = all(getattr(block.mixer, "graph_safe", False) for block in model.blocks)
         self.steps_run = 0
         self.graph_steps = 0
@@ -185,6 +189,7 @@ class ModelRunner:
 
     def finish(self, request_id: Hashable) -> None:
         self.cache.finish(request_id)
+        self._last_graph_ids = None
 
     def reserve(self, request_id: Hashable, new_len: int) -> bool:
         """Pages for the request's tokens up to ``new_len``; False when a pool is short."""
@@ -197,15 +202,25 @@ class ModelRunner:
         The tensor is reused by the next step."""
         return self.run(entries).logits
 
-    def run(self, entries: Sequence[StepEntry]) -> StepResult:
+    def run(self, entries: Sequence[StepEntry], feed_previous: bool = False) -> StepResult:
         """Run the entries as one batch: logits at the wanted places and, for entries
         with ``sample`` set, a token sampled from the logits of their last token.
-        Both tensors are reused by the next step."""
+        Both tensors are reused by the next step.
+
+        ``feed_previous``: the entries are the requests of the previous step, which was a
+        decode step replayed from a graph, in the same order; each one's token is the one
+        that step sampled, taken on the device (``tokens`` of the entries is ignored), so
+        this step can be launched before the host has seen those tokens."""
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepResult(None, None)
+        if feed_previous:
+            if not self.can_feed_previous(entries):
+                raise ValueError("feed_previous needs the previous step's requests, in its order, as a graph decode step")
+            return self._run_decode_graph(entries, feed_previous=True)
         if self._graphable(entries):
             return self._run_decode_graph(entries)
+        self._last_graph_ids = None
         ctx, caches = self._build(entries)
         with torch.no_grad():
             acc = self.model.forward(ctx, caches)
@@ -310,7 +325,26 @@ class ModelRunner:
         self._graphs[b] = state
         return state
 
-    def _run_decode_graph(self, entries) -> StepResult:
+    def can_feed_previous(self, entries) -> bool:
+        """Whether ``run(entries, feed_previous=True)`` applies: see ``run``."""
+        return (self._last_graph_ids is not None and self._graphable(entries)
+                and [e.request_id for e in entries] == self._last_graph_ids)
+
+    def tokens_to_host(self, result: StepResult):
+        """Starts the copy of a step's sampled tokens into pinned host memory; returns
+        (pinned int32 tensor, event).  After ``event.synchronize()`` the tensor holds them.
+        Two buffers take turns, so the tokens of two steps can be under way."""
+        turn = self._tokens_turn = self._tokens_turn ^ 1
+        count = result.tokens.numel()
+        if self._tokens_host[turn] is None or self._tokens_host[turn].numel() < count:
+            self._tokens_host[turn] = torch.empty(max(count, 256), dtype=torch.int32, pin_memory=True)
+            self._tokens_event[turn] = torch.cuda.Event()
+        host = self._tokens_host[turn][:count]
+        host.copy_(result.tokens, non_blocking=True)
+        self._tokens_event[turn].record()
+        return host, self._tokens_event[turn]
+
+    def _run_decode_graph(self, entries, feed_previous: bool = False) -> StepResult:
         cache = self.cache
         n = len(entries)
         b = self._bucket(n)
@@ -320,9 +354,12 @@ class ModelRunner:
         ids = [e.request_id for e in entries]
         if len(set(ids)) != n:
             raise ValueError("a request appears twice in one step")
-        toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
-        if n and (toks.min() < 0 or toks.max() >= self.vocab_size):
-            raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
+        if feed_previous:
+            toks = 0  # placeholders; the device copy below puts the sampled tokens in
+        else:
+            toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
+            if n and (toks.min() < 0 or toks.max() >= self.vocab_size):
+                raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
         room = cache.begin_decode(ids)
         if not isinstance(room, tuple):
             raise OutOfPages(f"no pages left for request {ids[room]!r}")
@@ -346,9 +383,13 @@ class ModelRunner:
         if self._meta_event[turn] is None:
             self._meta_event[turn] = torch.cuda.Event()
         self._meta_event[turn].record()
+        if feed_previous:  # the same graph sampled them into its token buffer one step ago
+            o = layout["tok"][0]
+            state["dev"][o:o + n].copy_(state["tokens"][:n])
         state["graph"].replay()
         ops.launch_count += state["kernels"]
         cache.end_decode(ids)
+        self._last_graph_ids = ids
         self.steps_run += 1
         self.graph_steps += 1
         return StepResult(state["logits"][:n], state["tokens"][:n])
