@@ -71,3 +71,47 @@ def test_many_requests_arriving_while_others_run(dtype):
         for request, fresh in zip(requests, again):
             alone.generate([fresh])
             assert fresh.output_tokens == request.output_tokens, f"request {request.request_id} depends on its batch"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_run_with_a_tight_pool_and_stop_tokens(dtype):
+    """``Engine.run`` (one decode step ahead) with everything at once: more requests than
+    slots, a pool that forces preemption (also when the step ahead finds no page), stop tokens
+    that end requests a step before the host knows.  In float32 every output equals the request
+    run alone with synchronous steps."""
+    from torchlet_b200.engine.scheduler import Request
+    from torchlet_b200.sampling import SamplingParams
+
+    count = 30
+    rng = random.Random(11)
+    stops = tuple(rng.sample(range(CONFIG["vocab_size"]), 60))  # 3 % of the vocabulary ends a request
+
+    def make():
+        r = random.Random(12)
+        out = []
+        for i in range(count):
+            prompt = [r.randrange(CONFIG["vocab_size"]) for _ in range(r.randint(4, 120))]
+            out.append(Request(prompt, SamplingParams(max_new_tokens=r.randint(8, 60), temperature=r.choice([0.0, 0.9]),
+                                                      seed=500 + i, stop_token_ids=stops)))
+        return out
+
+    engine = build(dtype, max_decode_slots=6, kv_block_size=16, max_num_blocks=31, max_num_batched_tokens=128)
+    requests = make()
+    engine.generate(requests)
+    engine.runner.cache.check()
+    stats = engine.scheduler.stats
+    assert stats.finished == count and stats.failed == 0
+    assert stats.preemptions > 0, "the pool was meant to be too small"
+    assert engine.steps_ahead > 0
+    assert all(r.error is None for r in requests)
+    assert any(len(r.output_tokens) < r.params.max_new_tokens for r in requests), "no stop token was drawn"
+    assert all(t not in stops for r in requests for t in r.output_tokens)
+    assert engine.runner.cache.live_requests() == []
+    assert engine.runner.cache.pools[0].num_free == 30 and engine.runner.cache.num_free_slots == 6
+    if dtype == "float32":
+        alone = build(dtype, max_decode_slots=1, kv_block_size=16, max_num_batched_tokens=512)
+        for request, fresh in zip(requests, make()):
+            alone.add_requests([fresh])
+            while alone.scheduler.has_work():
+                alone.step()
+            assert fresh.output_tokens == request.output_tokens, f"request {request.request_id} depends on its batch"
