@@ -19,7 +19,7 @@
 //       128 x block_q tiles with two accumulators in tensor memory, so that the epilogue of
 //       a tile overlaps the next tile's products; block_q is chosen for whole waves.
 //   gemm_tc_pair_kernel        the same with pairs of CTAs (cta_group::2) sharing a
-//       256 x block_q tile; selectable, it measures the same speed as the single-CTA form.
+//       256 x block_q tile; it serves 512 tokens and more.
 //
 // Reference counterparts: cuBLAS through nn.Linear (v10_triton_paged_gqa/layer/gqa.py:
 // 122-124, 84; model/qwen2_5.py:83-87) and the Triton GEMMs swiglu_kernel/down_kernel
