@@ -1,0 +1,86 @@
+"""The engine at Qwen2.5-7B LAYER SIZES (hidden 3584, 28 heads in 4 groups of 7, head_dim 128,
+intermediate 18944, vocabulary 152064, untied LM head), one layer, random weights: logits of a
+40-token sequence against the plain implementation for three ways of cutting it into steps,
+in float32 and in bfloat16.  These are the sizes the benchmark runs, so the kernels are the
+ones it times (tcgen05 products and attention, the fused finishing kernels of single-token
+steps)."""
+import pytest
+import torch
+
+import harness
+import plain_model
+import tiny_configs
+
+pytestmark = pytest.mark.gpu
+
+CONFIG = {
+    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 152064, "hidden_size": 3584, "intermediate_size": 18944,
+    "num_hidden_layers": 1, "num_attention_heads": 28, "num_key_value_heads": 4, "max_position_embeddings": 256,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
+}
+LENGTH = 40
+CUTS = {"whole": [40], "last tokens one by one": [33] + [1] * 7, "portions": [5, 2, 17, 3, 13]}
+
+
+@pytest.fixture(scope="module")
+def case():
+    weights = tiny_configs.make_weights(CONFIG, seed=21, std=0.02, norm_std=0.02, dtype=torch.bfloat16)
+    ids = tiny_configs.make_ids(CONFIG, LENGTH, seed=22)
+    plain = plain_model.forward_logits(CONFIG, {k: v.float() for k, v in weights.items()}, ids)
+    return weights, ids, plain
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_logits_at_benchmark_layer_sizes(case, dtype):
+    from torchlet_b200.config import EngineConfig, Qwen2Config
+    from torchlet_b200.engine import ModelRunner
+    from torchlet_b200.engine.loading import build_model
+
+    weights, ids, plain = case
+    model = build_model(Qwen2Config.from_dict(CONFIG), weights, dtype)
+    runner = ModelRunner(model, EngineConfig(dtype=dtype, max_decode_slots=2, kv_block_size=16, max_num_blocks=12,
+                                             max_seq_len=64, max_num_batched_tokens=64, cuda_graph=False))
+    limit = harness.TOLERANCE[dtype] * plain.abs().max()
+    results = {}
+    for name, cuts in CUTS.items():
+        got = harness.replay(runner, name, ids, cuts)
+        assert (got - plain).abs().max() <= limit, f"{dtype}, {name}: {(got - plain).abs().max()} > {limit}"
+        results[name] = got
+    if dtype == "float32":  # the 32-bit path does not depend on the cut at all
+        assert torch.equal(results["whole"], results["portions"])
+        assert torch.equal(results["whole"], results["last tokens one by one"])
+    runner.cache.check()
+
+
+def test_a_long_portion_in_bfloat16_against_the_32_bit_path(case):
+    """640 tokens in one step: the products run on the CTA-pair kernel (512 tokens and more),
+    the attention over several key tiles with two row tiles a CTA.  The 32-bit path of the
+    engine (checked against the plain implementation above and in the other tests) is the
+    reference here: the plain implementation would need minutes for this on the CPU."""
+    from torchlet_b200.config import EngineConfig, Qwen2Config
+    from torchlet_b200.engine import ModelRunner, StepEntry
+    from torchlet_b200.engine.loading import build_model
+
+    weights, _, _ = case
+    ids = tiny_configs.make_ids(CONFIG, 640, seed=23)
+    want_rows = [0, 1, 127, 128, 300, 511, 512, 639]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        model = build_model(Qwen2Config.from_dict(dict(CONFIG, max_position_embeddings=1024)), weights, dtype)
+        runner = ModelRunner(model, EngineConfig(dtype=dtype, max_decode_slots=2, kv_block_size=16, max_num_blocks=48,
+                                                 max_seq_len=704, max_num_batched_tokens=640, cuda_graph=False))
+        runner.admit("p")
+        got[dtype] = runner.step([StepEntry("p", ids, want_rows)]).cpu().clone()
+        # eight more tokens one by one, from the cache the long step left
+        tail = []
+        for token in tiny_configs.make_ids(CONFIG, 8, seed=24):
+            tail.append(runner.step([StepEntry("p", [token], [0])]).cpu().clone())
+        got[dtype] = torch.cat([got[dtype]] + tail)
+        runner.finish("p")
+        runner.cache.check()
+        del runner, model
+        torch.cuda.empty_cache()
+    harness.assert_close(got["bfloat16"], got["float32"], "bfloat16", "640 tokens and 8 decoded")
+    from torchlet_b200 import ops
+
+    ops.raise_on_wait_errors()
