@@ -44,6 +44,9 @@ class AttentionMixer(Mixer):
         if self.head_dim % 8 or self.head_dim > 256:
             raise ValueError(f"head_dim {self.head_dim} is not supported (multiples of 8 up to 256)")
         self.positions = build_part(POSITIONS, p["positions"]) if p.get("positions") else None
+        # single-token steps are replayed from a CUDA graph only if the position encoding, too,
+        # plans nothing on the host
+        self.graph_safe = getattr(self.positions, "graph_safe", True)
         self.q_size = self.num_heads * self.head_dim
         self.kv_size = self.num_kv_heads * self.head_dim
         self.qkv_proj: Linear | None = None
@@ -65,6 +68,8 @@ class AttentionMixer(Mixer):
         out.append(TensorSpec(f"{prefix}o_proj.weight", (hidden, q_size)))
         if p.get("o_bias", False):
             out.append(TensorSpec(f"{prefix}o_proj.bias", (hidden,)))
+        if p.get("positions"):  # a position encoding may have tensors of its own
+            out += POSITIONS.get(p["positions"].kind).expected_tensors(p["positions"], prefix)
         return out
 
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:

@@ -77,7 +77,10 @@ class Norm(Part):
 
 
 class Positions(Part):
-    """A position encoding applied inside a mixer."""
+    """A position encoding applied inside a mixer.  ``graph_safe`` False keeps a model that
+    uses it out of the captured decode graph (it plans on the host)."""
+
+    graph_safe = True
 
 
 class Mixer(Part):
