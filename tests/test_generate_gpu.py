@@ -181,3 +181,12 @@ def test_command_line(tmp_path):
     assert len(lines) == 2 and all(len(eval(line)) == 5 for line in lines)
     cfg, w = harness.weights_for("A")
     assert eval(lines[0]) == plain_model.greedy_generate(cfg, w, [1, 2, 3], 5)
+
+
+def test_a_pool_larger_than_the_memory_is_refused_in_words(tmp_path):
+    from torchlet_b200 import LLM
+    from torchlet_b200.cache.manager import CacheError
+
+    folder = model_dir(tmp_path, "A")
+    with pytest.raises(CacheError, match="GiB are free"):
+        LLM(folder, max_decode_slots=4, kv_block_size=16, max_num_blocks=200_000_000, dtype="float32", max_seq_len=128)

@@ -15,7 +15,7 @@ from typing import Optional
 
 import torch
 
-from .manager import CacheManager, GroupSpec
+from .manager import CacheError, CacheManager, GroupSpec
 
 
 @dataclass
@@ -56,6 +56,15 @@ class CacheStorage:
         self.needs = needs
         self.page_size = page_size
         self.groups, self.where = plan_groups(needs, num_pages)
+        element = torch.empty((), dtype=dtype).element_size()
+        need = sum(len(g.entries) * g.num_pages * 2 * g.num_kv_heads * page_size * g.head_dim * element for g in self.groups)
+        if torch.device(device).type == "cuda":
+            free, _ = torch.cuda.mem_get_info(device)
+            if need > free:
+                raise CacheError(
+                    f"the page pool needs {need / 2**30:.1f} GiB ({num_pages} pages of {page_size} tokens for "
+                    f"{max_slots} slots), {free / 2**30:.1f} GiB are free: lower max_num_blocks, max_seq_len or "
+                    "max_decode_slots")
         self.manager = CacheManager(self.groups, page_size, max_slots, max_seq_len)
         self.pages = [
             torch.zeros((len(g.entries), g.num_pages, 2, g.num_kv_heads, page_size, g.head_dim), device=device, dtype=dtype)
