@@ -752,6 +752,9 @@ Plan make_plan(int M, int N, int K) {
     const int tiles = ((N + BLOCK_P - 1) / BLOCK_P) * ((M + plan.block_q - 1) / plan.block_q);
     const int ctas_per_sm = plan.block_q <= 16 ? 3 : (plan.block_q <= 128 ? 2 : 1);
     int splits = ctas_per_sm * sm_count() / tiles;
+    // few tiles (the qkv, o and down products): three quarters of that; fewer, longer splits
+    // leave the finishing kernel less to add (measured: -1.2 % of a batch-8 decode step)
+    if (tiles < 100) splits = splits * 3 / 4;
     if (splits < 1) splits = 1;
     if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;  // at least 4 k-blocks a split
     plan.k_blocks_per_split = (k_blocks + splits - 1) / splits;
