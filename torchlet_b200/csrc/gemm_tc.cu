@@ -750,10 +750,11 @@ Plan make_plan(int M, int N, int K) {
   if (plan.swap) {
     plan.block_q = pick_block_q_swapped(M);
     const int tiles = ((N + BLOCK_P - 1) / BLOCK_P) * ((M + plan.block_q - 1) / plan.block_q);
-    const int ctas_per_sm = plan.block_q <= 16 ? 3 : (plan.block_q <= 128 ? 2 : 1);
+    const int ctas_per_sm = plan.block_q <= 128 ? 2 : 1;
     int splits = ctas_per_sm * sm_count() / tiles;
     // few tiles (the qkv, o and down products): three quarters of that; fewer, longer splits
-    // leave the finishing kernel less to add (measured: -1.2 % of a batch-8 decode step)
+    // leave the finishing kernel less to add (measured: -1.2 % of a batch-8 decode step; six stages
+    // and two CTAs an SM for the 16-token tile instead of four and three: another -0.9 %)
     if (tiles < 100) splits = splits * 3 / 4;
     if (splits < 1) splits = 1;
     if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;  // at least 4 k-blocks a split
@@ -849,7 +850,7 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
     switch (plan.block_q) {
       // few stages a CTA, several CTAs an SM: while one CTA starts up or runs its epilogue
       // the others keep the weight stream going
-      case 16: rc = launch_swapped<16, 4>(map_row, map_col, p, grid, stream); break;    //  72 KB: 3 CTAs/SM
+      case 16: rc = launch_swapped<16, 6>(map_row, map_col, p, grid, stream); break;    // 108 KB: 2 CTAs/SM
       case 32: rc = launch_swapped<32, 4>(map_row, map_col, p, grid, stream); break;    //  80 KB: 2 CTAs/SM
       case 64: rc = launch_swapped<64, 4>(map_row, map_col, p, grid, stream); break;    //  96 KB: 2 CTAs/SM
       case 128: rc = launch_swapped<128, 3>(map_row, map_col, p, grid, stream); break;  //  96 KB: 2 CTAs/SM
