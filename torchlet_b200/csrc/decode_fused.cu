@@ -43,18 +43,21 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ partial, int sp
   const float* src = partial + (size_t)t * N + (size_t)h * d;
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float x1 = bias ? bias[h * d + i] : 0.f, x2 = bias ? bias[h * d + i + half] : 0.f;
-    int s = 0;
-    for (; s + 4 <= splits; s += 4) {  // eight loads in flight
-      const float a0 = src[s * plane + i], a1 = src[(s + 1) * plane + i], a2 = src[(s + 2) * plane + i],
-                  a3 = src[(s + 3) * plane + i];
-      const float b0 = src[s * plane + i + half], b1 = src[(s + 1) * plane + i + half],
-                  b2 = src[(s + 2) * plane + i + half], b3 = src[(s + 3) * plane + i + half];
-      x1 += a0; x1 += a1; x1 += a2; x1 += a3;
-      x2 += b0; x2 += b1; x2 += b2; x2 += b3;
-    }
-    for (; s < splits; ++s) {
-      x1 += src[s * plane + i];
-      x2 += src[s * plane + i + half];
+    // all splits of the pair are requested before the first is added (up to 16 at a time): the
+    // kernel's time is its trips to L2
+    for (int s0 = 0; s0 < splits; s0 += 16) {
+      float a[16], b[16];
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {
+        const bool live = s0 + s < splits;
+        a[s] = live ? src[(size_t)(s0 + s) * plane + i] : 0.f;
+        b[s] = live ? src[(size_t)(s0 + s) * plane + i + half] : 0.f;
+      }
+#pragma unroll
+      for (int s = 0; s < 16; ++s) {  // ascending splits; past the last one zeros are added
+        x1 += a[s];
+        x2 += b[s];
+      }
     }
     // the product's output is bfloat16 in the unfused path: round here too, so that both
     // paths give the same numbers
