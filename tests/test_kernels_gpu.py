@@ -428,6 +428,8 @@ def test_sampling_over_a_vocabulary_scanned_by_several_blocks():
     ([64, 0], [200, 129], 4, 2, 8, 100),
     ([0], [130], 16, 1, 128, None),
     ([0, 2500], [2, 3], 28, 4, 16, None),        # the second row tile of a CTA is empty
+    ([300], [260], 4, 4, 16, 1),                # a window of the token itself: the row tiles' key ranges only touch
+    ([37, 0], [500, 257], 8, 8, 32, 3),          # tiny window, one head a group: 128 tokens a row tile
     ([3000], [200], 14, 2, 16, 512),            # the row tiles start at different key tiles
     ([4000], [300], 28, 4, 64, None, (0, 299, 7)),   # a far key that decides the last token
     ([1100], [150], 12, 4, 16, 300, (0, 20, 830)),   # a key just inside the window of token 1120: 821 and later
