@@ -25,11 +25,26 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+# Qwen2.5-7B layer sizes (the reference arm reads them here, so that it imports nothing of this package)
 QWEN25_7B = {
     "architectures": ["Qwen2ForCausalLM"], "vocab_size": 152064, "hidden_size": 3584, "intermediate_size": 18944,
     "num_hidden_layers": 28, "num_attention_heads": 28, "num_key_value_heads": 4, "max_position_embeddings": 32768,
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
 }
+
+
+def build_model(cfg: dict, layers: int, seed: int):
+    from torchlet_b200.benchmarks.common import build_model as build
+
+    return build(cfg, layers, seed)
+
+
+def fill_context(runner, ids, context: int, seed: int) -> None:
+    from torchlet_b200.benchmarks.common import fill_context as fill
+
+    fill(runner, ids, context, seed)
+
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -109,46 +124,6 @@ def model_numbers(cfg: dict, layers: int):
         return gemm + attention + head
 
     return read_params, kv_bytes_per_token, prefill_flops
-
-
-def build_model(cfg: dict, layers: int, seed: int):
-    import torch
-
-    from torchlet_b200.config import Qwen2Config
-    from torchlet_b200.engine.loading import build_model as build
-    from torchlet_b200.weights import random_tensors
-
-    config = Qwen2Config.from_dict(dict(cfg, num_hidden_layers=layers))
-    tensors = random_tensors(config, seed, std=0.02, norm_std=0.0, dtype="bfloat16", device="cuda:0")
-    model = build(config, tensors, "bfloat16")
-    del tensors
-    torch.cuda.empty_cache()
-    return model
-
-
-def fill_context(runner, ids, context: int, seed: int):
-    """Give each request ``context`` cached tokens of seeded random keys and values."""
-    import torch
-
-    generator = torch.Generator(device="cuda:0").manual_seed(seed)
-    for pages in runner.storage.pages:
-        _randn_chunks(pages, generator)
-    for rid in ids:
-        runner.admit(rid)
-        if not runner.cache.extend(rid, context):
-            raise RuntimeError("the page pool is too small for the benchmark's context")
-        runner.cache.advance(rid, context)
-
-
-def _randn_chunks(pages, generator):
-    import torch
-
-    flat = pages.view(-1)
-    step = 1 << 27
-    for start in range(0, flat.numel(), step):
-        chunk = flat[start:start + step]
-        chunk.copy_(torch.randn(chunk.shape, generator=generator, device=pages.device, dtype=torch.float32).mul_(0.5))
-    return pages
 
 
 def time_decode(model, batch: int, context: int, steps: int, warmup: int, clock=None):

@@ -15,17 +15,11 @@ import argparse
 import torch
 
 from .. import ops
-from ..config import EngineConfig, Qwen2Config
+from ..config import EngineConfig
 from ..engine import ModelRunner, StepEntry
-from ..engine.loading import build_model
 from ..sampling import SampleSpec
-from ..weights import random_tensors
+from .common import QWEN25_7B, build_model, fill_context
 
-SIZES = {
-    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 152064, "hidden_size": 3584, "intermediate_size": 18944,
-    "num_attention_heads": 28, "num_key_value_heads": 4, "max_position_embeddings": 32768,
-    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
-}
 CLASSES = ("attention_mma", "finish_accum_norm", "finish_qkv_rope")
 
 
@@ -35,18 +29,8 @@ def time_step(model, batch: int, context: int, steps: int, warmup: int = 4) -> f
     config = EngineConfig(dtype="bfloat16", max_decode_slots=batch, kv_block_size=page, max_seq_len=context,
                           max_num_blocks=batch * (-(-context // page)) + 1, max_num_batched_tokens=2048)
     runner = ModelRunner(model, config)
-    generator = torch.Generator(device="cuda:0").manual_seed(17)
-    for pages in runner.storage.pages:
-        flat = pages.view(-1)
-        for start in range(0, flat.numel(), 1 << 27):
-            chunk = flat[start:start + (1 << 27)]
-            chunk.copy_(torch.randn(chunk.shape, generator=generator, device=pages.device).mul_(0.5))
     ids = [f"d{i}" for i in range(batch)]
-    for rid in ids:
-        runner.admit(rid)
-        if not runner.cache.extend(rid, context - steps - warmup):
-            raise RuntimeError("the page pool is too small")
-        runner.cache.advance(rid, context - steps - warmup)
+    fill_context(runner, ids, context - steps - warmup, seed=17)
     tokens = torch.randint(0, model.spec.vocab_size, (steps + warmup, batch)).tolist()
 
     def step(k):
@@ -75,10 +59,7 @@ def main(argv=None) -> int:
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--layers", type=int, default=28)
     args = parser.parse_args(argv)
-    config = Qwen2Config.from_dict(dict(SIZES, num_hidden_layers=args.layers))
-    tensors = random_tensors(config, 4, std=0.02, norm_std=0.0, dtype="bfloat16", device="cuda:0")
-    model = build_model(config, tensors, "bfloat16")
-    del tensors
+    model = build_model(QWEN25_7B, args.layers, seed=4)
     full = time_step(model, args.batch, args.context, args.steps)
     print(f"batch {args.batch}, context {args.context}, {args.layers} layers")
     print(f"{'full step':32s} {full:9.1f} us")
