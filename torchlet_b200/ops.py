@@ -255,6 +255,18 @@ def _release_workspace() -> None:
         workspace_holder.flush_pending()
 
 
+_plans: dict = {}  # (M, N, K) -> (workspace bytes, swapped orientation, splits): fixed for a process
+
+
+def _gemm_plan(M: int, N: int, K: int) -> tuple:
+    plan = _plans.get((M, N, K))
+    if plan is None:
+        swap, splits = ctypes.c_int(0), ctypes.c_int(0)
+        need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, ctypes.byref(swap), ctypes.byref(splits))
+        plan = _plans[(M, N, K)] = (need, bool(swap.value), splits.value)
+    return plan
+
+
 def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs=None) -> None:
     """out (+)= x @ w.T (+ bias) on the tcgen05 tensor cores; see csrc/gemm_tc.cu.
     ``cta_pairs``: for many tokens, True forces the kernel in which two CTAs share one 256-row
@@ -267,10 +279,9 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs=None) -> No
     want = torch.bfloat16 if epilogue in (EPI_STORE_BF16, EPI_SWIGLU_BF16) else torch.float32
     assert out.dtype == want and out.shape == (M, N // 2 if epilogue == EPI_SWIGLU_BF16 else N)
     assert bias is None or (bias.dtype == torch.float32 and bias.numel() == N)
-    splits = ctypes.c_int(0)
-    need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, None, ctypes.byref(splits))
+    need, _, splits = _gemm_plan(M, N, K)
     ws = _workspace(x.device, need) if need else None
-    kernels = 2 if need and splits.value > 1 else 1  # several splits: product + finishing pass
+    kernels = 2 if need and splits > 1 else 1  # several splits: product + finishing pass
     code = _fn("gemm_tc", "tl_gemm_tc")(
         x.data_ptr(), w.data_ptr(), _ptr(bias), out.data_ptr(), out.stride(0), epilogue, M, N, K, x.stride(0),
         w.stride(0), _ptr(ws), ws.numel() * 4 if ws is not None else 0, {None: 0, True: 2, False: 3}[cta_pairs], None,
@@ -286,9 +297,8 @@ def gemm_tc_deferred(x, w):
     _release_workspace()
     M, K = x.shape
     N = w.shape[0]
-    swap = ctypes.c_int(0)
-    need = _fn("gemm_tc", "tl_gemm_tc_plan")(M, N, K, ctypes.byref(swap), None)
-    if not swap.value:
+    need, swap, _ = _gemm_plan(M, N, K)
+    if not swap:
         return None
     ws = _workspace(x.device, need)
     splits = ctypes.c_int(0)
