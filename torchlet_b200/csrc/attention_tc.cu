@@ -186,8 +186,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int req = p.tile_req[blockIdx.x];
-  const int kvh = blockIdx.y;
+  // KV heads vary fastest over the grid: the CTAs of the row tiles that see the most keys (the
+  // caller lists those first) start first for ALL heads, and the short ones fill the end
+  const int kvh = blockIdx.x;
+  const int req = p.tile_req[blockIdx.y];
   const int g = p.nh / p.nkv;
   const int tok0 = p.req_indptr[req];
   const int q_len = p.req_indptr[req + 1] - tok0;
@@ -197,7 +199,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
 #pragma unroll
   for (int x = 0; x < QTILES; ++x) {
     RowTile& t = tile[x];
-    t.row_start = p.tile_row[blockIdx.x] + x * p.rows_per_tile;
+    t.row_start = p.tile_row[blockIdx.y] + x * p.rows_per_tile;
     t.row_end = min(q_len * g, t.row_start + p.rows_per_tile);
     t.begin = t.end = 0;
     if (t.row_start < t.row_end) {
@@ -527,7 +529,7 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
                     int nkv, int d, int page_size, int window, float scale, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (d != D || nkv <= 0 || nh % nkv || nh / nkv > ROWS || page_size < 8 || page_size > KEYS || KEYS % page_size ||
-      q_stride % 8 || out_stride % 8 || nkv > 65535 || !tile_req || !tile_row)
+      q_stride % 8 || out_stride % 8 || tiles > 65535 || !tile_req || !tile_row)
     return TL_ERR_UNSUPPORTED;
   CUtensorMap map_kv;
   if (!cached_map(&map_kv, pages, (uint64_t)num_pages * 2 * nkv * page_size, (uint32_t)page_size))
@@ -557,7 +559,7 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  tl::launch_kernel(attention_tc_kernel, dim3(tiles, nkv), THREADS, SMEM, stream, map_kv, p);
+  tl::launch_kernel(attention_tc_kernel, dim3(nkv, tiles), THREADS, SMEM, stream, map_kv, p);
   return TL_LAUNCH_CHECK();
 }
 
