@@ -88,13 +88,13 @@ def test_gemm_simt(dtype, out_dtype, M, N, K):
 @pytest.mark.parametrize("M, N, K, epilogue, bias", [
     (1, 256, 128, 3, False), (8, 384, 264, 0, True), (64, 520, 1024, 1, False), (5, 448, 96, 2, False),
     (100, 1000, 520, 3, True), (300, 512, 256, 0, True), (1000, 384, 512, 1, True), (700, 448, 96, 2, False),
-    (513, 1000, 72, 3, False), (257, 331, 200, 0, True), (450, 520, 264, 1, True),
+    (513, 1000, 72, 3, False), (257, 331, 200, 0, True), (450, 520, 264, 1, True), (200, 19200, 72, 2, False),
 ])
-@pytest.mark.parametrize("cta_pairs", [False, True])
+@pytest.mark.parametrize("cta_pairs", [None, False, True])
 def test_gemm_tc(M, N, K, epilogue, bias, cta_pairs):
     ops = _ops()
-    if cta_pairs and M <= 256:
-        pytest.skip("CTA pairs serve the many-token orientation only")
+    if cta_pairs is not None and M <= 128:
+        pytest.skip("few tokens run in the swapped orientation, which has one kernel")
     x, w = randn(M, K, dtype=torch.bfloat16, scale=0.5), randn(N, K, dtype=torch.bfloat16, scale=0.5, seed=1)
     b = randn(N, seed=2) if bias else None
     want = x.double() @ w.double().t() + (b.double() if bias else 0)

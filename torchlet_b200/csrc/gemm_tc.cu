@@ -19,7 +19,7 @@
 //       128 x block_q tiles with two accumulators in tensor memory, so that the epilogue of
 //       a tile overlaps the next tile's products; block_q is chosen for whole waves.
 //   gemm_tc_pair_kernel        the same with pairs of CTAs (cta_group::2) sharing a
-//       256 x block_q tile; it serves more than 384 tokens.
+//       256 x block_q tile; it runs where its tiles cover no more rows than 128-row tiles would.
 //
 // Reference counterparts: cuBLAS through nn.Linear (v10_triton_paged_gqa/layer/gqa.py:
 // 122-124, 84; model/qwen2_5.py:83-87) and the Triton GEMMs swiglu_kernel/down_kernel
@@ -805,11 +805,12 @@ int tl_gemm_tc_error() {
 
 // defer == 1 (swapped orientation only): leave the float32 partials [splits][M][N] in the
 // workspace for a fused finishing kernel of the caller; *splits_out gets their number.
-// With many tokens the CTA-pair kernel (cta_group::2) runs above 384 tokens, where its 256-row
-// tiles waste no more rows than 128-row tiles do (measured faster there on every product of the
-// model, by 3-14 %: 1,585 against 1,445 TFLOP/s on the gate/up product at 2,048 tokens, 100 against
-// 115 us at 448; slower by 1-7 % at 272 and 384), the single-CTA persistent kernel below that;
-// defer == 2 forces the pair kernel, defer == 3 the single-CTA kernel.
+// In the normal orientation the CTA-pair kernel (cta_group::2) runs where its 256-row tiles cover
+// no more rows than 128-row tiles would (129-256, 385-512, ... tokens) and from 1,024 tokens on;
+// measured faster there on every product of the model, by 3-14 %: 1,585 against 1,445 TFLOP/s on
+// the gate/up product at 2,048 tokens, 100 against 115 us at 448, 60 against 69 us at 200; slower
+// by 1-7 % at 272 and 384.  The single-CTA persistent kernel takes the rest; defer == 2 forces
+// the pair kernel, defer == 3 the single-CTA kernel.
 // out (+)= x[M, K] . w[N, K]^T.  x and w bfloat16 with K contiguous, ldx/ldw elements
 // between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
 // 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
@@ -835,7 +836,7 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   int rc;
   if (!plan.swap && defer == 1) return TL_ERR_UNSUPPORTED;
   if (plan.swap && defer >= 2) defer = 0;
-  if (!plan.swap && defer == 0 && M > 384) defer = 2;
+  if (!plan.swap && defer == 0 && (M >= 1024 || (M + 255) / 256 * 256 == (M + BLOCK_P - 1) / BLOCK_P * BLOCK_P)) defer = 2;
   if (plan.swap) {
     // one split writes its output directly; several (or a deferred finish) go through partials
     const bool partials = plan.splits > 1 || defer;

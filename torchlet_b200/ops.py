@@ -270,7 +270,7 @@ def _gemm_plan(M: int, N: int, K: int) -> tuple:
 def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs=None) -> None:
     """out (+)= x @ w.T (+ bias) on the tcgen05 tensor cores; see csrc/gemm_tc.cu.
     ``cta_pairs``: for many tokens, True forces the kernel in which two CTAs share one 256-row
-    MMA, False the single-CTA kernel; None lets the library choose (pairs above 384 tokens)."""
+    MMA, False the single-CTA kernel; None lets the library choose (pairs where their 256-row tiles cover no more rows than 128-row tiles)."""
     _need_cuda(x, w, out, bias)
     _release_workspace()
     M, K = x.shape
