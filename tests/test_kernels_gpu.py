@@ -89,6 +89,8 @@ def test_gemm_simt(dtype, out_dtype, M, N, K):
     (1, 256, 128, 3, False), (8, 384, 264, 0, True), (64, 520, 1024, 1, False), (5, 448, 96, 2, False),
     (100, 1000, 520, 3, True), (300, 512, 256, 0, True), (1000, 384, 512, 1, True), (700, 448, 96, 2, False),
     (513, 1000, 72, 3, False), (257, 331, 200, 0, True), (450, 520, 264, 1, True), (200, 19200, 72, 2, False),
+    # few wide tiles and a long K: the CTA-pair kernel splits K
+    (200, 520, 8192, 1, True), (256, 384, 4096, 0, True), (448, 640, 2048, 2, False), (512, 300, 1544, 3, False),
 ])
 @pytest.mark.parametrize("cta_pairs", [None, False, True])
 def test_gemm_tc(M, N, K, epilogue, bias, cta_pairs):
@@ -397,6 +399,29 @@ def test_fused_finishing_kernels_equal_the_separate_ones():
     assert (acc_a - acc_b).abs().max() <= 1e-5 * acc_a.abs().max()
     assert (out_a.float() - out_b.float()).abs().max() <= 1e-2 * out_a.float().abs().max()
     assert ops.gemm_tc_error() == 0
+
+
+def test_partial_sums_of_the_pair_kernel_feed_the_fused_finishing_kernel():
+    """Some hundred tokens, a narrow output and a long K: the CTA-pair kernel runs K splits and
+    leaves partial sums like the few-token kernel does."""
+    ops = _ops()
+    T, H, K = 200, 520, 8192
+    x = randn(T, K, dtype=torch.bfloat16, scale=0.5)
+    w = randn(H, K, dtype=torch.bfloat16, scale=0.1, seed=1)
+    _, swapped, planned = ops._gemm_plan(T, H, K)
+    assert not swapped and planned > 1, "these sizes are meant to run as K splits of the pair kernel"
+    partials, splits = ops.gemm_tc_deferred(x, w)
+    assert splits == planned
+    norm_w = randn(H, seed=4) * 0.1 + 1
+    acc = randn(T, H, seed=5)
+    want_acc = acc.double() + x.double() @ w.double().t()
+    out = torch.zeros(T, H, dtype=torch.bfloat16, device=DEV)
+    ops.finish_accum_norm(partials, splits, None, acc, norm_w, 1e-6, out)
+    torch.cuda.synchronize()
+    assert ops.gemm_tc_error() == 0
+    assert (acc.double() - want_acc).abs().max() <= 2e-5 * want_acc.abs().max()
+    want_out = want_acc * torch.rsqrt(want_acc.pow(2).mean(-1, keepdim=True) + 1e-6) * norm_w.double()
+    assert (out.double() - want_out).abs().max() <= 1e-2 * want_out.abs().max()
 
 
 def test_sampling_over_a_vocabulary_scanned_by_several_blocks():

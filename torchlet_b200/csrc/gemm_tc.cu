@@ -52,7 +52,8 @@ struct Params {
   void* out;
   long long ldo;
   int epilogue;
-  float* partial;  // swapped: [splits][M = cols][N = rows]
+  float* partial;  // [splits][M][N] partial sums (swapped: M = cols, N = rows); nullptr: direct output
+  int splits;      // pair kernel: K splits of every tile (1: the tile's epilogue writes the output)
   int ahead;       // stages of weight tiles requested before the wait on the preceding kernel
   // persistent kernel (normal orientation): tile width, stages, tile counts
   int block_q, stages, row_tiles, num_tiles;
@@ -519,15 +520,18 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
   tl::pdl_launch_dependents();
   tl::pdl_wait();
 
-  const int num_kb = p.k_blocks;
+  // A work item is one K split of one tile; the splits of a tile are num_tiles items apart
+  const int num_items = p.num_tiles * p.splits;
   if (warp == 0) {
     if (lane == 0) {
       int s = 0;
       uint32_t phase = 0;
-      for (int tile = pair; tile < p.num_tiles; tile += num_pairs) {
+      for (int item = pair; item < num_items; item += num_pairs) {
+        const int tile = item % p.num_tiles, kb0 = (item / p.num_tiles) * p.k_blocks_per_split;
+        const int kb1 = min(p.k_blocks, kb0 + p.k_blocks_per_split);
         const int row0 = (tile % p.row_tiles) * 256 + (int)rank * BLOCK_P;
         const int col0 = (tile / p.row_tiles) * p.block_q + (int)rank * half_q;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1);
           if (rank == 0) mbar_expect_tx(&full[s], 2 * stage_bytes);  // the bytes of both CTAs
           const uint32_t bar = peer_addr(&full[s], 0);
@@ -550,8 +554,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
       int s = 0, local = 0;
       uint32_t phase = 0;
       uint64_t a_desc = a_desc0, b_desc = b_desc0;
-      for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++local) {
+      for (int item = pair; item < num_items; item += num_pairs, ++local) {
         const int a = local & 1;
+        const int kb0 = (item / p.num_tiles) * p.k_blocks_per_split;
+        const int num_kb = min(p.k_blocks, kb0 + p.k_blocks_per_split) - kb0;
         mbar_wait(&tmem_empty[a], ((local >> 1) & 1) ^ 1, abort_flag, &g_error_word, 4);
         const uint32_t acc = tmem_base + a * ACC_COLS;
         for (int kb = 0; kb < num_kb; ++kb) {
@@ -579,9 +585,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
   } else {
     const int quarter = warp & 3;
     int local = 0;
-    for (int tile = pair; tile < p.num_tiles; tile += num_pairs, ++local) {
+    Params e = p;  // where and how an item's values go: with K splits, as float32 into the split's plane
+    if (p.partial != nullptr) {
+      e.epilogue = EPI_STORE_F32;
+      e.bias = nullptr;
+      e.ldo = p.cols;
+    }
+    for (int item = pair; item < num_items; item += num_pairs, ++local) {
       const int a = local & 1;
+      const int tile = item % p.num_tiles;
       const int row0 = (tile % p.row_tiles) * 256 + (int)rank * BLOCK_P, col0 = (tile / p.row_tiles) * p.block_q;
+      if (p.partial != nullptr) e.out = p.partial + (size_t)(item / p.num_tiles) * p.rows * p.cols;
       mbar_wait(&tmem_full[a], (local >> 1) & 1, abort_flag, &g_error_word, 3);
       fence_after_sync();
       const int row = row0 + quarter * 32 + lane;
@@ -595,7 +609,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
         tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
-        if (live) epilogue_chunk(p, row, col0 + c, v, 32);
+        if (live) epilogue_chunk(e, row, col0 + c, v, 32);
       }
       fence_before_sync();
       __syncwarp();
@@ -710,7 +724,8 @@ int pick_block_q_swapped(int M) {
 }
 
 struct Plan {
-  bool swap;
+  bool swap;   // swapped orientation (rows = weight rows)
+  bool pairs;  // normal orientation: the CTA-pair kernel
   int block_q, splits, k_blocks_per_split;
 };
 
@@ -733,20 +748,61 @@ long long best_width(int M, int N, bool pairs, int* width) {
   return best_cost;
 }
 
+// K splits of the CTA-pair kernel for ONE row tile (129-256 tokens) times a narrow output and a
+// long K, like the down projection: 14 tiles of width 256 leave 60 of 74 SM pairs idle, and one
+// pair needs 100 us for K = 18,944.  Measured on that product at 256 tokens: 100 / 67 / 57 / 50 /
+// 51 us with 1 / 2 / 3 / 4 / 5 splits (the swapped kernel: 63 us).  With two row tiles (512
+// tokens) or K = 3,584 no split count gained anything: all SMs together take in operands at
+// 8-10 TB/s from the L2, which is what those sizes run into either way.
+bool pair_split_plan(int M, int N, int K, int* width, int* splits_out, int* k_blocks_per_split) {
+  const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  const int tiles = (N + 255) / 256, pairs = sm_count() / 2;
+  if (M > 256 || k_blocks < 128 || 2 * tiles > pairs) return false;
+  int splits = pairs / tiles;
+  if (splits > 4) splits = 4;
+  *width = 256;
+  *k_blocks_per_split = (k_blocks + splits - 1) / splits;
+  *splits_out = (k_blocks + *k_blocks_per_split - 1) / *k_blocks_per_split;
+  return true;
+}
+
+// TORCHLET_B200_PAIR_SPLITS=0 switches the K splits of the pair kernel off (for measurements).
+bool pair_splits_enabled() {
+  static int value = -1;
+  if (value < 0) {
+    const char* v = getenv("TORCHLET_B200_PAIR_SPLITS");
+    value = (v && atoi(v) == 0) ? 0 : 1;
+  }
+  return value == 1;
+}
+
 Plan make_plan(int M, int N, int K) {
   Plan plan;
   const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+  // In the normal orientation the CTA-pair kernel runs where its 256-row tiles cover no more rows
+  // than 128-row tiles would (129-256, 385-512, ... tokens) and from 1,024 tokens on
+  const bool pair_rows = sm_count() % 2 == 0 && (M >= 1024 || (M + 255) / 256 * 256 == (M + BLOCK_P - 1) / BLOCK_P * BLOCK_P);
+  int pair_q = 256, pair_n = 1, pair_kb = k_blocks;
+  best_width(M, N, true, &pair_q);
+  const bool pair_splits = pair_rows && pair_splits_enabled() && pair_split_plan(M, N, K, &pair_q, &pair_n, &pair_kb);
   // Which orientation.  Up to 64 tokens the swapped kernel streams the weights at 5.5-6.2 TB/s.
   // Beyond that its wide column tiles lose (4.7 TB/s at 128 columns, 2.5 at 256), and the
-  // persistent kernel takes over where it has a tile for every SM, or, past 128 tokens, where
-  // one CTA's pass over K (about 200 GB/s a CTA) is shorter than the swapped kernel's time.
+  // persistent kernels take over where they have a tile for every SM, or, past 128 tokens, where
+  // one CTA's pass over K (about 200 GB/s a CTA) is shorter than the swapped kernel's time or
+  // the pair kernel splits K.
   plan.swap = M <= swap_max_tokens();
   if (plan.swap && M > 64 && swap_max_tokens() == 256) {
     const long long normal_tiles = (long long)((M + BLOCK_P - 1) / BLOCK_P) * ((N + 255) / 256);
     const double pass_us = (double)K * (BLOCK_P + 256) * 2 / 200e3;
     const double swapped_us = (double)N * K * 2 / 2.5e6 + 8.0;
-    if (normal_tiles >= sm_count() || (M > 128 && pass_us < swapped_us)) plan.swap = false;
+    if (normal_tiles >= sm_count() || (M > 128 && (pass_us < swapped_us || pair_splits)))
+      plan.swap = false;
   }
+  // Up to 256 tokens the pair kernel needs a tile for every pair (the gate/up product, the LM head)
+  // or its K splits; the o and qkv products are a little faster in the single-CTA kernel there
+  // (256 tokens: 20 against 23 us)
+  plan.pairs = !plan.swap && pair_rows &&
+               (M > 256 || pair_splits || (long long)((N + 255) / 256) >= sm_count() / 2);
   if (plan.swap) {
     plan.block_q = pick_block_q_swapped(M);
     const int tiles = ((N + BLOCK_P - 1) / BLOCK_P) * ((M + plan.block_q - 1) / plan.block_q);
@@ -760,6 +816,10 @@ Plan make_plan(int M, int N, int K) {
     if (splits > k_blocks / 4) splits = k_blocks / 4 > 0 ? k_blocks / 4 : 1;  // at least 4 k-blocks a split
     plan.k_blocks_per_split = (k_blocks + splits - 1) / splits;
     plan.splits = (k_blocks + plan.k_blocks_per_split - 1) / plan.k_blocks_per_split;
+  } else if (plan.pairs) {
+    plan.block_q = pair_q;
+    plan.splits = pair_n;
+    plan.k_blocks_per_split = pair_kb;
   } else {
     best_width(M, N, false, &plan.block_q);
     plan.splits = 1;
@@ -787,12 +847,12 @@ int launch_swapped(const CUtensorMap& map_row, const CUtensorMap& map_col, const
 extern "C" {
 
 // How a product of these sizes would run: *swap (0/1), *splits; returns the bytes of
-// float32 workspace it needs (0 for the normal orientation).
+// float32 workspace it needs (partial sums: the swapped orientation, K splits of the pair kernel).
 long long tl_gemm_tc_plan(int M, int N, int K, int* swap, int* splits) {
   const Plan plan = make_plan(M, N, K);
   if (swap) *swap = plan.swap ? 1 : 0;
   if (splits) *splits = plan.splits;
-  return plan.swap ? (long long)plan.splits * M * N * 4 : 0;
+  return (plan.swap || plan.splits > 1) ? (long long)plan.splits * M * N * 4 : 0;
 }
 
 // Reads and clears the error word that a bounded wait sets when it gives up.
@@ -803,14 +863,15 @@ int tl_gemm_tc_error() {
   return value;
 }
 
-// defer == 1 (swapped orientation only): leave the float32 partials [splits][M][N] in the
-// workspace for a fused finishing kernel of the caller; *splits_out gets their number.
+// defer == 1 (products that run with partial sums: *splits of tl_gemm_tc_plan > 1, or swapped):
+// leave the float32 partials [splits][M][N] in the workspace for a fused finishing kernel of the
+// caller; *splits_out gets their number.
 // In the normal orientation the CTA-pair kernel (cta_group::2) runs where its 256-row tiles cover
 // no more rows than 128-row tiles would (129-256, 385-512, ... tokens) and from 1,024 tokens on;
 // measured faster there on every product of the model, by 3-14 %: 1,585 against 1,445 TFLOP/s on
 // the gate/up product at 2,048 tokens, 100 against 115 us at 448, 60 against 69 us at 200; slower
 // by 1-7 % at 272 and 384.  The single-CTA persistent kernel takes the rest; defer == 2 forces
-// the pair kernel, defer == 3 the single-CTA kernel.
+// the pair kernel, defer == 3 the single-CTA kernel (both without K splits).
 // out (+)= x[M, K] . w[N, K]^T.  x and w bfloat16 with K contiguous, ldx/ldw elements
 // between rows (multiples of 8, bases 16-byte aligned).  epilogue: 0 bf16 out + bias,
 // 1 float32 out += result, 2 SwiGLU over 16-interleaved gate/up rows of w -> bf16
@@ -830,13 +891,15 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   p.ldo = ldo;
   p.epilogue = epilogue;
   p.partial = nullptr;
+  p.splits = 1;
   p.ahead = 8;  // all stages
   if (splits_out) *splits_out = 0;
   CUtensorMap map_row, map_col;
   int rc;
-  if (!plan.swap && defer == 1) return TL_ERR_UNSUPPORTED;
+  const bool pair_splits = !plan.swap && plan.pairs && plan.splits > 1 && defer <= 1;
+  if (!plan.swap && defer == 1 && !pair_splits) return TL_ERR_UNSUPPORTED;
   if (plan.swap && defer >= 2) defer = 0;
-  if (!plan.swap && defer == 0 && (M >= 1024 || (M + 255) / 256 * 256 == (M + BLOCK_P - 1) / BLOCK_P * BLOCK_P)) defer = 2;
+  const bool pairs = !plan.swap && sm_count() % 2 == 0 && (defer == 2 || (defer <= 1 && plan.pairs));
   if (plan.swap) {
     // one split writes its output directly; several (or a deferred finish) go through partials
     const bool partials = plan.splits > 1 || defer;
@@ -872,12 +935,22 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
   p.rows = M;
   p.cols = N;
   constexpr int SMEM_LIMIT = 227 * 1024;
-  if (defer == 2 && sm_count() % 2 == 0) {
+  if (pairs) {
     // CTA pairs: 256-row tiles, tile width a multiple of 32 chosen for whole waves of pairs
-    const int pairs = sm_count() / 2;
+    const int num_pairs = sm_count() / 2;
     const int row_tiles = (M + 255) / 256;
     int block_q = 256;
-    best_width(M, N, true, &block_q);
+    if (plan.pairs && defer <= 1)
+      block_q = plan.block_q;
+    else
+      best_width(M, N, true, &block_q);
+    if (pair_splits) {  // partial sums [splits][M][N], added by the finishing pass below or by the caller's
+      if ((long long)plan.splits * M * N * 4 > workspace_bytes) return TL_ERR_UNSUPPORTED;
+      p.partial = (float*)workspace;
+      p.splits = plan.splits;
+    } else {
+      p.k_blocks_per_split = p.k_blocks;
+    }
     if (!cached_map(&map_row, x, M, K, ldx, BLOCK_P) || !cached_map(&map_col, w, N, K, ldw, block_q / 2))
       return TL_ERR_UNSUPPORTED;
     p.block_q = block_q;
@@ -894,11 +967,24 @@ int tl_gemm_tc(const void* x, const void* w, const float* bias, void* out, long 
       if (err != cudaSuccess) return (int)err;
       configured = true;
     }
-    const int ctas = 2 * (p.num_tiles < pairs ? p.num_tiles : pairs);
+    const int items = p.num_tiles * p.splits;
+    const int ctas = 2 * (items < num_pairs ? items : num_pairs);
     tl::launch_kernel(gemm_tc_pair_kernel, dim3(ctas), THREADS, smem, stream, map_row, map_col, p);
+    rc = TL_LAUNCH_CHECK();
+    if (rc || !pair_splits) return rc;
+    if (defer == 1) {
+      if (splits_out) *splits_out = plan.splits;
+      return 0;
+    }
+    const int out_cols = epilogue == EPI_SWIGLU_BF16 ? N / 2 : N;
+    const long long total = (long long)M * out_cols;
+    tl::launch_kernel(splitk_finish_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, p.partial, plan.splits, M, N,
+                      bias, epilogue, out, ldo);
     return TL_LAUNCH_CHECK();
   }
+  p.k_blocks_per_split = p.k_blocks;
   int block_q = plan.block_q;
+  if (plan.pairs) best_width(M, N, false, &block_q);  // the single-CTA kernel was forced
   if (epilogue == EPI_SWIGLU_BF16) block_q = (block_q + 31) / 32 * 32 > 256 ? 256 : (block_q + 31) / 32 * 32;
   if (!cached_map(&map_row, x, M, K, ldx, BLOCK_P) || !cached_map(&map_col, w, N, K, ldw, block_q))
     return TL_ERR_UNSUPPORTED;

@@ -291,14 +291,14 @@ def gemm_tc(x, w, out, bias=None, epilogue=EPI_STORE_BF16, cta_pairs=None) -> No
 
 def gemm_tc_deferred(x, w):
     """The product x @ w.T left as float32 partial sums ``[splits, M, N]`` for a fused
-    finishing kernel.  Returns (partials, splits), or None when the sizes run in the
-    orientation that writes its output directly (many tokens)."""
+    finishing kernel.  Returns (partials, splits), or None when the sizes run in a
+    kernel that writes its output directly (many tokens, no K splits)."""
     _need_cuda(x, w)
     _release_workspace()
     M, K = x.shape
     N = w.shape[0]
-    need, swap, _ = _gemm_plan(M, N, K)
-    if not swap:
+    need, swap, planned = _gemm_plan(M, N, K)
+    if not swap and planned <= 1:
         return None
     ws = _workspace(x.device, need)
     splits = ctypes.c_int(0)
