@@ -144,6 +144,55 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, int m, int n0, c
   }
 }
 
+// out[row][col0 .. col0 + width) += the accumulator row at ``taddr`` (+ bias), width a multiple of
+// 32 and everything 16-byte aligned (the caller checks; warp-uniform).  The old values of a
+// chunk are requested one chunk ahead, before the wait for the chunk's tensor-memory read: a
+// tile's epilogue is eight dependent trips to memory otherwise, which shows wherever no next
+// tile hides it (a CTA's last tile; products of few tiles).  All lanes call it (the tensor-memory
+// read is warp-wide); ``live`` lanes touch memory.
+__device__ __forceinline__ void accumulate_row(const Params& p, int row, int col0, int width, uint32_t taddr, bool live) {
+  float* o = (float*)p.out + (size_t)row * p.ldo + col0;
+  float4 cur[8];
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) cur[j] = reinterpret_cast<const float4*>(o)[j];
+  }
+#pragma unroll 1
+  for (int c = 0; c < width; c += 32) {
+    float4 nxt[8];
+    const bool more = c + 32 < width;
+    if (live && more) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) nxt[j] = reinterpret_cast<const float4*>(o + c + 32)[j];
+    }
+    uint32_t r[32];
+    tmem_ld_32(taddr + c, r);
+    tmem_ld_wait();
+    if (live) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int n = col0 + c + 4 * j;
+        cur[j].x += __uint_as_float(r[4 * j]) + (p.bias ? p.bias[n] : 0.f);
+        cur[j].y += __uint_as_float(r[4 * j + 1]) + (p.bias ? p.bias[n + 1] : 0.f);
+        cur[j].z += __uint_as_float(r[4 * j + 2]) + (p.bias ? p.bias[n + 2] : 0.f);
+        cur[j].w += __uint_as_float(r[4 * j + 3]) + (p.bias ? p.bias[n + 3] : 0.f);
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) reinterpret_cast<float4*>(o + c)[j] = cur[j];
+    }
+    if (more) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) cur[j] = nxt[j];
+    }
+  }
+}
+
+// Whether accumulate_row serves a tile of this width at these columns.
+__device__ __forceinline__ bool accumulate_row_serves(const Params& p, int col0, int width) {
+  return p.epilogue == EPI_ACCUM_F32 && width % 32 == 0 && col0 + width <= p.cols && p.ldo % 4 == 0 && col0 % 4 == 0 &&
+         (reinterpret_cast<uintptr_t>(p.out) & 15) == 0;
+}
+
 template <int BLOCK_Q, int STAGES>
 __global__ void __launch_bounds__(THREADS)
 gemm_tc_swapped_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_constant__ CUtensorMap map_col,
@@ -430,8 +479,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_row, const __g
       const int row = row0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + a * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       const bool live = row < p.rows;
+      const bool whole = accumulate_row_serves(p, col0, p.block_q);
+      if (whole) accumulate_row(p, row, col0, p.block_q, taddr, live);
 #pragma unroll 1
-      for (int c = 0; c < p.block_q; c += 32) {
+      for (int c = whole ? p.block_q : 0; c < p.block_q; c += 32) {
         float v[32];
         const int cols = min(32, p.block_q - c);
         if (cols == 32) {
@@ -601,8 +652,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_row, const __grid_co
       const int row = row0 + quarter * 32 + lane;
       const uint32_t taddr = tmem_base + a * ACC_COLS + ((uint32_t)(quarter * 32) << 16);
       const bool live = row < p.rows;
+      const bool whole = accumulate_row_serves(e, col0, p.block_q);
+      if (whole) accumulate_row(e, row, col0, p.block_q, taddr, live);
 #pragma unroll 1
-      for (int c = 0; c < p.block_q; c += 32) {
+      for (int c = whole ? p.block_q : 0; c < p.block_q; c += 32) {
         float v[32];
         uint32_t r[32];
         tmem_ld_32(taddr + c, r);
