@@ -53,7 +53,7 @@ def test_logits_at_benchmark_layer_sizes(case, dtype):
 
 
 def test_a_long_portion_in_bfloat16_against_the_32_bit_path(case):
-    """640 tokens in one step: the products run on the CTA-pair kernel (512 tokens and more),
+    """704 tokens in one step: the products run on the CTA-pair kernel (three 256-row tiles),
     the attention over several key tiles with two row tiles a CTA.  The 32-bit path of the
     engine (checked against the plain implementation above and in the other tests) is the
     reference here: the plain implementation would need minutes for this on the CPU."""
@@ -62,13 +62,13 @@ def test_a_long_portion_in_bfloat16_against_the_32_bit_path(case):
     from torchlet_b200.engine.loading import build_model
 
     weights, _, _ = case
-    ids = tiny_configs.make_ids(CONFIG, 640, seed=23)
-    want_rows = [0, 1, 127, 128, 300, 511, 512, 639]
+    ids = tiny_configs.make_ids(CONFIG, 704, seed=23)
+    want_rows = [0, 1, 127, 128, 300, 511, 512, 639, 703]
     got = {}
     for dtype in ("float32", "bfloat16"):
         model = build_model(Qwen2Config.from_dict(dict(CONFIG, max_position_embeddings=1024)), weights, dtype)
-        runner = ModelRunner(model, EngineConfig(dtype=dtype, max_decode_slots=2, kv_block_size=16, max_num_blocks=48,
-                                                 max_seq_len=704, max_num_batched_tokens=640, cuda_graph=False))
+        runner = ModelRunner(model, EngineConfig(dtype=dtype, max_decode_slots=2, kv_block_size=16, max_num_blocks=50,
+                                                 max_seq_len=768, max_num_batched_tokens=704, cuda_graph=False))
         runner.admit("p")
         got[dtype] = runner.step([StepEntry("p", ids, want_rows)]).cpu().clone()
         # eight more tokens one by one, from the cache the long step left
@@ -80,7 +80,7 @@ def test_a_long_portion_in_bfloat16_against_the_32_bit_path(case):
         runner.cache.check()
         del runner, model
         torch.cuda.empty_cache()
-    harness.assert_close(got["bfloat16"], got["float32"], "bfloat16", "640 tokens and 8 decoded")
+    harness.assert_close(got["bfloat16"], got["float32"], "bfloat16", "704 tokens and 8 decoded")
     from torchlet_b200 import ops
 
     ops.raise_on_wait_errors()
