@@ -217,6 +217,11 @@ def test_attention_generic(case, dtype):
 @pytest.mark.parametrize("case", [c for c in ATTENTION_CASES if c[4] in (64, 128)] + [
     ([0], [257], 8, 8, 64, 32, None),
     ([5, 1000, 0, 17], [3, 1, 64, 1], 28, 4, 128, 16, None),
+    # pages that the decode tiles' TMA boxes cannot take (larger than a key tile; not a multiple of 8): cp.async
+    ([300, 40, 0], [1, 1, 5], 4, 2, 64, 128, None),
+    ([33, 9], [1, 1], 6, 2, 128, 4, None),
+    # a long context without key splits: three stages of key tiles
+    ([1500, 2], [1, 1], 8, 2, 128, 32, 700),
 ])
 def test_attention_mma(case):
     ops = _ops()

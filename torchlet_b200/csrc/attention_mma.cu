@@ -18,15 +18,28 @@
 //           blockIdx.z; each split then writes its (max, sum, accumulator) to a workspace
 //           and a second kernel merges the splits.
 //
+// Decode tiles (ROWS16) with a page size that is a multiple of 8 and divides 64 get their keys
+// and values by TMA instead: one box of page_size x 64 elements per page, K or V and half of the
+// head, one lane of warp 0 a box, into the 128-byte-swizzled layout that ldmatrix reads without
+// bank conflicts; the warps wait on an mbarrier per stage (bounded; a wait that gives up leaves a
+// code that tl_attention_mma_error() returns).  The gather with cp.async costs every thread some
+// hundred instructions a tile, which is what the 16-row tiles spent most of their time on.
+//
 // Reference counterparts: forward_ragged_attention_kernel and
 // forward_slot_attention_decode_kernel (v10_triton_paged_gqa/kernel/gqa.py:5-228), which
 // use the same numerics: float32 scores scaled by head_dim^-0.5, float32 max/sum/acc, the
 // weights cast to the value dtype before P.V, acc / sum at the end.
 #include <math.h>
 
+#include <mutex>
+#include <unordered_map>
+
 #include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace {
+
+__device__ int g_error_word = 0;
 
 constexpr int WARPS = 4;
 constexpr int THREADS = WARPS * 32;
@@ -91,6 +104,35 @@ template <int D> __device__ __forceinline__ __nv_bfloat16* tile_at(__nv_bfloat16
   return tile + row * D + ((chunk ^ (row & 7)) << 3);
 }
 
+// The same for a [64][D] key or value tile: with TMA the tile is D / 64 slabs of [64 rows][64
+// elements], each row 128 bytes with its 16-byte chunks xor-ed by the row (the 128-byte swizzle
+// of the copy); for D = 64 the two layouts are one.
+template <int D, bool TMA> __device__ __forceinline__ __nv_bfloat16* kv_at(__nv_bfloat16* tile, int row, int chunk) {
+  if constexpr (TMA) return tile + (chunk >> 3) * (BLOCK_N * 64) + row * 64 + (((chunk & 7) ^ (row & 7)) << 3);
+  return tile_at<D>(tile, row, chunk);
+}
+
+// Requests the K and V pages of keys [tile * 64, tile * 64 + 64) of one KV head by TMA into a
+// stage (warp 0, one lane a box).  Pages past the request's last key or past the table are
+// read from page 0 (always there; their keys are masked and their values meet P = 0).
+template <int D>
+__device__ __forceinline__ void tma_kv_tile(const CUtensorMap* map, const Params& p, const int* table, int kvh, int tile,
+                                            int hi_key, __nv_bfloat16* stage, uint64_t* full, int lane) {
+  constexpr int SLABS = D / 64;
+  const int pages_per_tile = BLOCK_N / p.page_size;
+  const int boxes = pages_per_tile * 2 * SLABS;  // at most 8 * 2 * 2 = 32
+  if (lane == 0) tc::mbar_expect_tx(full, 2 * BLOCK_N * D * 2);
+  __syncwarp();
+  if (lane < boxes) {
+    const int slab = lane % SLABS, is_v = (lane / SLABS) & 1, page_i = lane / (2 * SLABS);
+    const int index = tile * pages_per_tile + page_i;
+    const bool wanted = index < p.table_width && index * p.page_size <= hi_key;
+    const int page = wanted ? table[index] : 0;
+    __nv_bfloat16* dst = stage + is_v * (BLOCK_N * D) + slab * (BLOCK_N * 64) + page_i * p.page_size * 64;
+    tc::tma_load_2d(dst, map, full, slab * 64, ((page * 2 + is_v) * p.nkv + kvh) * p.page_size);
+  }
+}
+
 // Gathers the K and V rows of keys [key0, key0 + 64) of one KV head into shared memory.
 // Rows outside [lo_key, hi_key] are zero-filled instead of read.
 template <int D>
@@ -130,9 +172,13 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
   }
 }
 
-template <int D, bool ROWS16>
-__global__ void __launch_bounds__(THREADS, 3)
-attention_mma_kernel(const Params p) {
+// STAGES: key/value tiles in shared memory; 2, or 3 with the TMA loader where the grid leaves
+// room for only two CTAs an SM anyway.
+template <int D, bool ROWS16, bool TMA, int STAGES>
+__global__ void __launch_bounds__(THREADS, STAGES == 2 ? 3 : 2)
+attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) {
+  static_assert(!TMA || ROWS16, "the TMA loader serves the 16-row tiles");
+  static_assert(STAGES == 2 || TMA, "more than two stages need the TMA loader");
   // The wait on the preceding kernel comes further down: the step's metadata is written
   // by a host copy before any kernel of the step, and key/value tiles that lie wholly
   // before the step's own tokens were written by earlier steps, so both may be read first.
@@ -147,10 +193,16 @@ attention_mma_kernel(const Params p) {
   // second stage's space; once every warp holds its Q fragments in registers that space
   // is free for the key/value tiles, so three CTAs fit an SM.
   extern __shared__ __align__(128) uint8_t smem_raw[];
-  __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(smem_raw);
+  // the swizzle of the TMA copies works on address bits: the stages start on a 1024-byte boundary
+  uint8_t* smem_base = TMA ? reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023)
+                           : smem_raw;
+  __nv_bfloat16* kv = reinterpret_cast<__nv_bfloat16*>(smem_base);
   // 64-row tiles: Q [64][D] inside stage 1.  16-row tiles (decode): Q [16][D] after the
   // stages, so that both stages can be filled before the wait on the preceding kernel.
-  __nv_bfloat16* qs = ROWS16 ? kv + 2 * 2 * BLOCK_N * D : kv + 2 * BLOCK_N * D;
+  __nv_bfloat16* qs = ROWS16 ? kv + STAGES * 2 * BLOCK_N * D : kv + 2 * BLOCK_N * D;
+  // TMA: one "tile has landed" barrier a stage and the block's "a wait gave up" word, after Q
+  uint64_t* full = reinterpret_cast<uint64_t*>(qs + BLOCK_M * D);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(full + STAGES);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int req = p.tile_req ? p.tile_req[blockIdx.x] : blockIdx.x;
@@ -170,6 +222,15 @@ attention_mma_kernel(const Params p) {
     tl::pdl_wait();
     return;
   }
+  if constexpr (TMA) {
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < STAGES; ++i) tc::mbar_init(&full[i], 1);
+      *abort_flag = 0;
+      tc::mbar_fence_init();
+      tc::prefetch_tensormap(&map_kv);
+    }
+    __syncthreads();
+  }
   const int first_tok = row_start / g, last_tok = (row_end - 1) / g;
   const int hi_key = before + last_tok;  // last key any row of the tile may see
   int lo_key = 0;
@@ -188,10 +249,14 @@ attention_mma_kernel(const Params p) {
   const int num_tiles = max(0, tile_end - tile_begin);
   int issued = 0;  // tiles requested so far, counted from tile_begin
   if constexpr (ROWS16) {
-    while (issued < min(2, num_tiles) && (tile_begin + issued) * BLOCK_N + BLOCK_N - 1 < before) {
+    while (issued < min(STAGES, num_tiles) && (tile_begin + issued) * BLOCK_N + BLOCK_N - 1 < before) {
       __nv_bfloat16* stage = kv + issued * STAGE_ELEMS;
-      load_kv_tile<D>(p, table, kvh, (tile_begin + issued) * BLOCK_N, lo_key, hi_key, stage, stage + BLOCK_N * D);
-      cp_async_commit();
+      if constexpr (TMA) {
+        if (warp == 0) tma_kv_tile<D>(&map_kv, p, table, kvh, tile_begin + issued, hi_key, stage, &full[issued], lane);
+      } else {
+        load_kv_tile<D>(p, table, kvh, (tile_begin + issued) * BLOCK_N, lo_key, hi_key, stage, stage + BLOCK_N * D);
+        cp_async_commit();
+      }
       ++issued;
     }
   }
@@ -209,7 +274,11 @@ attention_mma_kernel(const Params p) {
   }
   cp_async_commit();
   if (issued == 0 && num_tiles > 0) {
-    load_kv_tile<D>(p, table, kvh, tile_begin * BLOCK_N, lo_key, hi_key, kv, kv + BLOCK_N * D);
+    if constexpr (TMA) {
+      if (warp == 0) tma_kv_tile<D>(&map_kv, p, table, kvh, tile_begin, hi_key, kv, &full[0], lane);
+    } else {
+      load_kv_tile<D>(p, table, kvh, tile_begin * BLOCK_N, lo_key, hi_key, kv, kv + BLOCK_N * D);
+    }
     issued = 1;
   }
   cp_async_commit();
@@ -248,17 +317,29 @@ attention_mma_kernel(const Params p) {
 
   for (int tile = tile_begin; tile < tile_end; ++tile) {
     const int index = tile - tile_begin;
-    const int stage = index & 1;
+    const int stage = index % STAGES;
     __nv_bfloat16* ks_tile = kv + stage * STAGE_ELEMS;
     __nv_bfloat16* vs_tile = ks_tile + BLOCK_N * D;
-    if (issued == index + 1 && index + 1 < num_tiles) {  // request the next tile into the other stage
+    if constexpr (TMA) {
+      // keep STAGES tiles requested: the stage of tile index - 1 is free since the barrier that ended it
+      while (issued < min(num_tiles, index + STAGES)) {
+        const int s_next = issued % STAGES;
+        if (warp == 0)
+          tma_kv_tile<D>(&map_kv, p, table, kvh, tile_begin + issued, hi_key, kv + s_next * STAGE_ELEMS, &full[s_next], lane);
+        ++issued;
+      }
+    } else if (issued == index + 1 && index + 1 < num_tiles) {  // request the next tile into the other stage
       __nv_bfloat16* next = kv + (stage ^ 1) * STAGE_ELEMS;
       load_kv_tile<D>(p, table, kvh, (tile + 1) * BLOCK_N, lo_key, hi_key, next, next + BLOCK_N * D);
       ++issued;
     }
-    cp_async_commit();
-    cp_async_wait<1>();  // everything but the request just made has landed: this tile is here
-    __syncthreads();
+    if constexpr (TMA) {
+      tc::mbar_wait(&full[stage], (index / STAGES) & 1, abort_flag, &g_error_word, 1);  // this tile is here
+    } else {
+      cp_async_commit();
+      cp_async_wait<1>();  // everything but the request just made has landed: this tile is here
+      __syncthreads();
+    }
 
     const int key_base = tile * BLOCK_N + (ROWS16 ? warp * 16 : 0);  // first key this warp multiplies
     const int key_row0 = ROWS16 ? warp * 16 : 0;                      // its row inside the tile
@@ -274,7 +355,7 @@ attention_mma_kernel(const Params p) {
         unsigned b[4];
         const int r = key_row0 + nb * 16 + (lane & 7) + (lane >> 4) * 8;
         const int c = 2 * ks + ((lane >> 3) & 1);
-        ldmatrix_x4(b, tile_at<D>(ks_tile, r, c));
+        ldmatrix_x4(b, kv_at<D, TMA>(ks_tile, r, c));
         mma_16816(s[2 * nb], q_frag[ks], b[0], b[1]);
         mma_16816(s[2 * nb + 1], q_frag[ks], b[2], b[3]);
       }
@@ -343,7 +424,7 @@ attention_mma_kernel(const Params p) {
         unsigned b[4];
         const int r = key_row0 + kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8;
         const int c = 2 * nb + (lane >> 4);
-        ldmatrix_x4_trans(b, tile_at<D>(vs_tile, r, c));
+        ldmatrix_x4_trans(b, kv_at<D, TMA>(vs_tile, r, c));
         mma_16816(o_acc[2 * nb], p_frag[kk], b[0], b[1]);
         mma_16816(o_acc[2 * nb + 1], p_frag[kk], b[2], b[3]);
       }
@@ -459,15 +540,46 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
   out[(size_t)token * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / total[0]);
 }
 
-template <int D, bool ROWS16>
-int launch(const Params& p, int tiles, cudaStream_t stream) {
+// Tensor maps of cache layers [rows][D] with boxes of page_size x 64 elements, by base address.
+struct MapKey {
+  const void* base;
+  uint64_t rows;
+  uint32_t cols, box_rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
+};
+struct MapKeyHash {
+  size_t operator()(const MapKey& k) const {
+    return ((reinterpret_cast<size_t>(k.base) * 1000003u ^ k.rows) * 1000003u ^ k.cols) * 1000003u ^ k.box_rows;
+  }
+};
+bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {
+  static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
+  static std::mutex lock;
+  const MapKey key{base, rows, cols, box_rows};
+  std::lock_guard<std::mutex> guard(lock);
+  auto it = cache.find(key);
+  if (it == cache.end()) {
+    CUtensorMap map;
+    if (!tc_host::make_map_bf16(&map, base, rows, cols, cols, box_rows)) return false;
+    if (cache.size() > 1024) cache.clear();
+    it = cache.emplace(key, map).first;
+  }
+  *out = it->second;
+  return true;
+}
+
+template <int D, bool ROWS16, bool TMA, int STAGES>
+int launch(const CUtensorMap& map_kv, const Params& p, int tiles, cudaStream_t stream) {
   constexpr int BLOCK_M = ROWS16 ? 16 : 64;
-  constexpr int SMEM = (2 * 2 * BLOCK_N * D + (ROWS16 ? BLOCK_M * D : 0)) * 2;
+  // 16-row tiles: STAGES key/value stages and Q behind them; 64-row tiles: two stages, Q inside the second.
+  // TMA: room to start the stages on a 1024-byte boundary, the barriers and the abort word
+  constexpr int SMEM = ((ROWS16 ? STAGES : 2) * 2 * BLOCK_N * D + (ROWS16 ? BLOCK_M * D : 0)) * 2 + (TMA ? 1024 + 64 : 0);
   static_assert(BLOCK_M * D <= 2 * BLOCK_N * D, "the Q rows fit one stage");
   static_assert(!ROWS16 || WARPS * 16 * (D + 2) * 4 <= 2 * 2 * BLOCK_N * D * 2, "merge buffer fits the stages");
+  static_assert((STAGES == 2 ? 3 : 2) * (SMEM + 1024) <= 227 * 1024, "three CTAs an SM with two stages, two with three");
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_mma_kernel<D, ROWS16>,
+    cudaError_t err = cudaFuncSetAttribute(attention_mma_kernel<D, ROWS16, TMA, STAGES>,
                                            cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
     if (err != cudaSuccess) return (int)err;
     configured = true;
@@ -478,9 +590,48 @@ int launch(const Params& p, int tiles, cudaStream_t stream) {
   // grids are launched WITHOUT overlap: CTAs that start while the small kernel before them
   // still occupies the SMs are placed unevenly, and a bandwidth-bound grid's time is set by
   // its most loaded SM (measured: batch 64 decode lost 9% with an overlapped launch).
-  tl::launch_kernel_opt(ROWS16 && tiles <= p.overlap_max_tiles, attention_mma_kernel<D, ROWS16>, grid, THREADS, SMEM,
-                        stream, p);
+  tl::launch_kernel_opt(ROWS16 && tiles <= p.overlap_max_tiles, attention_mma_kernel<D, ROWS16, TMA, STAGES>, grid, THREADS,
+                        SMEM, stream, map_kv, p);
   return TL_LAUNCH_CHECK();
+}
+
+// TORCHLET_B200_DECODE_TMA=0: the 16-row tiles gather their keys and values with cp.async (for measurements).
+bool decode_tma_enabled() {
+  static int value = -1;
+  if (value < 0) {
+    const char* v = getenv("TORCHLET_B200_DECODE_TMA");
+    value = (v && atoi(v) == 0) ? 0 : 1;
+  }
+  return value == 1;
+}
+
+// TORCHLET_B200_DECODE_STAGES=2|3 forces the stage count of the TMA loader (for measurements).
+int decode_stages() {
+  static int value = -1;
+  if (value < 0) {
+    const char* v = getenv("TORCHLET_B200_DECODE_STAGES");
+    value = v ? atoi(v) : 0;
+    if (value != 2 && value != 3) value = 0;
+  }
+  return value;
+}
+
+template <int D>
+int launch_for(const Params& p, long long num_pages, int tiles, bool rows16, cudaStream_t stream) {
+  CUtensorMap map_kv;
+  memset(&map_kv, 0, sizeof(map_kv));
+  if (!rows16) return launch<D, false, false, 2>(map_kv, p, tiles, stream);
+  const bool tma = decode_tma_enabled() && num_pages > 0 && p.page_size >= 8 && p.page_size % 8 == 0 &&
+                   BLOCK_N % p.page_size == 0 &&
+                   cached_map(&map_kv, p.pages, (uint64_t)num_pages * 2 * p.nkv * p.page_size, D, (uint32_t)p.page_size);
+  if (!tma) return launch<D, true, false, 2>(map_kv, p, tiles, stream);
+  // Without key splits (large batches) every CTA walks its request's whole context, and a third
+  // stage keeps more of it requested (batch 128 at 2,048 tokens: 7.15 -> 6.68 ms a decode step;
+  // batch 64: equal).  With splits the grid is sized for three CTAs an SM, which three stages do
+  // not leave room for (batch 8 to 32: 5-14 % slower).
+  if (decode_stages() == 3 || (decode_stages() == 0 && p.splits == 1))
+    return launch<D, true, true, 3>(map_kv, p, tiles, stream);
+  return launch<D, true, true, 2>(map_kv, p, tiles, stream);
 }
 
 }  // namespace
@@ -492,9 +643,19 @@ long long tl_attention_mma_workspace(int tokens, int nh, int d, int splits) {
   return splits > 1 ? (long long)tokens * nh * splits * (d + 2) * 4 : 0;
 }
 
+// Reads and clears the code that a bounded wait left when it gave up (0: none).
+int tl_attention_mma_error() {
+  int value = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&value, g_error_word, sizeof(int)) != cudaSuccess) return -1;
+  if (value) cudaMemcpyToSymbol(g_error_word, &zero, sizeof(int));
+  return value;
+}
+
 // rows16 != 0: tiles of 16 packed rows with the keys split over the warps and over
 // ``splits`` CTAs (decode); else tiles of 64 packed rows (prompt portions), splits = 1.
-int tl_attention_mma(const void* q, long long q_stride, const void* pages, const int* block_table, int table_width,
+// pages: one cache layer [num_pages][2][nkv][page_size][d].
+int tl_attention_mma(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
+                     int table_width,
                      const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
                      int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
                      int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
@@ -528,11 +689,8 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, const
   p.window = window;
   p.splits = splits;
   p.scale_log2 = scale * 1.4426950408889634f;
-  int rc;
-  if (d == 128)
-    rc = rows16 ? launch<128, true>(p, tiles, stream) : launch<128, false>(p, tiles, stream);
-  else
-    rc = rows16 ? launch<64, true>(p, tiles, stream) : launch<64, false>(p, tiles, stream);
+  const int rc = d == 128 ? launch_for<128>(p, num_pages, tiles, rows16 != 0, stream)
+                           : launch_for<64>(p, num_pages, tiles, rows16 != 0, stream);
   if (rc || splits == 1) return rc;
   const int items = tokens * nh;
   if (d == 128)

@@ -53,9 +53,10 @@ _SIGNATURES = {
         "tl_gemm_tc_error": [],
     },
     "attention_mma": {
-        "tl_attention_mma": [c_void_p, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                             c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                             c_int, c_void_p, c_longlong, c_void_p],
+        "tl_attention_mma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                             c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+                             c_int, c_int, c_void_p, c_longlong, c_void_p],
+        "tl_attention_mma_error": [],
     },
     "decode_fused": {
         "tl_finish_qkv_rope": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
@@ -348,9 +349,10 @@ def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile
     need = tokens * nh * splits * (d + 2) * 4 if splits > 1 else 0
     ws = _workspace(("attention", qkv.device), need) if need else None
     code = _fn("attention_mma", "tl_attention_mma")(
-        qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), block_table.data_ptr(), block_table.shape[1],
-        req_indptr.data_ptr(), kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles, out.data_ptr(),
-        out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale), 1 if rows16 else 0, splits,
+        qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),
+        block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles,
+        out.data_ptr(), out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale),
+        1 if rows16 else 0, splits,
         _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
     _check(code, "attention_mma", 2 if splits > 1 else 1)
 
@@ -377,6 +379,11 @@ def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_
     _check(code, "attention_tc")
 
 
+def attention_mma_error() -> int:
+    """0, or the code a bounded wait of the decode attention's TMA loader left.  Reading clears it."""
+    return _fn("attention_mma", "tl_attention_mma_error")()
+
+
 def attention_tc_error() -> int:
     """0, or the code a bounded wait in the tcgen05 attention kernel left when it gave up."""
     return _fn("attention_tc", "tl_attention_tc_error")()
@@ -387,7 +394,8 @@ def raise_on_wait_errors() -> None:
     (the kernel then ran to its end with whatever it had, so its output is not to be used).
     Only libraries that are loaded are asked.  The read is a blocking copy on the default
     stream, so it sees every kernel launched before it."""
-    for library, read in (("gemm_tc", gemm_tc_error), ("attention_tc", attention_tc_error)):
+    for library, read in (("gemm_tc", gemm_tc_error), ("attention_tc", attention_tc_error),
+                          ("attention_mma", attention_mma_error)):
         if any(name in _functions for name in _SIGNATURES[library]):
             code = read()
             if code:
