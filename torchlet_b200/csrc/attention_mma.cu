@@ -629,8 +629,16 @@ int launch_for(const Params& p, long long num_pages, int tiles, bool rows16, cud
   // stage keeps more of it requested (batch 128 at 2,048 tokens: 7.15 -> 6.68 ms a decode step;
   // batch 64: equal).  With splits the grid is sized for three CTAs an SM, which three stages do
   // not leave room for (batch 8 to 32: 5-14 % slower).
-  if (decode_stages() == 3 || (decode_stages() == 0 && p.splits == 1))
-    return launch<D, true, true, 3>(map_kv, p, tiles, stream);
+  // A grid of at most two CTAs an SM (batch 1 and 2) has the room as well: batch 1 -0.8 %.
+  static int sms = 0;
+  if (sms <= 0) {
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0)
+      sms = 148;
+  }
+  const bool roomy = p.splits == 1 || (long long)tiles * p.nkv * p.splits <= 2ll * sms;
+  if (decode_stages() == 3 || (decode_stages() == 0 && roomy)) return launch<D, true, true, 3>(map_kv, p, tiles, stream);
   return launch<D, true, true, 2>(map_kv, p, tiles, stream);
 }
 
