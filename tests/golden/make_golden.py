@@ -22,10 +22,6 @@ sys.path.insert(0, str(HERE.parent))
 import tiny_configs  # noqa: E402
 
 
-def checksum(weights: dict) -> float:
-    return float(sum(w.double().abs().sum() for w in weights.values()))
-
-
 def dense_logits(cfg, weights, ids):
     from torchlet.v00_full_recompute.model.qwen2_5 import Qwen2ForCausalLM
 
@@ -75,15 +71,17 @@ def main():
     for name in ("A", "B"):
         cfg, init = tiny_configs.ALL[name]
         cfg = {k: v for k, v in cfg.items() if k not in ("use_sliding_window", "sliding_window", "max_window_layers")}
-        weights = tiny_configs.make_weights(cfg, **init)
+        weights = {k: v.float() for k, v in tiny_configs.make_weights(cfg, dtype=torch.bfloat16, **init).items()}
         ids = tiny_configs.make_ids(cfg, 45, seed=11)
         store[f"{name}_ids"] = np.array(ids, dtype=np.int64)
-        store[f"{name}_checksum"] = np.array(checksum(weights))
+        for key, value in weights.items():  # bfloat16-representable: the upper 16 bits say it all
+            store[f"{name}_weight:{key}"] = (value.contiguous().view(torch.int32) >> 16).to(torch.int16).numpy()
         store[f"{name}_dense"] = dense_logits(cfg, weights, ids).numpy()
         store[f"{name}_paged_from_30"] = paged_logits(cfg, weights, ids, 30).numpy()
     np.savez_compressed(HERE / "reference_logits.npz", **store)
     for key, value in store.items():
-        print(key, value.shape)
+        if "_weight:" not in key:
+            print(key, value.shape)
 
 
 if __name__ == "__main__":

@@ -32,7 +32,7 @@ def plain_logits(name: str, length: int, seed: int, schedule=None):
 
 
 def make_runner(name: str, dtype: str, num_pages: int = 200, slots: int = 4, page_size=None, budget: int = 2048,
-                schedule=None, max_seq_len=None):
+                schedule=None, max_seq_len=None, cuda_graph: bool = False):
     from torchlet_b200.config import EngineConfig, Qwen2Config
     from torchlet_b200.engine import ModelRunner
     from torchlet_b200.engine.loading import build_model
@@ -45,7 +45,7 @@ def make_runner(name: str, dtype: str, num_pages: int = 200, slots: int = 4, pag
     page = page_size or tiny_configs.ALL[name][1]["page_size"]
     engine = EngineConfig(dtype=dtype, max_decode_slots=slots, kv_block_size=page, max_num_blocks=num_pages,
                           max_seq_len=max_seq_len or cfg["max_position_embeddings"], max_num_batched_tokens=budget,
-                          cuda_graph=False)
+                          cuda_graph=cuda_graph)
     return ModelRunner(model, engine)
 
 
@@ -95,7 +95,49 @@ def changing_cuts(length: int, seed: int = 0):
 
 
 def assert_close(got, want, dtype: str, what: str = ""):
-    scale = want.abs().max().item()
-    err = (got - want).abs().max().item()
-    assert err <= TOLERANCE[dtype] * scale, f"{what}: max |diff| {err:.3e} > {TOLERANCE[dtype]:.1e} * {scale:.3f}"
-    assert torch.isfinite(got).all()
+    """Row by row (one row = the logits of one position): the largest difference of a row against
+    the largest |logit| of THAT row, so that an error confined to one position or one request
+    cannot hide under the largest logit of the whole comparison."""
+    assert got.shape == want.shape, f"{what}: shapes {tuple(got.shape)} and {tuple(want.shape)}"
+    assert torch.isfinite(got).all(), f"{what}: not finite"
+    got, want = got.reshape(-1, got.shape[-1]).double(), want.reshape(-1, want.shape[-1]).double()
+    err = (got - want).abs().amax(dim=1)
+    scale = want.abs().amax(dim=1)
+    ratio = err / scale
+    worst = int(ratio.argmax())
+    assert ratio[worst] <= TOLERANCE[dtype], (
+        f"{what}: row {worst}: max |diff| {err[worst]:.3e} > {TOLERANCE[dtype]:.1e} * {scale[worst]:.3f}")
+
+
+class KernelCalls:
+    """Counts the calls of the kernel wrappers in ``torchlet_b200.ops`` while it is active, so
+    that a test can say which kernels its comparison went through."""
+
+    NAMES = ("attention_mma", "attention_tc", "attention_generic", "gemm_tc", "gemm_tc_deferred", "gemm_simt",
+             "finish_qkv_rope", "finish_accum_norm")
+
+    def __enter__(self):
+        from torchlet_b200 import ops
+
+        self.counts = {name: 0 for name in self.NAMES}
+        self.decode_splits = []
+        self._saved = {name: getattr(ops, name) for name in self.NAMES}
+        for name, fn in self._saved.items():
+            setattr(ops, name, self._wrap(name, fn))
+        return self
+
+    def _wrap(self, name, fn):
+        def counted(*args, **kwargs):
+            self.counts[name] += 1
+            if name == "attention_mma" and kwargs.get("rows16"):
+                self.decode_splits.append(kwargs.get("splits", 1))
+            return fn(*args, **kwargs)
+
+        return counted
+
+    def __exit__(self, *exc):
+        from torchlet_b200 import ops
+
+        for name, fn in self._saved.items():
+            setattr(ops, name, fn)
+        return False

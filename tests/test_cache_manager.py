@@ -163,3 +163,27 @@ def test_decode_pass_matches_single_calls():
         assert small.extend(rid, 8)
         small.advance(rid, 8)
     assert small.begin_decode(["x", "y"]) == 0  # two pages, both taken
+
+
+def test_a_model_without_paged_history_needs_no_pages():
+    """Every mixer keeps fixed-size state only: no group, no pool; slots and lengths still work."""
+    manager = CacheManager([], page_size=16, max_slots=2, max_seq_len=128)
+    slot = manager.admit("a")
+    assert manager.extend("a", 5) and manager.can_extend("a", 128)
+    manager.advance("a", 5)
+    assert manager.num_tokens("a") == 5
+    before, slots = manager.begin_decode(["a"])
+    assert before.tolist() == [5] and slots.tolist() == [slot]
+    manager.end_decode(["a"])
+    assert manager.num_tokens("a") == 6
+    manager.admit("b")
+    with pytest.raises(CacheError):
+        manager.admit("c")  # slots are what runs out
+    with pytest.raises(CacheError):
+        manager.extend("a", 129)  # the length limit still holds
+    manager.check()
+    assert manager.finish("a") == slot
+    assert manager.admit("c") == slot  # the slot is used again
+    manager.reset()
+    manager.check()
+    assert manager.num_free_slots == 2

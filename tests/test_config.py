@@ -60,7 +60,7 @@ def test_model_spec_layers_follow_the_config():
     mixer = spec.layers[0].mixer.params
     assert (mixer["num_heads"], mixer["num_kv_heads"], mixer["head_dim"]) == (3, 1, 32)
     assert mixer["positions"].params["theta"] == 1e6
-    assert spec.layers[0].mixer_norm.params["eps"] == 1e-5 and not spec.tie_word_embeddings
+    assert spec.layers[0].norm("mixer_norm").part.params["eps"] == 1e-5 and not spec.tie_word_embeddings
     assert cfg.to_dict()["architectures"] == ["Qwen2ForCausalLM"]
     assert Qwen2Config.from_dict(cfg.to_dict()) == cfg
 
@@ -88,3 +88,40 @@ def test_engine_config():
         EngineConfig(dtype="fp8")
     with pytest.raises(ValueError):
         EngineConfig(max_seq_len=200).resolve(100)
+
+
+def test_tensor_names_come_from_the_layer_description():
+    """The architecture-neutral model spells no tensor name: another architecture names its
+    parts' tensors as its checkpoint does, and may give a block one norm or three."""
+    import dataclasses
+
+    from torchlet_b200.config import NormSlot, PartSpec
+    from torchlet_b200.parts import BLOCKS, Block, LayeredModel, expected_tensors
+
+    spec = Qwen2Config.from_dict(tiny_configs.TINY_A).model_spec()
+    names = {t.name for t in expected_tensors(spec)}
+    assert "model.layers.1.self_attn.q_proj.weight" in names and "model.layers.0.mlp.down_proj.weight" in names
+    assert "model.layers.0.input_layernorm.weight" in names
+
+    @BLOCKS.register("toy_one_norm")
+    class OneNorm(Block):
+        norm_roles = ("shared",)
+
+    norm = spec.layers[0].norms[0].part
+    renamed = tuple(
+        dataclasses.replace(layer, prefix=f"h.{i}.", block="toy_one_norm", norms=(NormSlot("shared", norm, "ln_1."),),
+                            mixer_prefix="attn.", feed_forward_prefix="ffn.")
+        for i, layer in enumerate(spec.layers))
+    other = dataclasses.replace(spec, layers=renamed, embedding_name="wte.weight", final_norm_prefix="ln_f.",
+                                lm_head_name="head.weight")
+    names = {t.name for t in expected_tensors(other)}
+    assert {"wte.weight", "h.0.ln_1.weight", "h.1.attn.k_proj.bias", "h.0.ffn.up_proj.weight", "ln_f.weight"} <= names
+    assert not any("self_attn" in n or "mlp" in n or "layernorm" in n for n in names)
+    model = LayeredModel(other)
+    assert list(model.blocks[0].norms) == ["shared"]
+    # an arrangement that lacks a norm it needs is refused when the model is put together
+    broken = dataclasses.replace(other, layers=(dataclasses.replace(renamed[0], norms=()),) + renamed[1:])
+    with pytest.raises(ValueError, match="shared"):
+        LayeredModel(broken)
+    with pytest.raises(KeyError, match="mixer_norm"):
+        renamed[0].norm("mixer_norm")

@@ -1,0 +1,122 @@
+"""Failure paths of the engine loop, on the CPU, with a stand-in for the step function: a step
+that raises ends every live request with that error, gives every page and slot back, and leaves
+the engine able to serve the next request (the reference's failure path:
+v10_triton_paged_gqa/engine.py:204-217, scheduler.py:294-332)."""
+import pytest
+
+from torchlet_b200.cache import CacheManager, GroupSpec
+from torchlet_b200.config import EngineConfig
+from torchlet_b200.engine.engine import Engine
+from torchlet_b200.engine.scheduler import Request, RequestState
+from torchlet_b200.sampling import SamplingParams
+
+
+class _Tokens(list):
+    def tolist(self):
+        return list(self)
+
+    def numel(self):
+        return len(self)
+
+
+class _Result:
+    def __init__(self, tokens):
+        self.tokens = _Tokens(tokens) if tokens else None
+        self.logits = None
+
+
+class _Event:
+    def synchronize(self):
+        pass
+
+
+class FailingRunner:
+    """The runner's interface as the engine uses it.  'Samples' 1000 + the request's length;
+    raises in the step numbered ``fail_at``."""
+
+    def __init__(self, fail_at=None, num_pages=64, page=4, slots=3):
+        self.cache = CacheManager([GroupSpec(1, 8, None, (0,), num_pages)], page, slots, 256)
+        self.fail_at = fail_at
+        self.steps_run = 0
+
+    def admit(self, rid):
+        return self.cache.admit(rid)
+
+    def finish(self, rid):
+        self.cache.finish(rid)
+
+    def reserve(self, rid, new_len):
+        return self.cache.extend(rid, new_len)
+
+    def can_feed_previous(self, entries):
+        return False
+
+    def tokens_to_host(self, result):
+        return result.tokens, _Event()
+
+    def run(self, entries, feed_previous=False):
+        if self.steps_run == self.fail_at:
+            self.steps_run += 1
+            raise RuntimeError("the step function failed")
+        self.steps_run += 1
+        tokens = []
+        for e in entries:
+            before = self.cache.num_tokens(e.request_id)
+            assert self.cache.extend(e.request_id, before + len(e.tokens))
+            self.cache.advance(e.request_id, before + len(e.tokens))
+            if e.sample is not None:
+                tokens.append(1000 + before + len(e.tokens))
+        return _Result(tokens)
+
+
+def _engine(runner):
+    config = EngineConfig(max_decode_slots=3, kv_block_size=4, max_seq_len=256, max_num_batched_tokens=16, cuda_graph=False)
+    return Engine(None, config, runner=runner)
+
+
+def _requests():
+    return [Request(list(range(n)), SamplingParams(max_new_tokens=5)) for n in (20, 3, 9, 30)]
+
+
+@pytest.mark.parametrize("loop", ["run", "step"])
+@pytest.mark.parametrize("fail_at", [0, 2, 5])
+def test_a_failed_step_fails_every_request_and_the_engine_serves_again(loop, fail_at):
+    runner = FailingRunner(fail_at=fail_at)
+    engine = _engine(runner)
+    requests = _requests()
+    engine.add_requests(requests)
+    with pytest.raises(RuntimeError, match="step function failed"):
+        if loop == "run":
+            engine.run()
+        else:
+            while engine.scheduler.has_work():
+                engine.step()
+    # every request that had not finished ends with the error; nothing is held any more
+    assert all(r.state is RequestState.FINISHED for r in requests)
+    unfinished = [r for r in requests if len(r.output_tokens) < 5]
+    assert unfinished and all(isinstance(r.error, RuntimeError) for r in unfinished)
+    assert not engine.scheduler.has_work() and engine.scheduler.drain_finished() == []
+    runner.cache.check()
+    assert runner.cache.live_requests() == [] and runner.cache.num_free_slots == 3
+    assert runner.cache.pools[0].num_free == runner.cache.pools[0].num_pages - 1
+    # a fresh request is served afterwards
+    fresh = Request(list(range(11)), SamplingParams(max_new_tokens=4))
+    engine.generate([fresh])
+    assert fresh.error is None and fresh.output_tokens == [1011, 1012, 1013, 1014]
+    runner.cache.check()
+
+
+def test_without_a_failure_both_loops_agree():
+    outputs = []
+    for loop in ("run", "step"):
+        engine = _engine(FailingRunner())
+        requests = _requests()
+        engine.add_requests(requests)
+        if loop == "run":
+            engine.run()
+        else:
+            while engine.scheduler.has_work():
+                engine.step()
+        assert all(r.error is None for r in requests)
+        outputs.append([r.output_tokens for r in requests])
+    assert outputs[0] == outputs[1]

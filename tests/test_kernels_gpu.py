@@ -493,3 +493,128 @@ def test_attention_tc(case):
         v_spike = x["dense"][spike[0]][2][spike[2], 0].float()
         assert (want[token, :d] - v_spike).abs().max() < 0.05 * v_spike.abs().max()
         assert (out[token, :d].float().cpu() - v_spike).abs().max() < 0.05 * v_spike.abs().max()
+
+
+# -------------------------------------------- what a kernel must leave alone, or must not be hurt by
+def _poison_unowned(x, before, q_lens, page, passed=None):
+    """NaN into every cache slot that no request of the step owns: page 0, pages outside every
+    table (also those a window has passed: ``passed[i]`` pages of request i), and the slots of a
+    request's last page past its last key."""
+    pages = x["pages"]
+    owned = torch.zeros(pages.shape[0], pages.shape[3], dtype=torch.bool)
+    for i, (b, q) in enumerate(zip(before, q_lens)):
+        for pos in range((passed[i] if passed else 0) * page, b + q):
+            owned[int(x["table"][i, pos // page]), pos % page] = True
+    assert not owned[0].any()
+    mask = (~owned).to(pages.device)[:, None, None, :, None].expand_as(pages)
+    pages[mask] = float("nan")
+    return int((~owned).sum())
+
+
+def test_decode_attention_beside_prompt_rows_touches_only_its_own():
+    """A mixed step: two decoding requests beside two prompt portions.  The decode launch (keys
+    split over CTAs, merged by a second kernel) gets ``out`` and the shared workspace full of NaN
+    and a cache whose every unowned slot is NaN: it must write the two decode rows, correctly,
+    and nothing else."""
+    ops = _ops()
+    nh, nkv, d, page = 14, 2, 128, 16
+    before, q_lens = [700, 0, 333, 40], [1, 90, 1, 37]
+    x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=9)
+    assert _poison_unowned(x, before, q_lens, page) > 0
+    scale = 0.37 / math.sqrt(d)
+    want = plain_attention(x["dense"], before, nh, nkv, None, scale)
+    to = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    decode_rows = [0, 91]
+    for splits in (1, 4, 8):
+        ops._workspace(("attention", x["qkv"].device), 1 << 20).fill_(float("nan"))
+        out = torch.full((x["T"], nh * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+        ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to([0, 2]), None, 2, out, x["T"],
+                          nh, nkv, d, page, None, scale, rows16=True, splits=splits)
+        host = out.float().cpu()
+        others = [r for r in range(x["T"]) if r not in decode_rows]
+        assert torch.isnan(host[others]).all(), f"splits {splits}: rows of other requests were written"
+        assert torch.isfinite(host[decode_rows]).all(), f"splits {splits}: NaN from unowned memory reached the output"
+        assert (host[decode_rows] - want[decode_rows]).abs().max() <= 1.5e-2 * want.abs().max()
+    # the workspace is sized by the decode requests, not by the step's tokens
+    assert ops._workspaces[("attention", x["qkv"].device)].numel() * 4 < x["T"] * nh * 8 * (d + 2) * 4
+
+
+@pytest.mark.parametrize("d, nh, nkv, page, window", [(128, 6, 2, 16, None), (128, 8, 2, 32, 150), (64, 14, 2, 16, None),
+                                                      (64, 4, 4, 8, 70)])
+def test_attention_kernels_are_not_hurt_by_nan_in_slots_they_do_not_own(d, nh, nkv, page, window):
+    """Pages are never cleared when they change hands.  Prompt portions and decode tokens over a
+    cache whose unowned slots (page 0, other pages, the tail of each last page) hold NaN."""
+    ops = _ops()
+    before, q_lens = [0, 170, 45, 301], [150, 1, 75, 1]
+    group = nh // nkv
+    x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=11)
+    passed = [0] * len(q_lens)
+    if window is not None:  # pages a window has passed are given back: their table entries name page 0
+        for i, b in enumerate(before):
+            passed[i] = max(0, (b + 1 - window)) // page
+            x["table"][i, :passed[i]] = 0
+    _poison_unowned(x, before, q_lens, page, passed)
+    scale = 0.37 / math.sqrt(d)
+    want = plain_attention(x["dense"], before, nh, nkv, window, scale)
+    to = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    out = torch.zeros(x["T"], nh * d, device=DEV, dtype=torch.bfloat16)
+    use_tc = ops.attention_tc_supported(d, group, page)
+    rows = ops.attention_tc_rows(group) if use_tc else 64
+    tile_req, tile_row = [], []
+    for r in (0, 2):
+        for start in range(0, q_lens[r] * group, rows):
+            tile_req.append(r)
+            tile_row.append(start)
+    ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to([1, 3]), None, 2, out, x["T"], nh,
+                      nkv, d, page, window, scale, rows16=True, splits=3)
+    if use_tc:
+        ops.attention_tc(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(tile_req), to(tile_row),
+                         len(tile_req), out, nh, nkv, d, page, window, scale)
+    else:
+        ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(tile_req), to(tile_row),
+                          len(tile_req), out, x["T"], nh, nkv, d, page, window, scale, rows16=False)
+    host = out.float().cpu()
+    assert torch.isfinite(host).all(), "NaN from a slot no request owns reached an output"
+    assert (host - want).abs().max() <= 1.5e-2 * want.abs().max()
+    ops.raise_on_wait_errors()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_store_kv_writes_keys_and_values_unrotated(dtype):
+    ops = _ops()
+    nh, nkv, d, page, T = 4, 2, 32, 8, 11
+    g = torch.Generator().manual_seed(4)
+    qkv = torch.randn(T, (nh + 2 * nkv) * d, generator=g).to(dtype).to(DEV)
+    positions = torch.tensor([0, 1, 7, 8, 9, 30, 31, 32, 33, 5, 6], dtype=torch.int32, device=DEV)
+    token_req = torch.tensor([0] * 9 + [1] * 2, dtype=torch.int32, device=DEV)
+    table = torch.tensor([[3, 1, 4, 6, 2], [5, 0, 0, 0, 0]], dtype=torch.int32, device=DEV)
+    pages = torch.zeros(8, 2, nkv, page, d, dtype=dtype, device=DEV)
+    kept = qkv.clone()
+    ops.store_kv(qkv, positions, token_req, table, pages, nh, nkv, d, page)
+    assert torch.equal(qkv, kept)  # q is left as it is
+    for t in range(T):
+        pos, req = int(positions[t]), int(token_req[t])
+        page_id = int(table[req, pos // page])
+        assert torch.equal(pages[page_id, 0, :, pos % page].reshape(-1), kept[t, nh * d:(nh + nkv) * d])
+        assert torch.equal(pages[page_id, 1, :, pos % page].reshape(-1), kept[t, (nh + nkv) * d:])
+    assert pages[0].abs().max() == 0 and pages[7].abs().max() == 0
+
+
+def test_a_bounded_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """The error path of the tensor-core kernels' waits, without a fault or a hang: a block waits
+    on a barrier nobody arrives at, gives up after 2^16 cycles, records its code and returns.  The
+    host reads the code and raises; the code is cleared, and the next product is right."""
+    ops = _ops()
+    ops.raise_on_wait_errors()  # nothing pending from earlier tests
+    x, w = randn(8, 256, dtype=torch.bfloat16), randn(128, 256, dtype=torch.bfloat16)
+    out = torch.empty(8, 128, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_tc(x, w, out)  # loads the library, as the engine would have
+    ops.wait_selftest(code=99)
+    torch.cuda.synchronize()  # returns: the kernel ended by itself
+    with pytest.raises(ops.KernelError, match="code 99"):
+        ops.raise_on_wait_errors()
+    ops.raise_on_wait_errors()  # reading cleared the word
+    assert ops.gemm_tc_error() == 0
+    ops.gemm_tc(x, w, out)
+    want = x.float() @ w.float().t()
+    assert (out.float() - want).abs().max() <= 1e-2 * want.abs().max()

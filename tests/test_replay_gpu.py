@@ -11,17 +11,40 @@ from harness import assert_close, changing_cuts, make_runner, plain_logits, repl
 
 pytestmark = pytest.mark.gpu
 
-CASES = [(name, dtype) for name in ("A", "B") for dtype in ("float32", "bfloat16")]
-LENGTHS = {"A": (5, 17, 33, 90), "B": (1, 9, 24, 40, 131)}
+# A and B: the two tiny configurations (SIMT kernels in both dtypes: head_dim 16 and 32).  D and E
+# (head_dim 128 with 3 heads a KV head, head_dim 64 with 7): in bfloat16 every cut below runs
+# through the tensor-core attention kernels, the tcgen05 products and the fused finishing kernels.
+CASES = [(name, dtype) for name in ("A", "B") for dtype in ("float32", "bfloat16")] + [
+    ("D", "bfloat16"), ("E", "bfloat16"), ("E", "float32")]
+TENSOR_CORE = {("D", "bfloat16"), ("E", "bfloat16")}
+LENGTHS = {"A": (5, 17, 33, 90), "B": (1, 9, 24, 40, 131), "D": (3, 40, 200), "E": (1, 70, 259)}
+
+
+def check_kernels(calls, name, dtype, prompt: bool, decode: bool):
+    """The comparison went through the kernels it is meant to cover."""
+    if (name, dtype) not in TENSOR_CORE:
+        return
+    c = calls.counts
+    assert c["attention_generic"] == 0 and c["gemm_simt"] == 0, c
+    assert c["gemm_tc"] + c["gemm_tc_deferred"] > 0, c
+    if prompt:
+        assert c["attention_tc"] + c["attention_mma"] - len(calls.decode_splits) > 0, c
+        if harness.tiny_configs.head_dim(harness.tiny_configs.ALL[name][0]) == 128:
+            assert c["attention_tc"] > 0, c
+    if decode:
+        assert calls.decode_splits, c
+        assert c["finish_qkv_rope"] > 0 and c["finish_accum_norm"] > 0, c
 
 
 @pytest.mark.parametrize("name, dtype", CASES)
 def test_whole_requests_alone(name, dtype):
     runner = make_runner(name, dtype)
-    for i, length in enumerate(LENGTHS[name]):
-        ids, want = plain_logits(name, length, 100 + i)
-        got = replay(runner, f"r{i}", ids, [length])
-        assert_close(got, want, dtype, f"{name} whole {length}")
+    with harness.KernelCalls() as calls:
+        for i, length in enumerate(LENGTHS[name]):
+            ids, want = plain_logits(name, length, 100 + i)
+            got = replay(runner, f"r{i}", ids, [length])
+            assert_close(got, want, dtype, f"{name} whole {length}")
+    check_kernels(calls, name, dtype, prompt=True, decode=False)
 
 
 @pytest.mark.parametrize("name, dtype", CASES)
@@ -29,8 +52,12 @@ def test_last_32_tokens_one_by_one(name, dtype):
     runner = make_runner(name, dtype)
     length = LENGTHS[name][-1]
     ids, want = plain_logits(name, length, 7)
-    got = replay(runner, "r", ids, [length - 32] + [1] * 32)
+    with harness.KernelCalls() as calls:
+        got = replay(runner, "r", ids, [length - 32] + [1] * 32)
     assert_close(got, want, dtype, f"{name} decode tail")
+    check_kernels(calls, name, dtype, prompt=True, decode=True)
+    if (name, dtype) in TENSOR_CORE:
+        assert max(calls.decode_splits) > 1, "the keys of a decode step were never split over CTAs"
     whole = replay(runner, "w", ids, [length])
     if dtype == "float32":  # the 32-bit kernels are cut-invariant to the bit
         assert torch.equal(got, whole)
@@ -39,13 +66,15 @@ def test_last_32_tokens_one_by_one(name, dtype):
 @pytest.mark.parametrize("name, dtype", CASES)
 def test_portions_of_changing_size(name, dtype):
     runner = make_runner(name, dtype)
-    length = 150
+    length = 150 if (name, dtype) not in TENSOR_CORE else 330
     ids, want = plain_logits(name, length, 8)
-    for seed in (0, 5):
-        cuts = changing_cuts(length, seed)
-        assert min(cuts) <= 2
-        got = replay(runner, f"c{seed}", ids, cuts)
-        assert_close(got, want, dtype, f"{name} cuts {cuts[:6]}")
+    with harness.KernelCalls() as calls:
+        for seed in (0, 5):
+            cuts = changing_cuts(length, seed)
+            assert min(cuts) <= 2
+            got = replay(runner, f"c{seed}", ids, cuts)
+            assert_close(got, want, dtype, f"{name} cuts {cuts[:6]}")
+    check_kernels(calls, name, dtype, prompt=True, decode=True)
 
 
 @pytest.mark.parametrize("name, dtype", CASES)
@@ -56,54 +85,62 @@ def test_mixed_batches_with_pages_used_again(name, dtype):
 
     page = harness.tiny_configs.ALL[name][1]["page_size"]
     lengths = [70, 45, 96, 33, 61, 80, 52]
+    if (name, dtype) in TENSOR_CORE:  # long enough that decode steps split their keys over CTAs
+        lengths = [4 * n for n in lengths]
     plain = [plain_logits(name, n, 200 + i) for i, n in enumerate(lengths)]
     # pool: enough for about 2.5 of the longest requests, so pages change hands
-    num_pages = 1 + sum(-(-n // page) for n in sorted(lengths)[-2:]) + 3 * -(-40 // page)
+    num_pages = 1 + sum(-(-n // page) for n in sorted(lengths)[-2:]) + 3 * -(-lengths[3] // page)
     runner = make_runner(name, dtype, num_pages=num_pages, slots=4)
     progress = {}  # index -> tokens fed
     collected = {i: [] for i in range(len(lengths))}
     waiting = list(range(len(lengths)))
-    step = 0
+    step = mixed_steps = 0
     pages_seen = {}
-    while waiting or progress:
-        # admit while a slot is free and the pool could hold the request
-        while waiting and len(progress) < 4:
-            i = waiting[0]
-            need = -(-lengths[i] // page)
-            in_use = sum(-(-lengths[j] // page) for j in progress)
-            if in_use + need > num_pages - 1:
-                break
-            waiting.pop(0)
-            runner.admit(f"m{i}")
-            progress[i] = 0
-        entries, meta = [], []
-        for order, i in enumerate(sorted(progress)):
-            ids = plain[i][0]
-            done = progress[i]
-            left = lengths[i] - done
-            # the first live request decodes one token at a time once past half; the
-            # others take portions of changing size
-            size = 1 if (done > lengths[i] // 2) else [11, 2, 19, 5, 3][(step + order) % 5]
-            size = min(size, left)
-            entries.append(StepEntry(f"m{i}", ids[done:done + size], list(range(size))))
-            meta.append((i, size))
-        assert any(s == 1 for _, s in meta) or step < 12
-        logits = runner.step(entries).cpu()
-        row = 0
-        for i, size in meta:
-            collected[i].append(logits[row:row + size].clone())
-            row += size
-            progress[i] += size
-            for p in runner.cache.table(f"m{i}", 0):
-                pages_seen.setdefault(p, set()).add(i)
-            if progress[i] == lengths[i]:
-                runner.finish(f"m{i}")
-                del progress[i]
-        runner.cache.check()
-        step += 1
+    with harness.KernelCalls() as calls:
+        while waiting or progress:
+            # admit while a slot is free and the pool could hold the request
+            while waiting and len(progress) < 4:
+                i = waiting[0]
+                need = -(-lengths[i] // page)
+                in_use = sum(-(-lengths[j] // page) for j in progress)
+                if in_use + need > num_pages - 1:
+                    break
+                waiting.pop(0)
+                runner.admit(f"m{i}")
+                progress[i] = 0
+            entries, meta = [], []
+            for order, i in enumerate(sorted(progress)):
+                ids = plain[i][0]
+                done = progress[i]
+                left = lengths[i] - done
+                # a live request decodes one token at a time once past half (at most 24 such steps
+                # where the requests are long); the others take portions of changing size
+                decoding = done > lengths[i] // 2 and (lengths[i] <= 100 or done <= lengths[i] // 2 + 24)
+                size = 1 if decoding else [11, 2, 19, 5, 3][(step + order) % 5] * (1 if lengths[i] <= 100 else 3)
+                size = min(size, left)
+                entries.append(StepEntry(f"m{i}", ids[done:done + size], list(range(size))))
+                meta.append((i, size))
+            mixed_steps += any(size == 1 for _, size in meta) and any(size > 1 for _, size in meta)
+            logits = runner.step(entries).cpu()
+            row = 0
+            for i, size in meta:
+                collected[i].append(logits[row:row + size].clone())
+                row += size
+                progress[i] += size
+                for p in runner.cache.table(f"m{i}", 0):
+                    pages_seen.setdefault(p, set()).add(i)
+                if progress[i] == lengths[i]:
+                    runner.finish(f"m{i}")
+                    del progress[i]
+            runner.cache.check()
+            step += 1
     assert any(len(users) > 1 for p, users in pages_seen.items() if p), "no page was used again"
+    assert mixed_steps >= 10, "portions of prompts hardly ever ran beside decoded tokens"
     for i, n in enumerate(lengths):
         assert_close(torch.cat(collected[i]), plain[i][1], dtype, f"{name} mixed request {i}")
+    check_kernels(calls, name, dtype, prompt=True, decode=True)
+    if (name, dtype) in TENSOR_CORE:
+        assert max(calls.decode_splits) > 1, "the keys of a decode step were never split over CTAs"
 
 
 @pytest.mark.parametrize("name, dtype", CASES)
@@ -113,6 +150,39 @@ def test_long_decoding(name, dtype):
     ids, want = plain_logits(name, length, 9)
     got = replay(runner, "long", ids, [3] + [1] * (length - 3))
     assert_close(got, want, dtype, f"{name} long decode")
+
+
+@pytest.mark.parametrize("name, dtype", CASES)
+def test_decode_steps_replayed_from_the_cuda_graph(name, dtype):
+    """The captured decode graph (static buffers, padded batch, fused finishing kernels, key
+    splits planned without the host) against the plain implementation: LOGITS of every decode
+    step, not only tokens.  Three requests of different lengths are fed their known tokens."""
+    from torchlet_b200.engine import StepEntry
+    from torchlet_b200.sampling import SampleSpec
+
+    runner = make_runner(name, dtype, slots=4, cuda_graph=True)
+    lengths = (LENGTHS[name][-1], LENGTHS[name][-2] + 20, 30)
+    plain = [plain_logits(name, n, 300 + i) for i, n in enumerate(lengths)]
+    steps = 24
+    for i in range(3):
+        runner.admit(f"g{i}")
+    runner.step([StepEntry(f"g{i}", plain[i][0][:n - steps], []) for i, n in enumerate(lengths)])
+    got = [[] for _ in lengths]
+    with harness.KernelCalls() as calls:
+        for k in range(steps):
+            entries = [StepEntry(f"g{i}", [plain[i][0][n - steps + k]], sample=SampleSpec(0.0, 0, k))
+                       for i, n in enumerate(lengths)]
+            result = runner.run(entries)
+            logits = result.logits.cpu()
+            assert result.tokens.tolist() == logits.argmax(-1).tolist()
+            for i in range(3):
+                got[i].append(logits[i].clone())
+    assert runner.graph_steps == steps
+    for i, n in enumerate(lengths):
+        assert_close(torch.stack(got[i]), plain[i][1][n - steps:], dtype, f"{name} graph decode, request {i}")
+    for i in range(3):
+        runner.finish(f"g{i}")
+    runner.cache.check()
 
 
 @pytest.mark.parametrize("name, dtype", CASES)

@@ -188,3 +188,29 @@ def test_random_workloads_finish_and_return_all_pages(seed):
             assert r.output_tokens == [1000 + n + i for i in range(r.params.max_new_tokens)]
     assert runner.cache.live_requests() == []
     assert runner.cache.pools[0].num_free == runner.cache.pools[0].num_pages - 1
+
+
+def test_state_only_model_schedules_by_slots_alone():
+    """A model whose every mixer keeps fixed-size state has no page pool: admission is bounded
+    by slots, prompts are still cut by the budget, a preempted request is recomputed from its
+    first token (its state row is cleared when it is admitted again)."""
+    runner = FakeRunner(slots=2)
+    runner.cache = CacheManager([], 4, 2, 256)
+    sched = Scheduler(runner, max_num_batched_tokens=8, max_seq_len=256)
+    reqs = [req(13, new=3), req(5, new=2), req(9, new=4)]
+    for r in reqs:
+        sched.add_request(r)
+    plan = sched.schedule()
+    assert [(p.request is reqs[0], p.length) for p in plan.portions] == [(True, 8)]
+    sched.update(plan, runner.run(plan))
+    plan = sched.schedule()  # the rest of the first prompt, then the second request in the same step
+    assert [(reqs.index(p.request), p.start, p.length) for p in plan.portions] == [(0, 8, 5), (1, 0, 3)]
+    sched.update(plan, runner.run(plan))
+    assert reqs[2].state is RequestState.WAITING  # no slot left
+    sched._preempt(reqs[1])  # what a scheduler does when it must take a request's place away
+    assert reqs[1].num_computed == 0 and sched.waiting[0] is reqs[1]
+    drive(sched, runner)
+    for r in reqs:
+        n = len(r.prompt_tokens)
+        assert r.error is None and r.output_tokens == [1000 + n + i for i in range(r.params.max_new_tokens)]
+    assert runner.cache.live_requests() == [] and runner.cache.num_free_slots == 2

@@ -24,8 +24,8 @@ def register_toys():
 
     @POSITIONS.register("toy_added_positions")
     class AddedPositions(Positions):
-        """q += table[position], k += table[position] (every head the same vector); k and v are
-        then written to the token's place in the request's pages."""
+        """q += table[position], k += table[position] (every head the same vector).  It only
+        encodes; the attention mixer stores k and v in the request's pages itself."""
 
         graph_safe = False  # indexes with host-side shapes: stays out of the captured decode graph
 
@@ -40,20 +40,13 @@ def register_toys():
         def load(self, tensors, prefix, device, dtype):
             self.table = tensors[prefix + "position_table.weight"].to(device=device, dtype=torch.float32)
 
-        def encode_and_store(self, ctx, qkv, num_heads, num_kv_heads, cache, partials=None):
+        def encode(self, ctx, qkv, num_heads, num_kv_heads):
             d, T = self.head_dim, qkv.shape[0]
-            pos = ctx.positions.long()
-            add = self.table[pos][:, None, :]
+            add = self.table[ctx.positions.long()][:, None, :]
             q = qkv[:, : num_heads * d].view(T, num_heads, d)
             k = qkv[:, num_heads * d: (num_heads + num_kv_heads) * d].view(T, num_kv_heads, d)
-            v = qkv[:, (num_heads + num_kv_heads) * d:].view(T, num_kv_heads, d)
             q.copy_((q.float() + add).to(qkv.dtype))
             k.copy_((k.float() + add).to(qkv.dtype))
-            if cache.writable:
-                page = cache.block_table[ctx.token_req.long(), pos // cache.page_size].long()
-                offset = pos % cache.page_size
-                cache.pages[page, 0, :, offset] = k
-                cache.pages[page, 1, :, offset] = v
 
     @FEED_FORWARDS.register("toy_switch")
     class SwitchFeedForward(FeedForward):

@@ -63,3 +63,22 @@ def test_static_scratch_entry_point_refuses_what_does_not_fit():
     assert _call(fn, logits[:1], out[:1]) == 0  # a size that fits still works afterwards
     torch.cuda.synchronize()
     assert int(out[0]) == 0
+
+
+def test_static_scratch_entry_point_refuses_a_temperature_without_seed_or_counter():
+    """Return codes only: a refused call launches nothing."""
+    fn = _static_entry()
+    logits = torch.zeros(2, 100, device="cuda")
+    out = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    temperature = torch.ones(2, device="cuda")
+    seed = torch.zeros(2, dtype=torch.int64, device="cuda")
+    counter = torch.zeros(2, dtype=torch.int32, device="cuda")
+    unsupported = 10001
+    assert _call(fn, logits, out, temperature, None, None) == unsupported
+    assert _call(fn, logits, out, temperature, seed, None) == unsupported
+    assert _call(fn, logits, out, temperature, None, counter) == unsupported
+    torch.cuda.synchronize()
+    assert out.tolist() == [-1, -1]  # nothing ran
+    assert _call(fn, logits, out, temperature, seed, counter) == 0
+    torch.cuda.synchronize()
+    assert all(0 <= t < 100 for t in out.tolist())

@@ -76,7 +76,26 @@ TINY_D = {
 }
 TINY_D_INIT = {"seed": 7, "std": 0.02, "norm_std": 0.02, "page_size": 16}
 
-ALL = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT)}
+# head_dim 64 with 7 query heads a KV head (the head geometry of the reference's own example
+# size), a width and a vocabulary that are no power of two, tied head
+TINY_E = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 411,
+    "hidden_size": 896,
+    "intermediate_size": 304,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 14,
+    "num_key_value_heads": 2,
+    "max_position_embeddings": 1024,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "attention_bias": True,
+    "tie_word_embeddings": True,
+}
+TINY_E_INIT = {"seed": 8, "std": 0.02, "norm_std": 0.02, "page_size": 16}
+
+ALL = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT),
+       "E": (TINY_E, TINY_E_INIT)}
 
 
 def head_dim(cfg: dict) -> int:

@@ -156,7 +156,10 @@ class CacheManager:
                 start = len(table)
                 table.extend(pool.take(n))
                 self.table_arrays[g][record.slot, start:start + n] = table[start:]
-        record.capacity = min(min(len(table) for table in record.tables) * self.page_size, self.max_seq_len)
+        # a model without any paged group (every mixer keeps fixed-size state only) is bounded
+        # by the length limit alone
+        pages = min((len(table) for table in record.tables), default=self.max_pages_per_request)
+        record.capacity = min(pages * self.page_size, self.max_seq_len)
         return True
 
     def begin_decode(self, request_ids) -> tuple:

@@ -6,13 +6,14 @@ from .registry import (
     load_config,
     register_architecture,
 )
-from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .spec import LayerSpec, ModelSpec, NormSlot, PartSpec, ScheduleEntry
 from .qwen2 import Qwen2Config
 
 __all__ = [
     "EngineConfig",
     "LayerSpec",
     "ModelSpec",
+    "NormSlot",
     "PartSpec",
     "Qwen2Config",
     "ScheduleEntry",

@@ -12,7 +12,7 @@ from dataclasses import asdict, dataclass, fields
 from typing import Optional
 
 from .registry import register_architecture
-from .spec import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+from .spec import LayerSpec, ModelSpec, NormSlot, PartSpec, ScheduleEntry
 
 _REQUIRED = (
     "vocab_size",
@@ -153,8 +153,11 @@ class Qwen2Config:
                     block="pre_norm",
                     mixer=mixer,
                     feed_forward=feed_forward,
-                    mixer_norm=norm,
-                    feed_forward_norm=norm,
+                    norms=(NormSlot("mixer_norm", norm, "input_layernorm."),
+                           NormSlot("feed_forward_norm", norm, "post_attention_layernorm.")),
+                    # the checkpoint's names (v10_triton_paged_gqa/layer/transformer_block.py:20-35)
+                    mixer_prefix="self_attn.",
+                    feed_forward_prefix="mlp.",
                 )
             )
         spec = ModelSpec(

@@ -26,15 +26,39 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class NormSlot:
+    """One norm of a layer: the role the block arrangement knows it by (for instance
+    "mixer_norm"), its part, and the tensor-name prefix of its weights below the layer's."""
+
+    role: str
+    part: PartSpec
+    prefix: str
+
+
+@dataclass(frozen=True)
 class LayerSpec:
-    """One layer's parts.  ``prefix`` is the tensor-name prefix of its weights."""
+    """One layer's parts and where their tensors are found.
+
+    ``prefix`` is the tensor-name prefix of the layer; each part's tensors lie below
+    ``prefix + <part prefix>``.  The part prefixes are the checkpoint's own names, set by the
+    architecture's configuration; nothing below the configuration layer spells one out.
+    ``norms`` holds as many norms as the block arrangement ``block`` asks for, by role.
+    """
 
     prefix: str
     block: str  # arrangement of the parts, e.g. "pre_norm"
     mixer: PartSpec
     feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    norms: tuple = ()  # of NormSlot
+    mixer_prefix: str = "mixer."
+    feed_forward_prefix: str = "feed_forward."
+
+    def norm(self, role: str) -> NormSlot:
+        for slot in self.norms:
+            if slot.role == role:
+                return slot
+        raise KeyError(f"layer {self.prefix!r} has no norm for the role {role!r}; "
+                       f"it has: {', '.join(s.role for s in self.norms) or 'none'}")
 
 
 @dataclass(frozen=True)

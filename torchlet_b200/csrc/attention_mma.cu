@@ -57,8 +57,8 @@ struct Params {
   const int* tile_row;    // [tiles] first packed row of the tile (null: 0)
   __nv_bfloat16* out;     // [tokens][nh*D]
   long long out_stride;
-  float* part_acc;  // [tokens*nh][splits][D]   (splits > 1)
-  float* part_ml;   // [tokens*nh][splits][2]
+  float* part_acc;  // [tiles*nh][splits][D]   (splits > 1: decode tiles of one token each)
+  float* part_ml;   // [tiles*nh][splits][2]
   int nh, nkv, page_size, window, splits;
   int page_shift;  // log2(page_size) when it is a power of two, else -1
   int overlap_max_tiles;  // host only: overlapped launch up to this many row tiles
@@ -114,7 +114,8 @@ template <int D, bool TMA> __device__ __forceinline__ __nv_bfloat16* kv_at(__nv_
 
 // Requests the K and V pages of keys [tile * 64, tile * 64 + 64) of one KV head by TMA into a
 // stage (warp 0, one lane a box).  Pages past the request's last key or past the table are
-// read from page 0 (always there; their keys are masked and their values meet P = 0).
+// read from page 0 (always there; their keys are masked and their value rows are cleared in
+// shared memory before use).
 template <int D>
 __device__ __forceinline__ void tma_kv_tile(const CUtensorMap* map, const Params& p, const int* table, int kvh, int tile,
                                             int hi_key, __nv_bfloat16* stage, uint64_t* full, int lane) {
@@ -335,6 +336,19 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
     }
     if constexpr (TMA) {
       tc::mbar_wait(&full[stage], (index / STAGES) & 1, abort_flag, &g_error_word, 1);  // this tile is here
+      // Whole pages were copied: value rows of keys outside [lo_key, hi_key] hold whatever the page
+      // held before (another request's values, page 0).  Their weights are exactly 0, but 0 x NaN
+      // is NaN, so the warp clears those of its own 16 rows before it multiplies.
+      const int key_first = tile * BLOCK_N + warp * 16;
+      if (key_first + 15 > hi_key || key_first < lo_key) {
+        for (int i = lane; i < 16 * (D / 8); i += 32) {
+          const int r = i / (D / 8), c = i % (D / 8);
+          if (key_first + r > hi_key || key_first + r < lo_key)
+            *reinterpret_cast<uint4*>(kv_at<D, true>(vs_tile, warp * 16 + r, c)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // a later TMA copy may refill the stage
+        __syncwarp();
+      }
     } else {
       cp_async_commit();
       cp_async_wait<1>();  // everything but the request just made has landed: this tile is here
@@ -472,7 +486,9 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       const int row = row_start + r;
       const int token = tok0 + row / g, head = kvh * g + row % g;
       if (p.splits > 1) {
-        const size_t item = ((size_t)token * p.nh + head) * p.splits + split;
+        // key splits serve tiles of ONE token: the partial sums are indexed by (tile, head)
+        if (row >= g) continue;
+        const size_t item = ((size_t)blockIdx.x * p.nh + head) * p.splits + split;
         p.part_acc[item * D + c] = acc;
         if (c == 0) {
           p.part_ml[item * 2] = m_all;
@@ -498,11 +514,13 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
   }
 }
 
-// Merges the key splits of every (token, head): one block of D threads each, thread c
-// owning output element c.  The first threads turn each split's max into its weight.
+// Merges the key splits of every (decode tile, head): one block of D threads each, thread c
+// owning output element c.  The first threads turn each split's max into its weight.  Only the
+// rows of the tiles' own tokens are written.
 template <int D>
 __global__ void __launch_bounds__(D)
 attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                         const int* __restrict__ tile_req, const int* __restrict__ req_indptr,
                          __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int splits) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
@@ -536,7 +554,8 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
     for (int j = 0; j < 8; ++j) acc = fmaf(v[j], weight[s + j], acc);
   }
   for (; s < splits; ++s) acc = fmaf(src[(size_t)s * D], weight[s], acc);
-  const int token = item / nh, head = item % nh;
+  const int tile = item / nh, head = item % nh;
+  const int token = req_indptr[tile_req ? tile_req[tile] : tile];
   out[(size_t)token * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / total[0]);
 }
 
@@ -646,9 +665,9 @@ int launch_for(const Params& p, long long num_pages, int tiles, bool rows16, cud
 
 extern "C" {
 
-// Bytes of float32 workspace for ``splits`` key splits over ``tokens`` tokens.
-long long tl_attention_mma_workspace(int tokens, int nh, int d, int splits) {
-  return splits > 1 ? (long long)tokens * nh * splits * (d + 2) * 4 : 0;
+// Bytes of float32 workspace for ``splits`` key splits of ``tiles`` decode tiles.
+long long tl_attention_mma_workspace(int tiles, int nh, int d, int splits) {
+  return splits > 1 ? (long long)tiles * nh * splits * (d + 2) * 4 : 0;
 }
 
 // Reads and clears the code that a bounded wait left when it gave up (0: none).
@@ -661,6 +680,9 @@ int tl_attention_mma_error() {
 
 // rows16 != 0: tiles of 16 packed rows with the keys split over the warps and over
 // ``splits`` CTAs (decode); else tiles of 64 packed rows (prompt portions), splits = 1.
+// With splits > 1 every tile is a request that brings ONE token (tile_row null, at most 16
+// query heads a KV head); the workspace holds tiles * nh * splits * (d + 2) floats, and only
+// the output rows of those tokens are written.
 // pages: one cache layer [num_pages][2][nkv][page_size][d].
 int tl_attention_mma(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
                      int table_width,
@@ -672,7 +694,8 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 2)
     return TL_ERR_UNSUPPORTED;
   if (splits < 1 || (!rows16 && splits != 1) || nkv > 65535 || splits > 64) return TL_ERR_UNSUPPORTED;
-  if (tl_attention_mma_workspace(tokens, nh, d, splits) > workspace_bytes) return TL_ERR_UNSUPPORTED;
+  if (splits > 1 && (tile_row || nh / nkv > 16)) return TL_ERR_UNSUPPORTED;
+  if (tl_attention_mma_workspace(tiles, nh, d, splits) > workspace_bytes) return TL_ERR_UNSUPPORTED;
   Params p;
   p.q = (const __nv_bfloat16*)q;
   p.q_stride = q_stride;
@@ -686,7 +709,7 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   p.out = (__nv_bfloat16*)out;
   p.out_stride = out_stride;
   p.part_acc = (float*)workspace;
-  p.part_ml = p.part_acc + (size_t)tokens * nh * splits * d;
+  p.part_ml = p.part_acc + (size_t)tiles * nh * splits * d;
   p.nh = nh;
   p.nkv = nkv;
   p.page_size = page_size;
@@ -700,11 +723,13 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   const int rc = d == 128 ? launch_for<128>(p, num_pages, tiles, rows16 != 0, stream)
                            : launch_for<64>(p, num_pages, tiles, rows16 != 0, stream);
   if (rc || splits == 1) return rc;
-  const int items = tokens * nh;
+  const int items = tiles * nh;
   if (d == 128)
-    tl::launch_kernel(attention_combine_kernel<128>, items, 128, 0, stream, p.part_acc, p.part_ml, p.out, out_stride, nh, splits);
+    tl::launch_kernel(attention_combine_kernel<128>, items, 128, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
+                      p.out, out_stride, nh, splits);
   else
-    tl::launch_kernel(attention_combine_kernel<64>, items, 64, 0, stream, p.part_acc, p.part_ml, p.out, out_stride, nh, splits);
+    tl::launch_kernel(attention_combine_kernel<64>, items, 64, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
+                      p.out, out_stride, nh, splits);
   return TL_LAUNCH_CHECK();
 }
 

@@ -56,19 +56,6 @@ constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 __device__ int g_error_word = 0;
 
-// Built with -DATTN_TIMING every role adds up the cycles it spends between its TICK marks (eight
-// slots a role: loader K, MMA, softmax of row tile 0 and 1); tl_attention_tc_timing() reads the sums.
-#ifdef ATTN_TIMING
-__device__ unsigned long long g_timing[32];
-#define TIMING_BEGIN() long long t_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; long long t_last = clock64();
-#define TICK(slot) { const long long t_now = clock64(); t_acc[slot] += t_now - t_last; t_last = t_now; }
-#define TIMING_END(base) if (lane == 0) { for (int t_i = 0; t_i < 8; ++t_i) atomicAdd(&g_timing[(base) + t_i], (unsigned long long)t_acc[t_i]); }
-#else
-#define TIMING_BEGIN()
-#define TICK(slot)
-#define TIMING_END(base)
-#endif
-
 struct Params {
   const __nv_bfloat16* q;
   long long q_stride;
@@ -182,6 +169,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   uint64_t* s_full = bars + 8;    // [2 row tiles]  S_X of the next key tile is in tensor memory
   uint64_t* p_full = bars + 10;   // [2 row tiles]  (4 arrivals: one per softmax warp) P_X is written
   uint64_t* o_done = bars + 12;   // [2 row tiles]  the last P_X V is done
+  uint64_t* v_clean = bars + 14;  // value rows outside the CTA's keys are cleared (edge tiles only)
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -196,6 +184,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   const int before = p.kv_before[req];
   const int* table = p.block_table + (size_t)req * p.table_width;
   RowTile tile[QTILES];
+  int cta_lo_key = 0, cta_hi_key = -1;  // the keys any row of the CTA may see
 #pragma unroll
   for (int x = 0; x < QTILES; ++x) {
     RowTile& t = tile[x];
@@ -207,11 +196,17 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       const int lo_key = p.window > 0 ? max(0, before + first_tok - p.window + 1) : 0;
       t.begin = lo_key / KEYS;
       t.end = (before + last_tok) / KEYS + 1;
+      if (x == 0) cta_lo_key = lo_key;
+      cta_hi_key = before + last_tok;
     }
   }
   // Later rows need later keys, so the CTA's key tiles are [first of tile 0, last of the last tile)
   const int j_begin = tile[0].begin;
   const int j_end = max(tile[0].end, tile[1].end);
+  // Whole pages are copied, so the first and the last key tile may hold rows of keys outside
+  // [cta_lo_key, cta_hi_key]: whatever the pages held before.  Their weights are exactly 0, but
+  // 0 x NaN is NaN, so the V loader clears those value rows before the tensor core reads them.
+  const bool edge_first = cta_lo_key % KEYS != 0, edge_last = cta_hi_key % KEYS != KEYS - 1;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -223,6 +218,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       mbar_init(&p_full[i], 4);
       mbar_init(&o_done[i], 1);
     }
+    mbar_init(v_clean, 1);
     *abort_flag = 0;
     mbar_fence_init();
     prefetch_tensormap(&map_kv);
@@ -264,23 +260,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     const int pages_per_tile = KEYS / p.page_size;
     const int my_page = lane >> 1, my_half = lane & 1;
     const bool active = my_page < pages_per_tile;
-    TIMING_BEGIN();
     for (int j = j_begin; j < j_end; ++j) {
       const int jj = j - j_begin, s = jj & 1;
       const uint32_t phase = (jj >> 1) & 1;
       const int index = j * pages_per_tile + my_page;
       const int page = (active && index < p.table_width) ? table[index] : 0;  // beyond the table: page 0
       const uint32_t offset = s * TILE_BYTES + my_half * SLAB + my_page * p.page_size * 128;
-      TICK(0);
       mbar_wait(&empty[s], phase ^ 1, abort_flag, &g_error_word, 1 + is_v);
-      TICK(1);
       if (lane == 0) mbar_expect_tx(&full[s], TILE_BYTES);
       __syncwarp();
       if (active)
         tma_load_2d(tiles + offset, &map_kv, &full[s], my_half * 64, ((page * 2 + is_v) * p.nkv + kvh) * p.page_size);
-      TICK(2);
+      if (is_v && ((edge_first && j == j_begin) || (edge_last && j == j_end - 1))) {
+        mbar_wait(&full[s], phase, abort_flag, &g_error_word, 10);  // the tile has landed
+        for (int i = lane; i < KEYS * 16; i += 32) {  // a key's row: 128 bytes in each of the two slabs
+          const int k = i >> 4, key = j * KEYS + k;
+          if (key < cta_lo_key || key > cta_hi_key)
+            *reinterpret_cast<uint4*>(tiles + s * TILE_BYTES + ((i >> 3) & 1) * SLAB + k * 128 + (i & 7) * 16) =
+                make_uint4(0u, 0u, 0u, 0u);
+        }
+        fence_proxy_async();  // the tensor core reads, and later copies overwrite, what these stores wrote
+        __syncwarp();
+        if (lane == 0) mbar_arrive(v_clean);
+      }
     }
-    if (is_v == 0) TIMING_END(0);
   } else if (warp == 8) {
     // --------------------------------------------------------------------- MMA
     // The whole warp walks the loop and waits; one elected lane issues (with the loop inside a
@@ -297,16 +300,15 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     const uint64_t q_desc[QTILES] = {smem_desc_sw128(smem_addr(q_tiles)), smem_desc_sw128(smem_addr(q_tiles + TILE_BYTES))};
     const uint64_t k_desc[2] = {smem_desc_sw128(smem_addr(k_tiles)), smem_desc_sw128(smem_addr(k_tiles + TILE_BYTES))};
     const uint64_t v_desc[2] = {smem_desc_v(smem_addr(v_tiles)), smem_desc_v(smem_addr(v_tiles + TILE_BYTES))};
-    TIMING_BEGIN();
     // One step past the last key tile, for the P V that runs a tile behind
     for (int j = j_begin; j <= j_end; ++j) {
       const int jj = j - j_begin;
-      TICK(0);
       // V of the previous key tile has long arrived, K of this one nearly always
       if (jj > 0) mbar_wait(&v_full[(jj - 1) & 1], ((jj - 1) >> 1) & 1, abort_flag, &g_error_word, 6);
-      TICK(1);
+      if (jj > 0 && ((edge_first && j - 1 == j_begin) || (edge_last && j == j_end)))
+        mbar_wait(v_clean, (edge_first && edge_last && j == j_end && j_end - j_begin > 1) ? 1 : 0, abort_flag,
+                  &g_error_word, 11);
       if (j < j_end) mbar_wait(&k_full[jj & 1], (jj >> 1) & 1, abort_flag, &g_error_word, 3);
-      TICK(2);
       // the last row tile with work at this step (row tile 0 always has some)
       const bool work_1 = (j - 1 >= tile[1].begin && j - 1 < tile[1].end) || (j >= tile[1].begin && j < tile[1].end);
 #pragma unroll
@@ -318,7 +320,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         if (!do_pv && !do_s) continue;
         const int t = j - 1 - tile[x].begin;
         if (do_pv) mbar_wait(&p_full[x], t & 1, abort_flag, &g_error_word, 5);
-        TICK(3);
         fence_after_sync();
         if (elect_one()) {
           if (do_pv) {
@@ -345,10 +346,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
           }
         }
         __syncwarp();
-        TICK(4);
       }
     }
-    TIMING_END(8);
   } else {
     // ----------------------------------------------------------------- softmax
     const int x = warp >> 2, quarter = warp & 3;
@@ -363,12 +362,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     const uint32_t tmem_o = tmem_base + 256 + x * D + lane_base;
     const int num_tiles = mine.end - mine.begin;
     float m_ref = -INFINITY, l_sum = 0.f;  // m_ref in log2 units (already scaled)
-    TIMING_BEGIN();
     for (int t = 0; t < num_tiles; ++t) {
       const int key0 = (mine.begin + t) * KEYS;
-      TICK(0);
       mbar_wait(&s_full[x], t & 1, abort_flag, &g_error_word, 7);
-      TICK(1);
       fence_after_sync();
       uint32_t v[KEYS];  // the row of S, in registers
 #pragma unroll
@@ -396,7 +392,6 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         m_d = max3(m_d, __uint_as_float(v[i + 6]), __uint_as_float(v[i + 7]));
       }
       const float m_tile = fmaxf(fmaxf(m_a, m_b), fmaxf(m_c, m_d)) * p.scale_log2;  // the scale is positive
-      TICK(2);
       // the reference max moves only when the row's max has grown past the threshold
       float factor = 1.f;
       bool rescale = false;
@@ -418,23 +413,19 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
           tmem_st_32(tmem_o + c, o);
         }
       }
-      TICK(3);
       // P = exp2(S * scale - m_ref) as bfloat16 pairs over the first half of S's columns; row sum
       const float neg_m = m_ref == -INFINITY ? 0.f : -m_ref;
       float sum_a = 0.f, sum_b = 0.f;
       exp_and_store(v, p.scale_log2, neg_m, tmem_s, sum_a, sum_b);
       l_sum += sum_a + sum_b;
       tmem_st_wait();
-      TICK(4);
       fence_before_sync();  // our tcgen05.ld/st of S, P and O are done
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[x]);
-      TICK(5);
     }
     // ---- output: O / l
     if (num_tiles > 0) {
       mbar_wait(&o_done[x], 0, abort_flag, &g_error_word, 9);
-      TICK(6);
       fence_after_sync();
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
       __nv_bfloat16* dst = nullptr;
@@ -457,9 +448,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
                 make_uint4(packed[4 * q4], packed[4 * q4 + 1], packed[4 * q4 + 2], packed[4 * q4 + 3]);
         }
       }
-      TICK(7);
     }
-    if (quarter == 0) TIMING_END(16 + 8 * x);
   }
   __syncwarp();
   fence_before_sync();
@@ -502,14 +491,6 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_
 }  // namespace
 
 extern "C" {
-
-#ifdef ATTN_TIMING
-int tl_attention_tc_timing(unsigned long long* out) {  // reads and clears the 32 counters
-  unsigned long long zero[32] = {};
-  if (cudaMemcpyFromSymbol(out, g_timing, sizeof(zero)) != cudaSuccess) return -1;
-  return (int)cudaMemcpyToSymbol(g_timing, zero, sizeof(zero));
-}
-#endif
 
 int tl_attention_tc_error() {
   int value = 0, zero = 0;

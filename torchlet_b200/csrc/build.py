@@ -95,7 +95,8 @@ def build_dir() -> Path:
 def _source_hash(name: str) -> str:
     digest = hashlib.sha256()
     digest.update(" ".join(NVCC_FLAGS).encode())
-    for path in [SOURCE_DIR / f"{name}.cu", *sorted(SOURCE_DIR.glob("*.cuh"))]:
+    # every header beside the sources counts: a changed constant must rebuild its users
+    for path in [SOURCE_DIR / f"{name}.cu", *sorted(SOURCE_DIR.glob("*.cuh")), *sorted(SOURCE_DIR.glob("*.h"))]:
         digest.update(path.name.encode())
         digest.update(path.read_bytes())
     return digest.hexdigest()

@@ -113,6 +113,7 @@ rms_norm_vec_kernel(const float* __restrict__ acc, const float* __restrict__ w, 
 //   q heads are rotated in place;
 //   k heads are rotated and written to the page of (request, p);
 //   v heads are copied to the page.
+// inv_freq null: nothing is rotated; k and v are copied to the pages as they are.
 // Page layout of one cache layer: [page][2 (k, v)][kv head][slot in page][d].
 template <typename T>
 __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ positions,
@@ -139,9 +140,11 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     const float x1 = to_float(row[i]);
     const float x2 = to_float(row[i + half]);
-    if (is_v) {
-      dst[i] = row[i];
-      dst[i + half] = row[i + half];
+    if (is_v || !inv_freq) {
+      if (dst != row) {
+        dst[i] = row[i];
+        dst[i + half] = row[i + half];
+      }
     } else {
       const float angle = (float)pos * inv_freq[i];
       float s, c;
@@ -179,9 +182,11 @@ rope_kv_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ posi
     }
     const uint4 lo = *reinterpret_cast<const uint4*>(row + i);
     const uint4 hi = *reinterpret_cast<const uint4*>(row + i + half);
-    if (is_v) {
-      *reinterpret_cast<uint4*>(dst + i) = lo;
-      *reinterpret_cast<uint4*>(dst + i + half) = hi;
+    if (is_v || !inv_freq) {
+      if (dst != row) {
+        *reinterpret_cast<uint4*>(dst + i) = lo;
+        *reinterpret_cast<uint4*>(dst + i + half) = hi;
+      }
       continue;
     }
     float x1[8], x2[8];

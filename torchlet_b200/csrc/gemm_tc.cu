@@ -895,9 +895,40 @@ int launch_swapped(const CUtensorMap& map_row, const CUtensorMap& map_col, const
   return TL_LAUNCH_CHECK();
 }
 
+// A wait that nothing ends, with a limit of 2^16 cycles (tens of microseconds): the same
+// mbar_wait the products use gives up, leaves its code in the error word and in the block's
+// abort flag, the block's second wait then gives up at once, and the kernel returns normally.
+__global__ void wait_selftest_kernel(int code) {
+  tl::pdl_wait();
+  tl::pdl_launch_dependents();
+  __shared__ uint64_t bar;
+  __shared__ int abort_word;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    abort_word = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    mbar_wait(&bar, 0, abort_flag, &g_error_word, code, 1ll << 16);  // nobody arrives
+    mbar_wait(&bar, 0, abort_flag, &g_error_word, code + 1);         // the block has given up: a short limit
+  }
+  __syncthreads();
+}
+
 }  // namespace
 
 extern "C" {
+
+// Shows, without a fault or a hang, what happens when a bounded wait runs out: launches one
+// block that waits on a barrier nobody arrives at (limit 2^16 cycles).  Afterwards
+// tl_gemm_tc_error() returns ``code``.  For tests of the error path.
+int tl_gemm_tc_wait_selftest(int code, cudaStream_t stream) {
+  if (code <= 0) return TL_ERR_UNSUPPORTED;
+  tl::launch_kernel(wait_selftest_kernel, 1, 32, 0, stream, code);
+  return TL_LAUNCH_CHECK();
+}
 
 // How a product of these sizes would run: *swap (0/1), *splits; returns the bytes of
 // float32 workspace it needs (partial sums: the swapped orientation, K splits of the pair kernel).

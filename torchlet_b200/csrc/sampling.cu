@@ -145,7 +145,7 @@ extern "C" {
 
 // Bytes of scratch that let a row be scanned by several blocks (0: one block a row).
 long long tl_sample_scratch_bytes(int rows, int vocab) {
-  const int chunks = (vocab + CHUNK - 1) / CHUNK;
+  const long long chunks = ((long long)vocab + CHUNK - 1) / CHUNK;
   return chunks > 1 ? (long long)rows * chunks * (long long)sizeof(Best) : 0;
 }
 
@@ -153,16 +153,18 @@ int tl_sample(const float* logits, long long row_stride, int rows, int vocab, co
               const long long* seed, const int* counter, int* out, void* scratch, long long scratch_bytes,
               cudaStream_t stream) {
   if (rows <= 0) return 0;
-  if (vocab <= 0) return TL_ERR_UNSUPPORTED;
-  int chunks = (vocab + CHUNK - 1) / CHUNK;
+  if (vocab <= 0 || !logits || !out) return TL_ERR_UNSUPPORTED;
+  // a row with temperature > 0 reads its seed and its counter: all three, or none
+  if (temperature && (!seed || !counter)) return TL_ERR_UNSUPPORTED;
+  long long chunks = ((long long)vocab + CHUNK - 1) / CHUNK;
   if (chunks > 1 && (!scratch || scratch_bytes < tl_sample_scratch_bytes(rows, vocab))) chunks = 1;
   if (chunks > 65535) return TL_ERR_UNSUPPORTED;
   const int span = chunks > 1 ? CHUNK : vocab;
-  tl::launch_kernel(sample_kernel, dim3(rows, chunks), NT, 0, stream, logits, (size_t)row_stride, vocab, span, temperature, seed,
-                                                      counter, out, (Best*)scratch);
+  tl::launch_kernel(sample_kernel, dim3(rows, (unsigned)chunks), NT, 0, stream, logits, (size_t)row_stride, vocab, span,
+                    temperature, seed, counter, out, (Best*)scratch);
   int rc = TL_LAUNCH_CHECK();
   if (rc || chunks == 1) return rc;
-  tl::launch_kernel(sample_merge_kernel, rows, 32, 0, stream, (const Best*)scratch, chunks, out);
+  tl::launch_kernel(sample_merge_kernel, rows, 32, 0, stream, (const Best*)scratch, (int)chunks, out);
   return TL_LAUNCH_CHECK();
 }
 
@@ -175,7 +177,9 @@ int tl_sample_static(const float* logits, long long row_stride, int rows, int vo
                      const long long* seed, const int* counter, int* out, cudaStream_t stream) {
   if (rows <= 0) return 0;
   if (vocab <= 0 || !logits || !out) return TL_ERR_UNSUPPORTED;
-  const long long chunks = (vocab + CHUNK - 1) / CHUNK;
+  // a row with temperature > 0 reads its seed and its counter: all three, or none
+  if (temperature && (!seed || !counter)) return TL_ERR_UNSUPPORTED;
+  const long long chunks = ((long long)vocab + CHUNK - 1) / CHUNK;
   if (chunks > 65535 || (long long)rows * chunks > TL_SAMPLE_STATIC_MAX_PARTIALS) return TL_SAMPLE_STATIC_TOO_LARGE;
   // In host code the array's name is only a stand-in: the device address is looked up
   // once per device, with that device current, and kept.

@@ -39,7 +39,9 @@ extern "C" {
 #endif
 
 // Returns 0, TL_SAMPLE_STATIC_TOO_LARGE, 10001 (bad arguments) or a cudaError_t.
-// temperature / seed / counter may all be null: every row is then greedy.
+// temperature / seed / counter may all be null: every row is then greedy.  A non-null
+// temperature needs a seed and a counter as well (a row with temperature > 0 reads both);
+// with either missing the call is refused with 10001 and nothing is launched.
 int tl_sample_static(const float* logits, long long row_stride, int rows, int vocab, const float* temperature,
                      const long long* seed, const int* counter, int* out, cudaStream_t stream);
 

@@ -53,11 +53,12 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return done != 0;
 }
 // Bounded wait.  ``abort_flag`` is a word in shared memory, ``error_word`` in global.
+// ``cycles``: the limit of a block that has not given up yet.
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
-                                          int* error_word, int code) {
+                                          int* error_word, int code, long long cycles = TL_WAIT_CYCLES) {
   if (mbar_try_wait(bar, parity)) return;
   const long long start = clock64();
-  const long long limit = *abort_flag ? TL_WAIT_CYCLES_ABORTED : TL_WAIT_CYCLES;
+  const long long limit = *abort_flag ? TL_WAIT_CYCLES_ABORTED : cycles;
   while (!mbar_try_wait(bar, parity)) {
     if (clock64() - start > limit) {
       if (!*abort_flag) {

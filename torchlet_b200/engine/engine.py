@@ -21,9 +21,11 @@ from .scheduler import Request, RequestState, ScheduledPortion, Scheduler, StepP
 
 
 class Engine:
-    def __init__(self, model: LayeredModel, config: Optional[EngineConfig] = None):
+    def __init__(self, model: LayeredModel, config: Optional[EngineConfig] = None, runner=None):
+        """``runner``: the step function to drive, default a ``ModelRunner`` over ``model`` (tests
+        of the loop's own decisions pass a stand-in and no model)."""
         self.config = config or EngineConfig()
-        self.runner = ModelRunner(model, self.config)
+        self.runner = runner if runner is not None else ModelRunner(model, self.config)
         self.scheduler = Scheduler(self.runner, self.config.max_num_batched_tokens, self.config.max_seq_len)
         self.steps_ahead = 0  # decode steps launched before the tokens of the step before were read
 
@@ -51,18 +53,31 @@ class Engine:
         return entries
 
     def step(self) -> list:
-        """One engine step; returns the requests that finished (or failed) in it."""
+        """One engine step; returns the requests that finished (or failed) in it.  A failure
+        inside the step ends every live request with that error, gives everything back, and
+        is raised again."""
         scheduler = self.scheduler
-        plan = scheduler.schedule()
-        done = list(plan.failed)
-        if plan.portions:
-            result = self.runner.run(self._entries(plan))
-            sampled = result.tokens.tolist() if result.tokens is not None else []
-            done += scheduler.update(plan, sampled)
-            if done:  # nothing is handed back before the kernels' own error words have been read
-                ops.raise_on_wait_errors()
+        try:
+            plan = scheduler.schedule()
+            done = list(plan.failed)
+            if plan.portions:
+                result = self.runner.run(self._entries(plan))
+                sampled = result.tokens.tolist() if result.tokens is not None else []
+                done += scheduler.update(plan, sampled)
+                if done:  # nothing is handed back before the kernels' own error words have been read
+                    ops.raise_on_wait_errors()
+        except Exception as exc:
+            self._fail_everything(exc)
+            raise
         scheduler.drain_finished()
         return done
+
+    def _fail_everything(self, exc: Exception) -> list:
+        """A failed step fails every live request (the reference: engine.py:215-217)."""
+        logger.error("engine step failed: %s", exc)
+        failed = self.scheduler.fail_all(exc)
+        self.scheduler.drain_finished()
+        return failed
 
     # ----------------------------------------------------- decode, one step ahead
     # While every running request decodes, the next step's inputs are known before this
@@ -139,9 +154,7 @@ class Engine:
                     ended += done
                 scheduler.drain_finished()
         except Exception as exc:  # a failed step fails every live request
-            logger.error("engine step failed: %s", exc)
-            ended += self.scheduler.fail_all(exc)
-            self.scheduler.drain_finished()
+            ended += self._fail_everything(exc)
             raise
         return ended
 

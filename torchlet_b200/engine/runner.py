@@ -48,6 +48,16 @@ class StepResult:
     tokens: Optional[torch.Tensor]  # int32 [sampled entries], in the order of the entries
 
 
+@dataclass
+class PendingSum:
+    """A sum into the float32 stream ``acc`` that a product left unfinished."""
+
+    partials: torch.Tensor  # float32 [splits, tokens, width] in the shared workspace
+    splits: int
+    bias: Optional[torch.Tensor]
+    acc: torch.Tensor
+
+
 class StepContext:
     """Everything a part may read about the current step."""
 
@@ -66,28 +76,35 @@ class StepContext:
         # host copies (numpy int32) for parts that plan on the host
         self.req_indptr_host = self.kv_before_host = self.slots_host = None
         self.plans: dict = {}  # per-step plans parts share across layers
-        # a sum into the residual stream that a product left unfinished for the next norm
-        # to complete: (partials, splits, bias, acc) or None
-        self._pending = None
+        self._pending: Optional[PendingSum] = None  # see ``leave_pending``
         # sampling rows of the step (device), None when every sampled row is greedy
         self.num_sampled = 0
         self.sample_temperature = self.sample_seed = self.sample_counter = None
 
-    @property
-    def pending(self):
-        return self._pending
+    # A product may leave its last sum into a stream unfinished (float32 partial sums in the
+    # shared workspace) so that whoever reads the stream next completes it inside its own kernel.
+    def leave_pending(self, partials, splits: int, bias, acc) -> None:
+        """``acc`` still lacks the sum of ``splits`` partial results (+ ``bias``)."""
+        self.flush_pending()
+        self._pending = PendingSum(partials, splits, bias, acc)
+        ops.workspace_holder = self
 
-    @pending.setter
-    def pending(self, value) -> None:
-        self._pending = value
-        ops.workspace_holder = self if value is not None else None
+    def take_pending(self, acc) -> Optional["PendingSum"]:
+        """The unfinished sum into this very ``acc``, if there is one; the caller completes it."""
+        pending = self._pending
+        if pending is None or pending.acc is not acc:
+            return None
+        self._pending = None
+        ops.workspace_holder = None
+        return pending
 
     def flush_pending(self) -> None:
-        """Complete an unfinished sum into the residual stream (see ``pending``)."""
-        if self._pending is not None:
-            partials, splits, bias, acc = self._pending
-            self.pending = None
-            ops.finish_accum_norm(partials, splits, bias, acc)
+        """Complete an unfinished sum into a stream (see ``leave_pending``)."""
+        pending = self._pending
+        if pending is not None:
+            self._pending = None
+            ops.workspace_holder = None
+            ops.finish_accum_norm(pending.partials, pending.splits, pending.bias, pending.acc)
 
     def buffer(self, name: str, shape: tuple, dtype: torch.dtype) -> torch.Tensor:
         return self._runner.buffer(name, shape, dtype)
@@ -115,7 +132,11 @@ class ModelRunner:
         )
         self.cache = self.storage.manager
         self.num_groups = len(self.storage.groups)
-        self.token_capacity = max(config.max_num_batched_tokens, config.max_decode_slots)
+        # rows of the persistent scratch buffers: the token budget, and the largest padded decode
+        # batch a captured graph runs (a buffer that grew later would leave earlier graphs with
+        # freed addresses)
+        largest_graph = self._bucket(min(config.max_decode_slots, self.GRAPH_BUCKETS[-1]))
+        self.token_capacity = max(config.max_num_batched_tokens, config.max_decode_slots, largest_graph)
         self._buffers: dict[str, torch.Tensor] = {}
         # two pinned staging blocks used in turn, each guarded by the event of its last copy
         self._meta_host = [None, None]

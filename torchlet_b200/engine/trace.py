@@ -27,7 +27,8 @@ def parse_args(argv=None):
     parser.add_argument("--out", required=True, help="folder the logits are written to")
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens live requests hold at any time (each rounded up to 64)")
-    parser.add_argument("--page-size", type=int, default=16, help="tokens per cache page (divides 64)")
+    parser.add_argument("--page-size", type=int, default=16,
+                        help="tokens per cache page (any size the kernels take)")
     parser.add_argument("--max-live", type=int, default=8, help="most requests live at a time")
     return parser.parse_args(argv)
 
@@ -36,8 +37,8 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     args = parse_args(argv)
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
-    if args.page_size <= 0 or 64 % args.page_size:
-        raise SystemExit("--page-size must divide 64")
+    if args.page_size <= 0:
+        raise SystemExit("--page-size must be positive")
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
 
@@ -51,12 +52,15 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     print("[trace_run] loading the model and compiling kernels if needed ...", file=sys.stderr, flush=True)
     model = load_model(args.model, args.dtype)
     max_tokens = -(-max(args.max_tokens, 64) // 64) * 64
+    # pages for that many tokens; a page size that does not divide 64 may leave every live request
+    # one page short of its rounded count, so those get one page each on top
+    num_pages = -(-max_tokens // args.page_size) + (0 if 64 % args.page_size == 0 else args.max_live)
     max_pos = model.spec.max_position_embeddings
     config = EngineConfig(
         dtype=args.dtype,
         max_decode_slots=args.max_live,
         kv_block_size=args.page_size,
-        max_num_blocks=max_tokens // args.page_size + 1,
+        max_num_blocks=num_pages + 1,
         max_seq_len=min(max_tokens, max_pos),
         max_num_batched_tokens=max(2048, min(max_tokens, max_pos)),
         cuda_graph=False,

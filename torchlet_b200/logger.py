@@ -11,14 +11,14 @@ import logging
 import os
 import sys
 
-_FORMAT = "%(asctime)s [%(levelname)s] %(name)s %(filename)s:%(lineno)d - %(message)s"
+_FORMAT = "%(levelname).1s %(asctime)s %(name)s (%(module)s:%(lineno)d) %(message)s"
 
 
 def get_logger(name: str = "torchlet_b200") -> logging.Logger:
     log = logging.getLogger(name)
     if not log.handlers:
         handler = logging.StreamHandler(sys.stderr)
-        handler.setFormatter(logging.Formatter(_FORMAT, datefmt="%Y-%m-%d %H:%M:%S"))
+        handler.setFormatter(logging.Formatter(_FORMAT, datefmt="%H:%M:%S"))
         log.addHandler(handler)
         log.propagate = False
         level = os.environ.get("TORCHLET_B200_LOG", "WARNING").upper()

@@ -51,6 +51,7 @@ _SIGNATURES = {
                        c_longlong, c_void_p, c_longlong, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_plan": [c_int, c_int, c_int, c_void_p, c_void_p],
         "tl_gemm_tc_error": [],
+        "tl_gemm_tc_wait_selftest": [c_int, c_void_p],
     },
     "attention_mma": {
         "tl_attention_mma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
@@ -164,6 +165,18 @@ def rope_kv(qkv, positions, token_req, block_table, pages, inv_freq, nh, nkv, d,
         block_table.data_ptr(), block_table.shape[1], pages.data_ptr(), inv_freq.data_ptr(), tokens, nh, nkv,
         d, page_size, 1 if write_kv else 0, _stream())
     _check(code, "rope_kv")
+
+
+def store_kv(qkv, positions, token_req, block_table, pages, nh, nkv, d, page_size) -> None:
+    """Write the k and v heads of the fused ``qkv`` rows to the cache pages, unchanged (for a mixer
+    whose position encoding, if any, does not store them itself)."""
+    _need_cuda(qkv, positions, token_req, block_table, pages)
+    assert qkv.is_contiguous() and qkv.shape[1] == (nh + 2 * nkv) * d and pages.dtype == qkv.dtype
+    code = _fn("elementwise", "tl_rope_kv")(
+        qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), token_req.data_ptr(),
+        block_table.data_ptr(), block_table.shape[1], pages.data_ptr(), None, qkv.shape[0], nh, nkv,
+        d, page_size, 1, _stream())
+    _check(code, "store_kv")
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -340,13 +353,22 @@ def gemm_tc_error() -> int:
     return _fn("gemm_tc", "tl_gemm_tc_error")()
 
 
+def wait_selftest(code: int = 99) -> None:
+    """Launches one block whose bounded wait runs out (nothing ever arrives at its barrier; the
+    limit is 2^16 cycles) and that then returns normally: ``gemm_tc_error()`` afterwards gives
+    ``code`` and ``raise_on_wait_errors()`` raises.  Nothing faults or hangs; for tests."""
+    _check(_fn("gemm_tc", "tl_gemm_tc_wait_selftest")(code, _stream()), "wait_selftest")
+
+
 def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, tokens, nh, nkv,
                   d, page_size, window, scale, rows16: bool, splits: int = 1) -> None:
     """Tensor-core paged attention (csrc/attention_mma.cu).  ``tile_req``/``tile_row`` None:
-    tile i is request i from its first packed row."""
+    tile i is request i from its first packed row.  With ``splits`` > 1 every tile is a request
+    that brings one token; only those tokens' rows of ``out`` are written."""
     _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16
-    need = tokens * nh * splits * (d + 2) * 4 if splits > 1 else 0
+    # key splits: float32 partial results of every (decode tile, head, split), merged by a second kernel
+    need = tiles * nh * splits * (d + 2) * 4 if splits > 1 else 0
     ws = _workspace(("attention", qkv.device), need) if need else None
     code = _fn("attention_mma", "tl_attention_mma")(
         qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),

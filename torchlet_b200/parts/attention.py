@@ -1,6 +1,7 @@
 """Grouped-query attention mixer over a paged cache.
 
-q = x Wq^T + bq, k = x Wk^T + bk, v = x Wv^T + bv; position encoding on q and k; keys
+q = x Wq^T + bq, k = x Wk^T + bk, v = x Wv^T + bv; position encoding on q and k (if the
+layer has one; ``positions`` may be absent); keys
 and values of the step's tokens go to the request's pages; every token attends to the
 keys of its request at positions <= its own (and within ``window`` of it, if set), query
 head h reading KV head h // (heads / kv_heads); softmax(q.k * scale) in float32; the
@@ -85,15 +86,21 @@ class AttentionMixer(Mixer):
     def forward(self, ctx, x, acc, cache) -> None:
         tokens = x.shape[0]
         qkv = ctx.buffer("attention.qkv", (tokens, self.q_size + 2 * self.kv_size), ctx.dtype)
-        if self.positions is None:
-            raise NotImplementedError("an attention mixer needs a position encoding that stores k and v")
-        partials = self.qkv_proj.deferred(ctx, x) if getattr(self.positions, "accepts_partials", False) else None
+        positions = self.positions
+        partials = self.qkv_proj.deferred(ctx, x) if getattr(positions, "accepts_partials", False) else None
         if partials is not None:
-            self.positions.encode_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, cache,
-                                            partials=(partials[0], partials[1], self.qkv_proj.bias))
+            positions.encode_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, cache,
+                                       partials=(partials[0], partials[1], self.qkv_proj.bias))
         else:
             self.qkv_proj.forward(x, qkv)
-            self.positions.encode_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, cache)
+            if positions is not None and positions.stores_kv:
+                positions.encode_and_store(ctx, qkv, self.num_heads, self.num_kv_heads, cache)
+            else:  # no encoding at all, or one that only encodes: the mixer stores k and v itself
+                if positions is not None:
+                    positions.encode(ctx, qkv, self.num_heads, self.num_kv_heads)
+                if cache.writable:
+                    ops.store_kv(qkv, ctx.positions, ctx.token_req, cache.block_table, cache.pages, self.num_heads,
+                                 self.num_kv_heads, self.head_dim, cache.page_size)
         out = ctx.buffer("attention.out", (tokens, self.q_size), ctx.dtype)
         from . import attention_bf16
 

@@ -71,16 +71,38 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, ctx, acc, out=None):
-        """Return the normed ``acc`` rows in the compute dtype."""
+    """A norm reads rows of the float32 stream ``acc`` and returns them normed in the compute
+    dtype.  A sub-class implements ``forward``; blocks and the model call ``apply``, which first
+    completes any sum into ``acc`` that a product left unfinished, so that ``forward`` can read
+    ``acc`` as it stands.  A norm that can take over such a sum and finish it inside its own
+    kernel sets ``fuses_pending`` and asks ``ctx.take_pending(acc)`` itself."""
+
+    fuses_pending = False
+
+    def apply(self, ctx, acc, out=None, rows=None, name="normed"):
+        if not self.fuses_pending:
+            ctx.flush_pending()
+        return self.forward(ctx, acc, out=out, rows=rows, name=name)
+
+    def forward(self, ctx, acc, out=None, rows=None, name="normed"):
+        """Return the normed ``acc`` rows (all, or those ``rows`` names, int32) in the compute
+        dtype; ``out`` or a buffer called ``name`` receives them."""
         raise NotImplementedError
 
 
 class Positions(Part):
-    """A position encoding applied inside a mixer.  ``graph_safe`` False keeps a model that
-    uses it out of the captured decode graph (it plans on the host)."""
+    """A position encoding applied inside a mixer: ``encode(ctx, qkv, num_heads, num_kv_heads)``
+    changes the q and k heads of the fused ``qkv`` rows in place; the mixer then stores k and v
+    itself.  An encoding that can write k and v to the cache pages in the same pass sets
+    ``stores_kv`` and implements ``encode_and_store(ctx, qkv, num_heads, num_kv_heads, cache)``
+    instead.  ``graph_safe`` False keeps a model that uses it out of the captured decode graph
+    (it plans on the host)."""
 
     graph_safe = True
+    stores_kv = False
+
+    def encode(self, ctx, qkv, num_heads, num_kv_heads) -> None:
+        raise NotImplementedError
 
 
 class Mixer(Part):
@@ -107,15 +129,20 @@ class FeedForward(Part):
 
 
 class Block:
-    """An arrangement of a layer's parts around the residual stream."""
+    """An arrangement of a layer's parts around the residual stream.  ``norm_roles`` names the
+    norms the arrangement needs; the layer's description must hold one for each role, and
+    ``norms`` maps the roles to the built parts."""
 
     kind: str = ""
+    norm_roles: tuple = ()
 
-    def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
+    def __init__(self, mixer: Mixer, feed_forward: FeedForward, norms: dict):
+        missing = [role for role in self.norm_roles if role not in norms]
+        if missing:
+            raise ValueError(f"block arrangement {self.kind!r} needs norms for the roles {missing}")
         self.mixer = mixer
         self.feed_forward = feed_forward
-        self.mixer_norm = mixer_norm
-        self.feed_forward_norm = feed_forward_norm
+        self.norms = dict(norms)
 
     def forward(self, ctx, acc, cache) -> None:
         raise NotImplementedError

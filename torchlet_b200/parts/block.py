@@ -11,8 +11,10 @@ from .base import BLOCKS, Block
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
+    norm_roles = ("mixer_norm", "feed_forward_norm")
+
     def forward(self, ctx, acc, cache) -> None:
-        x = self.mixer_norm.forward(ctx, acc)
+        x = self.norms["mixer_norm"].apply(ctx, acc)
         self.mixer.forward(ctx, x, acc, cache)
-        x = self.feed_forward_norm.forward(ctx, acc)
+        x = self.norms["feed_forward_norm"].apply(ctx, acc)
         self.feed_forward.forward(ctx, x, acc)

@@ -38,12 +38,13 @@ class Linear:
         return ops.gemm_tc_deferred(x, self.weight)
 
     def accumulate_later(self, ctx, x: torch.Tensor, acc: torch.Tensor) -> bool:
-        """acc += x W^T + b, with the final sum left to the next norm (``ctx.pending``).
+        """acc += x W^T + b, with the final sum left to whoever reads ``acc`` next
+        (``ctx.leave_pending``: the next norm, or ``ctx.flush_pending``).
         False: not applicable, nothing was done."""
         result = self.deferred(ctx, x)
         if result is None:
             return False
-        ctx.pending = (result[0], result[1], self.bias, acc)
+        ctx.leave_pending(result[0], result[1], self.bias, acc)
         return True
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, accumulate: bool = False) -> None:

@@ -25,24 +25,21 @@ class ExecutionCacheNeed:
     state: Optional[StateSpec]
 
 
-def _layer_part_prefixes(prefix: str) -> dict:
-    return {
-        "mixer": prefix + "self_attn.",
-        "feed_forward": prefix + "mlp.",
-        "mixer_norm": prefix + "input_layernorm.",
-        "feed_forward_norm": prefix + "post_attention_layernorm.",
-    }
+def _layer_parts(layer) -> list:
+    """(registry, part description, full tensor-name prefix, role) of every part of a layer, in the
+    order their tensors are listed and loaded.  The names come from the layer's description."""
+    parts = [(NORMS, slot.part, layer.prefix + slot.prefix, slot.role) for slot in layer.norms]
+    parts.insert(min(1, len(parts)), (MIXERS, layer.mixer, layer.prefix + layer.mixer_prefix, "mixer"))
+    parts.append((FEED_FORWARDS, layer.feed_forward, layer.prefix + layer.feed_forward_prefix, "feed_forward"))
+    return parts
 
 
 def expected_tensors(spec: ModelSpec) -> list[TensorSpec]:
     """Every tensor the checkpoint must hold, by name, with its shape."""
     out = [TensorSpec(spec.embedding_name, (spec.vocab_size, spec.hidden_size))]
     for layer in spec.layers:
-        pre = _layer_part_prefixes(layer.prefix)
-        out += NORMS.get(layer.mixer_norm.kind).expected_tensors(layer.mixer_norm, pre["mixer_norm"])
-        out += MIXERS.get(layer.mixer.kind).expected_tensors(layer.mixer, pre["mixer"])
-        out += NORMS.get(layer.feed_forward_norm.kind).expected_tensors(layer.feed_forward_norm, pre["feed_forward_norm"])
-        out += FEED_FORWARDS.get(layer.feed_forward.kind).expected_tensors(layer.feed_forward, pre["feed_forward"])
+        for registry, part, prefix, _ in _layer_parts(layer):
+            out += registry.get(part.kind).expected_tensors(part, prefix)
     out += NORMS.get(spec.final_norm.kind).expected_tensors(spec.final_norm, spec.final_norm_prefix)
     out.append(TensorSpec(spec.lm_head_name, (spec.vocab_size, spec.hidden_size), optional=spec.tie_word_embeddings))
     return out
@@ -55,12 +52,14 @@ class LayeredModel:
         self.blocks = []
         for layer in spec.layers:
             block_cls = BLOCKS.get(layer.block)
+            missing = [role for role in block_cls.norm_roles if role not in {slot.role for slot in layer.norms}]
+            if missing:
+                raise ValueError(f"layer {layer.prefix!r}: the arrangement {layer.block!r} needs norms for {missing}")
             self.blocks.append(
                 block_cls(
                     build_part(MIXERS, layer.mixer),
                     build_part(FEED_FORWARDS, layer.feed_forward),
-                    build_part(NORMS, layer.mixer_norm),
-                    build_part(NORMS, layer.feed_forward_norm),
+                    {slot.role: build_part(NORMS, slot.part) for slot in layer.norms},
                 )
             )
         self.final_norm = build_part(NORMS, spec.final_norm)
@@ -90,11 +89,9 @@ class LayeredModel:
         self.device, self.dtype = torch.device(device), dtype
         self.embedding = tensors[spec.embedding_name].to(device=device, dtype=dtype).contiguous()
         for layer, block in zip(spec.layers, self.blocks):
-            pre = _layer_part_prefixes(layer.prefix)
-            block.mixer_norm.load(tensors, pre["mixer_norm"], device, dtype)
-            block.mixer.load(tensors, pre["mixer"], device, dtype)
-            block.feed_forward_norm.load(tensors, pre["feed_forward_norm"], device, dtype)
-            block.feed_forward.load(tensors, pre["feed_forward"], device, dtype)
+            for _, _, prefix, role in _layer_parts(layer):
+                part = {"mixer": block.mixer, "feed_forward": block.feed_forward}.get(role) or block.norms[role]
+                part.load(tensors, prefix, device, dtype)
         self.final_norm.load(tensors, spec.final_norm_prefix, device, dtype)
         if spec.tie_word_embeddings:
             self.lm_head = Linear.from_device_weight(self.embedding)
@@ -113,5 +110,5 @@ class LayeredModel:
 
     def logits(self, ctx, acc: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
         """Float32 logits of the stream rows ``rows`` (int32) into ``out`` [len(rows), vocab]."""
-        x = self.final_norm.forward(ctx, acc, rows=rows, name="final.normed")
+        x = self.final_norm.apply(ctx, acc, rows=rows, name="final.normed")
         self.lm_head.forward(x, out)

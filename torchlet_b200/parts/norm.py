@@ -24,18 +24,19 @@ class RMSNorm(Norm):
     def load(self, tensors: dict, prefix: str, device, dtype) -> None:
         self.weight = tensors[prefix + "weight"].to(device=device, dtype=torch.float32).contiguous()
 
+    fuses_pending = True  # a product's unfinished sum into the stream is completed in the norm's own kernel
+
     def forward(self, ctx, acc, out=None, rows=None, name="normed"):
         """Normed rows of the float32 stream ``acc`` in the compute dtype; ``rows``
         (int32) selects and orders the rows, default all."""
         count = acc.shape[0] if rows is None else rows.numel()
         if out is None:
             out = ctx.buffer(name, (count, self.size), ctx.dtype)
-        pending = ctx.pending
-        if pending is not None and pending[3] is acc and rows is None and out.dtype == torch.bfloat16:
-            # a product left its last sum into ``acc`` to us: finish it and norm in one kernel
-            ctx.pending = None
-            ops.finish_accum_norm(pending[0], pending[1], pending[2], acc, self.weight, self.eps, out)
-            return out
+        if rows is None and out.dtype == torch.bfloat16:
+            pending = ctx.take_pending(acc)
+            if pending is not None:  # finish the sum and norm in one kernel
+                ops.finish_accum_norm(pending.partials, pending.splits, pending.bias, acc, self.weight, self.eps, out)
+                return out
         ctx.flush_pending()
         ops.rms_norm(acc, self.weight, self.eps, out, rows)
         return out

@@ -3,10 +3,8 @@ y1 = x1 cos - x2 sin, y2 = x2 cos + x1 sin, angle = position * theta^(-2i/d),
 angles and rotation in float32 (v10_triton_paged_gqa/layer/rope.py:18-69,
 kernel/rope.py:21-41).
 
-A position encoding used by an attention mixer implements ``encode_and_store``:
-encode the q and k heads of the fused ``qkv`` rows in place as it needs, and write the
-k and v heads to the cache pages of each token when the cache is writable.  The write
-is fused here because the encoded key never needs to exist anywhere else.
+This encoding writes the k and v heads to the cache pages of each token in the same pass
+(``stores_kv``): the encoded key never needs to exist anywhere else.
 """
 from __future__ import annotations
 
@@ -33,6 +31,7 @@ class RotarySplitHalf(Positions):
         self.inv_freq = (1.0 / (self.theta ** (i / self.head_dim))).to(device)
 
     accepts_partials = True
+    stores_kv = True
 
     def encode_and_store(self, ctx, qkv, num_heads, num_kv_heads, cache, partials=None) -> None:
         """``partials``: (float32 split sums, splits, bias) of the qkv product when the
