@@ -33,18 +33,6 @@ QWEN25_7B = {
 }
 
 
-def build_model(cfg: dict, layers: int, seed: int):
-    from torchlet_b200.benchmarks.common import build_model as build
-
-    return build(cfg, layers, seed)
-
-
-def fill_context(runner, ids, context: int, seed: int) -> None:
-    from torchlet_b200.benchmarks.common import fill_context as fill
-
-    fill(runner, ids, context, seed)
-
-
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
 
 
@@ -64,48 +52,71 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+    """Samples nvidia-smi clocks and throttle reasons.  It is started before the warm-up (the
+    tool needs a moment to come up) and told when the timed region begins and ends; the record
+    is made of the samples that fall inside the region, or, if the region was shorter than three
+    sampling periods, of the samples since the warm-up began (the GPU was under the same load)."""
 
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+    PERIOD_MS = 20
 
     def __init__(self):
         self.proc = None
+        self.begin = self.end = None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms",
+                 str(self.PERIOD_MS)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
 
+    def mark_begin(self):
+        self.begin = time.time()
+
+    def mark_end(self):
+        self.end = time.time()
+
     def stop(self):
         if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"], "samples": 0}
+        if self.end is None:
+            self.mark_end()
+        time.sleep(2 * self.PERIOD_MS / 1e3)  # let the last sample of the region be written
         self.proc.terminate()
         try:
             out, _ = self.proc.communicate(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
             out, _ = self.proc.communicate()
-        clocks, max_clock, reasons = [], None, set()
+        import datetime
+
         names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        samples = []  # (seconds since the epoch or None, clock, reasons)
+        max_clock = None
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
-            if len(parts) < 6:
+            if len(parts) < 7:
                 continue
             try:
-                clocks.append(float(parts[0]))
-                max_clock = float(parts[1])
+                clock, max_clock = float(parts[1]), float(parts[2])
             except ValueError:
                 continue
-            for name, value in zip(names, parts[2:6]):
-                if value.lower().startswith("active"):
-                    reasons.add(name)
-        clocks.sort()
-        median = clocks[len(clocks) // 2] if clocks else None
-        return {"sm_mhz": median, "sm_max_mhz": max_clock, "reasons": sorted(reasons), "samples": len(clocks)}
+            try:
+                when = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+            except ValueError:
+                when = None
+            samples.append((when, clock, {n for n, v in zip(names, parts[3:7]) if v.lower().startswith("active")}))
+        inside = [x for x in samples if x[0] is not None and self.begin is not None and self.begin <= x[0] <= self.end]
+        used, span = (inside, "timed region") if len(inside) >= 3 else (samples, "warm-up and timed region")
+        clocks = sorted(x[1] for x in used)
+        reasons = set().union(*[x[2] for x in used]) if used else set()
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": max_clock,
+                "reasons": sorted(reasons), "samples": len(clocks), "samples_in_timed_region": len(inside),
+                "span": span, "period_ms": self.PERIOD_MS}
 
 
 def model_numbers(cfg: dict, layers: int):
@@ -131,6 +142,7 @@ def time_decode(model, batch: int, context: int, steps: int, warmup: int, clock=
     import torch
 
     from torchlet_b200 import ops
+    from torchlet_b200.benchmarks import common
     from torchlet_b200.config import EngineConfig
     from torchlet_b200.engine import ModelRunner, StepEntry
     from torchlet_b200.sampling import SampleSpec
@@ -141,7 +153,7 @@ def time_decode(model, batch: int, context: int, steps: int, warmup: int, clock=
                           max_num_blocks=batch * (-(-context // page)) + 1, max_num_batched_tokens=2048)
     runner = ModelRunner(model, config)
     ids = [f"d{i}" for i in range(batch)]
-    fill_context(runner, ids, start_len, seed=17)
+    common.fill_context(runner, ids, start_len, seed=17)
     vocab = model.spec.vocab_size
     generator = torch.Generator().manual_seed(batch)
     tokens = torch.randint(0, vocab, (steps + warmup, batch), generator=generator).tolist()
@@ -150,18 +162,22 @@ def time_decode(model, batch: int, context: int, steps: int, warmup: int, clock=
         entries = [StepEntry(rid, [tokens[k][i]], sample=SampleSpec(0.0, i, k)) for i, rid in enumerate(ids)]
         return runner.run(entries)
 
+    if clock:
+        clock.start()
     for k in range(warmup):
         step(k)
     torch.cuda.synchronize()
     begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches = ops.launch_count
     if clock:
-        clock.start()
+        clock.mark_begin()
     begin.record()
     for k in range(warmup, warmup + steps):
         step(k)
     end.record()
     torch.cuda.synchronize()
+    if clock:
+        clock.mark_end()
     stats = clock.stop() if clock else None
     ms = begin.elapsed_time(end)
     launches = ops.launch_count - launches
@@ -399,12 +415,13 @@ def main() -> int:
     import torch
 
     from torchlet_b200 import ops
+    from torchlet_b200.benchmarks import common
 
     cfg = QWEN25_7B
     layers = args.layers or cfg["num_hidden_layers"]
     peaks, peak_source = load_peaks()
     read_params, kv_per_token, prefill_flops = model_numbers(cfg, layers)
-    model = build_model(cfg, layers, seed=4)
+    model = common.build_model(cfg, layers, seed=4)
 
     clock = ClockSampler()
     main_run = time_decode(model, args.batch, args.context, args.steps, args.warmup, clock)

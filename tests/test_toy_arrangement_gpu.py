@@ -258,7 +258,7 @@ def test_a_model_whose_every_mixer_keeps_only_state(tmp_path):
     cut by a small token budget, one request preempted in mid-flight and recomputed: the
     greedy outputs equal the plain implementation's."""
     from torchlet_b200.config import EngineConfig
-    from torchlet_b200.engine import Engine
+    from torchlet_b200.engine.engine import Engine
     from torchlet_b200.engine.loading import load_model
     from torchlet_b200.engine.scheduler import Request
     from torchlet_b200.sampling import SamplingParams
