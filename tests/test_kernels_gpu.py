@@ -246,11 +246,22 @@ def test_attention_mma(case):
     singles = [r for r, q in enumerate(q_lens) if q == 1]
     if singles and group <= 16:
         rows = torch.tensor([sum(q_lens[:r]) for r in singles])
-        for splits in (1, 3, 8):
+        # the grid holds up to ``splits`` CTAs for a request's keys; a request uses as many as its length
+        # warrants; the split that finishes last merges them, or (the other mode) a second kernel does
+        for splits, in_kernel in ((1, True), (3, True), (8, True), (3, False), (8, False), (64, True)):
             out2 = torch.zeros_like(out)
-            ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(singles), None,
-                              len(singles), out2, x["T"], nh, nkv, d, page, window, scale, rows16=True, splits=splits)
-            assert (out2.float().cpu()[rows] - want[rows]).abs().max() <= 1.5e-2 * want.abs().max()
+            saved, ops._merge_in_kernel = ops._merge_in_kernel, in_kernel
+            try:
+                for _ in range(2):  # twice: the arrival counters must be zero again after a launch
+                    out2.zero_()
+                    ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(singles), None,
+                                      len(singles), out2, x["T"], nh, nkv, d, page, window, scale, rows16=True,
+                                      splits=splits)
+                    assert (out2.float().cpu()[rows] - want[rows]).abs().max() <= 1.5e-2 * want.abs().max()
+            finally:
+                ops._merge_in_kernel = saved
+        counters = ops._arrival_counters.get(x["qkv"].device)
+        assert counters is None or int(counters.abs().max()) == 0
 
 
 @pytest.mark.parametrize("kernel", ["generic_f32", "generic_bf16", "mma"])

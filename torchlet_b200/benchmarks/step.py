@@ -1,6 +1,7 @@
 """What each kernel class costs inside the running decode step.
 
     python -m torchlet_b200.benchmarks.step [--batch 8] [--context 4096] [--steps 64] [--layers 28]
+                                            [--max-seq-len N] [--only-full]
 
 Builds a model of Qwen2.5-7B layer sizes with random bfloat16 weights, gives ``batch``
 requests a cached context of random keys and values, and times the decode step (CUDA events
@@ -23,10 +24,13 @@ from .common import QWEN25_7B, build_model, fill_context
 CLASSES = ("attention_mma", "finish_accum_norm", "finish_qkv_rope")
 
 
-def time_step(model, batch: int, context: int, steps: int, warmup: int = 4) -> float:
-    """Microseconds of one decode step of ``batch`` requests near ``context`` cached tokens."""
+def time_step(model, batch: int, context: int, steps: int, warmup: int = 4, max_seq_len=None) -> float:
+    """Microseconds of one decode step of ``batch`` requests near ``context`` cached tokens.
+    ``max_seq_len``: the engine's length limit (default: the context), which the captured decode
+    graph is planned for."""
     page = 16
-    config = EngineConfig(dtype="bfloat16", max_decode_slots=batch, kv_block_size=page, max_seq_len=context,
+    config = EngineConfig(dtype="bfloat16", max_decode_slots=batch, kv_block_size=page,
+                          max_seq_len=max_seq_len or context,
                           max_num_blocks=batch * (-(-context // page)) + 1, max_num_batched_tokens=2048)
     runner = ModelRunner(model, config)
     ids = [f"d{i}" for i in range(batch)]
@@ -58,16 +62,19 @@ def main(argv=None) -> int:
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--layers", type=int, default=28)
+    parser.add_argument("--max-seq-len", type=int, default=None,
+                        help="the engine's length limit, if it is to differ from the context")
+    parser.add_argument("--only-full", action="store_true", help="time the step as it is and stop")
     args = parser.parse_args(argv)
     model = build_model(QWEN25_7B, args.layers, seed=4)
-    full = time_step(model, args.batch, args.context, args.steps)
-    print(f"batch {args.batch}, context {args.context}, {args.layers} layers")
+    full = time_step(model, args.batch, args.context, args.steps, max_seq_len=args.max_seq_len)
+    print(f"batch {args.batch}, context {args.context}, {args.layers} layers, length limit {args.max_seq_len or args.context}")
     print(f"{'full step':32s} {full:9.1f} us")
-    for name in CLASSES:
+    for name in () if args.only_full else CLASSES:
         original = getattr(ops, name)
         setattr(ops, name, lambda *a, **k: None)
         try:
-            without = time_step(model, args.batch, args.context, args.steps)
+            without = time_step(model, args.batch, args.context, args.steps, max_seq_len=args.max_seq_len)
         finally:
             setattr(ops, name, original)
         print(f"{'without ' + name:32s} {without:9.1f} us   {name} costs {full - without:7.1f} us a step, "

@@ -59,6 +59,7 @@ struct Params {
   long long out_stride;
   float* part_acc;  // [tiles*nh][splits][D]   (splits > 1: decode tiles of one token each)
   float* part_ml;   // [tiles*nh][splits][2]
+  int* arrivals;    // [tiles*nkv] zero between launches: splits of a (tile, KV head) that have written (null: a second kernel merges)
   int nh, nkv, page_size, window, splits;
   int page_shift;  // log2(page_size) when it is a power of two, else -1
   int overlap_max_tiles;  // host only: overlapped launch up to this many row tiles
@@ -173,6 +174,14 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
   }
 }
 
+// Key splits a request really uses out of the ``splits`` CTAs the grid holds for it: no split
+// shorter than two key tiles (128 keys).  The grid is sized on the host for the longest request it
+// may meet (under a CUDA graph: the longest the engine allows); a request's own count follows from
+// its length on the device, and the CTAs beyond it leave at once.
+__device__ __forceinline__ int effective_splits(int splits, int key_tiles) {
+  return min(splits, max(1, (key_tiles + 1) >> 1));
+}
+
 // STAGES: key/value tiles in shared memory; 2, or 3 with the TMA loader where the grid leaves
 // room for only two CTAs an SM anyway.
 template <int D, bool ROWS16, bool TMA, int STAGES>
@@ -223,6 +232,24 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
     tl::pdl_wait();
     return;
   }
+  const int first_tok = row_start / g, last_tok = (row_end - 1) / g;
+  const int hi_key = before + last_tok;  // last key any row of the tile may see
+  int lo_key = 0;
+  if (p.window > 0) lo_key = max(0, before + first_tok - p.window + 1);
+
+  // key tiles of this CTA
+  int tile_begin = lo_key / BLOCK_N, tile_end = hi_key / BLOCK_N + 1;
+  int my_splits = 1;
+  if (p.splits > 1) {
+    my_splits = effective_splits(p.splits, tile_end - tile_begin);
+    if (split >= my_splits) {  // the request is too short to need this CTA
+      tl::pdl_wait();
+      return;
+    }
+    const int per = (tile_end - tile_begin + my_splits - 1) / my_splits;
+    tile_begin = tile_begin + split * per;
+    tile_end = min(tile_end, tile_begin + per);
+  }
   if constexpr (TMA) {
     if (threadIdx.x == 0) {
       for (int i = 0; i < STAGES; ++i) tc::mbar_init(&full[i], 1);
@@ -231,18 +258,6 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       tc::prefetch_tensormap(&map_kv);
     }
     __syncthreads();
-  }
-  const int first_tok = row_start / g, last_tok = (row_end - 1) / g;
-  const int hi_key = before + last_tok;  // last key any row of the tile may see
-  int lo_key = 0;
-  if (p.window > 0) lo_key = max(0, before + first_tok - p.window + 1);
-
-  // key tiles of this CTA
-  int tile_begin = lo_key / BLOCK_N, tile_end = hi_key / BLOCK_N + 1;
-  if (p.splits > 1) {
-    const int per = (tile_end - tile_begin + p.splits - 1) / p.splits;
-    tile_begin = tile_begin + split * per;
-    tile_end = min(tile_end, tile_begin + per);
   }
 
   // ---- key/value tiles that earlier steps wrote may be requested before the wait
@@ -498,6 +513,64 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
         p.out[(size_t)token * p.out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / l);
       }
     }
+    if (p.splits > 1 && p.arrivals) {
+      // The split that writes last merges all of them: no second kernel.  The last CTA reads the
+      // others' partial results from the L2.
+      __shared__ int last_to_arrive;
+      __syncthreads();  // every thread's partial results are written ...
+      int* counter = p.arrivals + (size_t)blockIdx.x * p.nkv + kvh;
+      if (threadIdx.x == 0) {
+        int ticket;  // ... and released to the GPU by the arrival itself; the last one acquires the others'
+        asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], 1;" : "=r"(ticket) : "l"(counter) : "memory");
+        last_to_arrive = ticket == my_splits - 1;
+        if (last_to_arrive) *counter = 0;  // zero again for the next launch
+      }
+      __syncthreads();
+      if (last_to_arrive) {
+        // Four output elements a thread and pass.  A thread asks for every split's (max, sum) of its
+        // head and for every split's four sums at once (one round trip to the L2), then weighs them.
+        for (int i = threadIdx.x; i < g * (D / 4); i += THREADS) {
+          const int r = i / (D / 4), c = (i % (D / 4)) * 4;
+          const size_t item = ((size_t)blockIdx.x * p.nh + kvh * g + r) * p.splits;
+          const float2* ml = reinterpret_cast<const float2*>(p.part_ml) + item;
+          const float4* src = reinterpret_cast<const float4*>(p.part_acc + item * D + c);
+          float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+          float m_ref = -INFINITY, l = 0.f;
+          for (int sp = 0; sp < my_splits; sp += 16) {
+            float4 v[16];
+            float2 w[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const bool used = sp + j < my_splits;
+              w[j] = used ? __ldcg(ml + sp + j) : make_float2(-INFINITY, 0.f);
+              v[j] = used ? __ldcg(src + (size_t)(sp + j) * (D / 4)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+            float m_new = m_ref;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) m_new = fmaxf(m_new, w[j].x);
+            const float m_use = m_new == -INFINITY ? 0.f : m_new;
+            const float corr = exp2f(m_ref - m_use);  // 0 in the first round
+            acc.x *= corr; acc.y *= corr; acc.z *= corr; acc.w *= corr;
+            l *= corr;
+            m_ref = m_new;
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float f = exp2f(w[j].x - m_use);  // exp2(-inf) = 0 for the unused ones
+              l = fmaf(w[j].y, f, l);
+              acc.x = fmaf(v[j].x, f, acc.x);
+              acc.y = fmaf(v[j].y, f, acc.y);
+              acc.z = fmaf(v[j].z, f, acc.z);
+              acc.w = fmaf(v[j].w, f, acc.w);
+            }
+          }
+          const float inv = 1.f / l;
+          uint2 packed;
+          packed.x = pack_bf16(acc.x * inv, acc.y * inv);
+          packed.y = pack_bf16(acc.z * inv, acc.w * inv);
+          *reinterpret_cast<uint2*>(p.out + (size_t)tok0 * p.out_stride + (size_t)(kvh * g + r) * D + c) = packed;
+        }
+      }
+    }
   } else {
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
@@ -514,21 +587,29 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
   }
 }
 
-// Merges the key splits of every (decode tile, head): one block of D threads each, thread c
-// owning output element c.  The first threads turn each split's max into its weight.  Only the
-// rows of the tiles' own tokens are written.
+// Merges the key splits of every (decode tile, head) in a kernel of its own (used when the caller
+// gives no arrival counters): one block of D threads each, thread c owning output element c.  The
+// first threads turn each split's max into its weight.  Only the rows of the tiles' own tokens
+// are written.
 template <int D>
 __global__ void __launch_bounds__(D)
 attention_combine_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
                          const int* __restrict__ tile_req, const int* __restrict__ req_indptr,
-                         __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int splits) {
+                         const int* __restrict__ kv_before, int window,
+                         __nv_bfloat16* __restrict__ out, long long out_stride, int nh, int grid_splits) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
 
   __shared__ float weight[64];
   __shared__ float total[2];
   const int item = blockIdx.x, c = threadIdx.x;
-  const float* ml = part_ml + (size_t)item * splits * 2;
+  const int tile = item / nh, head = item % nh;
+  const int req = tile_req ? tile_req[tile] : tile;
+  // the splits this request used: as the attention kernel counted them
+  const int hi_key = kv_before[req];
+  const int lo_key = window > 0 ? max(0, hi_key - window + 1) : 0;
+  const int splits = effective_splits(grid_splits, hi_key / BLOCK_N + 1 - lo_key / BLOCK_N);
+  const float* ml = part_ml + (size_t)item * grid_splits * 2;
   if (c < 32) {  // splits <= 64: two per lane
     const float m0 = c < splits ? ml[2 * c] : -INFINITY;
     const float m1 = c + 32 < splits ? ml[2 * (c + 32)] : -INFINITY;
@@ -543,7 +624,7 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
     if (c == 0) total[0] = l;
   }
   __syncthreads();
-  const float* src = part_acc + (size_t)item * splits * D + c;
+  const float* src = part_acc + (size_t)item * grid_splits * D + c;
   float acc = 0.f;
   int s = 0;
   for (; s + 8 <= splits; s += 8) {
@@ -554,8 +635,7 @@ attention_combine_kernel(const float* __restrict__ part_acc, const float* __rest
     for (int j = 0; j < 8; ++j) acc = fmaf(v[j], weight[s + j], acc);
   }
   for (; s < splits; ++s) acc = fmaf(src[(size_t)s * D], weight[s], acc);
-  const int tile = item / nh, head = item % nh;
-  const int token = req_indptr[tile_req ? tile_req[tile] : tile];
+  const int token = req_indptr[req];
   out[(size_t)token * out_stride + (size_t)head * D + c] = __float2bfloat16_rn(acc / total[0]);
 }
 
@@ -682,16 +762,19 @@ int tl_attention_mma_error() {
 // ``splits`` CTAs (decode); else tiles of 64 packed rows (prompt portions), splits = 1.
 // With splits > 1 every tile is a request that brings ONE token (tile_row null, at most 16
 // query heads a KV head); the workspace holds tiles * nh * splits * (d + 2) floats, and only
-// the output rows of those tokens are written.
+// the output rows of those tokens are written.  ``splits`` is what the grid provides; a request
+// uses as many of them as its length warrants.  ``arrivals``: tiles * nkv ints, zero before the
+// call and zero again after it: the split that finishes last merges (one kernel); null: a second
+// kernel merges.
 // pages: one cache layer [num_pages][2][nkv][page_size][d].
 int tl_attention_mma(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
                      int table_width,
                      const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
                      int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
                      int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
-                     cudaStream_t stream) {
+                     int* arrivals, cudaStream_t stream) {
   if (tiles <= 0 || tokens <= 0) return 0;
-  if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 2)
+  if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 4)
     return TL_ERR_UNSUPPORTED;
   if (splits < 1 || (!rows16 && splits != 1) || nkv > 65535 || splits > 64) return TL_ERR_UNSUPPORTED;
   if (splits > 1 && (tile_row || nh / nkv > 16)) return TL_ERR_UNSUPPORTED;
@@ -710,6 +793,7 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   p.out_stride = out_stride;
   p.part_acc = (float*)workspace;
   p.part_ml = p.part_acc + (size_t)tiles * nh * splits * d;
+  p.arrivals = splits > 1 ? arrivals : nullptr;
   p.nh = nh;
   p.nkv = nkv;
   p.page_size = page_size;
@@ -722,14 +806,14 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   p.scale_log2 = scale * 1.4426950408889634f;
   const int rc = d == 128 ? launch_for<128>(p, num_pages, tiles, rows16 != 0, stream)
                            : launch_for<64>(p, num_pages, tiles, rows16 != 0, stream);
-  if (rc || splits == 1) return rc;
+  if (rc || splits == 1 || arrivals) return rc;
   const int items = tiles * nh;
   if (d == 128)
     tl::launch_kernel(attention_combine_kernel<128>, items, 128, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
-                      p.out, out_stride, nh, splits);
+                      kv_before, window, p.out, out_stride, nh, splits);
   else
     tl::launch_kernel(attention_combine_kernel<64>, items, 64, 0, stream, p.part_acc, p.part_ml, tile_req, req_indptr,
-                      p.out, out_stride, nh, splits);
+                      kv_before, window, p.out, out_stride, nh, splits);
   return TL_LAUNCH_CHECK();
 }
 

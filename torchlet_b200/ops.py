@@ -8,6 +8,7 @@ a kernel refuses, or a missing library is an error here.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
@@ -56,7 +57,7 @@ _SIGNATURES = {
     "attention_mma": {
         "tl_attention_mma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                             c_int, c_int, c_void_p, c_longlong, c_void_p],
+                             c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p],
         "tl_attention_mma_error": [],
     },
     "decode_fused": {
@@ -360,23 +361,49 @@ def wait_selftest(code: int = 99) -> None:
     _check(_fn("gemm_tc", "tl_gemm_tc_wait_selftest")(code, _stream()), "wait_selftest")
 
 
+_arrival_counters: dict = {}
+_outgrown_counters: list = []  # kept alive: captured CUDA graphs may still hold their addresses
+
+
+def _arrivals(device, count: int) -> torch.Tensor:
+    """Per device, ints that are zero between launches: the decode attention counts the key
+    splits of a (request, KV head) that have finished; the last one merges and zeroes its counter."""
+    counters = _arrival_counters.get(device)
+    if counters is None or counters.numel() < count:
+        if counters is not None:
+            _outgrown_counters.append(counters)
+        counters = torch.zeros(max(count, 4096), dtype=torch.int32, device=device)
+        _arrival_counters[device] = counters
+    return counters
+
+
+# TORCHLET_B200_DECODE_MERGE=kernel: a second kernel merges the key splits (for measurements)
+_merge_in_kernel = os.environ.get("TORCHLET_B200_DECODE_MERGE", "") != "kernel"
+
+
 def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, tokens, nh, nkv,
                   d, page_size, window, scale, rows16: bool, splits: int = 1) -> None:
     """Tensor-core paged attention (csrc/attention_mma.cu).  ``tile_req``/``tile_row`` None:
     tile i is request i from its first packed row.  With ``splits`` > 1 every tile is a request
-    that brings one token; only those tokens' rows of ``out`` are written."""
+    that brings one token; only those tokens' rows of ``out`` are written.  ``splits`` is the
+    number of CTAs the grid holds for a request's keys; the kernel uses as many as the request's
+    own length warrants."""
     _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16
-    # key splits: float32 partial results of every (decode tile, head, split), merged by a second kernel
+    # key splits: float32 partial results of every (decode tile, head, split); the split that finishes last merges
     need = tiles * nh * splits * (d + 2) * 4 if splits > 1 else 0
     ws = _workspace(("attention", qkv.device), need) if need else None
+    # up to 16 splits the last split to finish merges them inside the kernel (one round of loads;
+    # measured -1 % of a decode step at batch 8 to 32); more are merged by a second kernel, whose
+    # many small CTAs do better than one CTA's two rounds (batch 1 at 4,096 tokens: 32 splits)
+    arrivals = _arrivals(qkv.device, tiles * nkv) if need and _merge_in_kernel and splits <= 16 else None
     code = _fn("attention_mma", "tl_attention_mma")(
         qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),
         block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles,
         out.data_ptr(), out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale),
         1 if rows16 else 0, splits,
-        _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
-    _check(code, "attention_mma", 2 if splits > 1 else 1)
+        _ptr(ws), ws.numel() * 4 if ws is not None else 0, _ptr(arrivals), _stream())
+    _check(code, "attention_mma", 2 if splits > 1 and arrivals is None else 1)
 
 
 def attention_tc_rows(group: int) -> int:
@@ -402,8 +429,13 @@ def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_
 
 
 def attention_mma_error() -> int:
-    """0, or the code a bounded wait of the decode attention's TMA loader left.  Reading clears it."""
-    return _fn("attention_mma", "tl_attention_mma_error")()
+    """0, or the code a bounded wait of the decode attention's TMA loader left.  Reading clears it
+    (and the arrival counters, which a kernel that gave up may have left half counted)."""
+    code = _fn("attention_mma", "tl_attention_mma_error")()
+    if code:
+        for counters in _arrival_counters.values():
+            counters.zero_()
+    return code
 
 
 def attention_tc_error() -> int:

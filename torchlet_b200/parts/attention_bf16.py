@@ -17,14 +17,26 @@ import torch
 
 from .. import ops
 
+import functools
+
 ROWS = 64
-SM_COUNT = 148
 
 
-def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int) -> int:
-    """Key splits of a decode step: as many as fill ONE wave of CTAs (three are resident per
-    SM), but no split shorter than 128 keys and at most 64 splits."""
-    resident = 3 * SM_COUNT
+@functools.lru_cache(maxsize=None)
+def _sm_count(device_index: int) -> int:
+    return torch.cuda.get_device_properties(device_index).multi_processor_count
+
+
+def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int, device=None) -> int:
+    """CTAs the grid of a decode step holds for the keys of one (request, KV head): as many as
+    fill ONE wave (three CTAs are resident per SM), at most 64, and no more than the longest
+    request the step may meet could use at 128 keys a split.  ``max_kv_len`` is that longest
+    length: the step's own longest request, or, where the step is captured in a CUDA graph, the
+    engine's length limit.  How many of them a request really uses is decided on the device from
+    its own length (csrc/attention_mma.cu, ``effective_splits``), so a grid sized for the limit
+    costs a short request nothing but CTAs that leave at once."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    resident = 3 * _sm_count(index)
     room = max(1, resident // max(1, num_requests * num_kv_heads))
     return max(1, min(room, -(-max_kv_len // 128), 64))
 
@@ -75,7 +87,7 @@ def forward(mixer, ctx, qkv, cache, out) -> bool:
                   window=mixer.window, scale=mixer.scale)
     if plan["decode"] is not None:
         tile_req, count = plan["decode"]
-        splits = decode_splits(count, nkv, ctx.max_kv_len)
+        splits = decode_splits(count, nkv, ctx.max_kv_len, qkv.device)
         ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, None,
                           count, rows16=True, splits=splits, **common)
     if plan["prefill"] is not None and use_tc:
