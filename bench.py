@@ -181,14 +181,14 @@ def time_decode(model, batch: int, context: int, steps: int, warmup: int, clock=
     stats = clock.stop() if clock else None
     ms = begin.elapsed_time(end)
     launches = ops.launch_count - launches
-    meta_words = runner._graphs[runner._bucket(batch)]["words"] if runner._graphs else 0
+    h2d_bytes = runner.h2d_bytes_last_step  # the command block of a steady decode step
     mean_context = start_len + warmup + steps / 2
     for rid in ids:
         runner.finish(rid)
     del runner
     torch.cuda.empty_cache()
     return {"ms_per_step": ms / steps, "tok_s": batch * steps / (ms / 1e3), "launches": launches,
-            "h2d_bytes": meta_words * 4, "mean_context": mean_context, "clocks": stats}
+            "h2d_bytes": h2d_bytes, "mean_context": mean_context, "clocks": stats}
 
 
 def time_prefill(model, tokens: int, repeats: int):
@@ -261,11 +261,11 @@ def time_e2e(model, batch: int, context: int, steps: int, warmup: int):
     graph_steps = engine.runner.graph_steps - graph_before
     if produced != batch * steps:
         raise RuntimeError(f"e2e run produced {produced} tokens, expected {batch * steps}")
-    words = engine.runner._graphs[engine.runner._bucket(batch)]["words"] if engine.runner._graphs else 0
+    h2d_bytes = engine.runner.h2d_bytes_last_step  # the command block of a steady decode step
     ahead = engine.steps_ahead
     del llm, engine
     torch.cuda.empty_cache()
-    return {"tok_s": produced / seconds, "ms_per_step": seconds * 1e3 / steps, "h2d_bytes": words * 4,
+    return {"tok_s": produced / seconds, "ms_per_step": seconds * 1e3 / steps, "h2d_bytes": h2d_bytes,
             "d2h_bytes": batch * 4, "graph_steps": graph_steps, "steps_launched_ahead": ahead}
 
 

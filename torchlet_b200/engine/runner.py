@@ -147,6 +147,16 @@ class ModelRunner:
         self._aux_offset = 0
         self._graphs: dict = {}
         self._last_graph_ids: Optional[list] = None  # requests of the last step, if it was a graph decode step
+        # The slot records on the device (csrc/slots.cu): last token, position, sampling counter,
+        # temperature and seed of every slot, and the block tables of all slots.  Captured decode
+        # steps read and advance them; ``_synced`` says which slots' records the device has as the
+        # host knows them: slot -> (request, position, counter, temperature, seed); ``_device_pages``
+        # says how many entries of such a slot's table rows the device has.
+        self._records: Optional[torch.Tensor] = None
+        self._slot_tables: Optional[torch.Tensor] = None
+        self._synced: dict = {}
+        self._device_pages = np.zeros(config.max_decode_slots, dtype=np.int32)
+        self.h2d_bytes_last_step = 0
         self._tokens_host = [None, None]
         self._tokens_event = [None, None]
         self._tokens_turn = 0
@@ -204,12 +214,13 @@ class ModelRunner:
     # -------------------------------------------------------------- requests
     def admit(self, request_id: Hashable) -> int:
         slot = self.cache.admit(request_id)
+        self._synced.pop(slot, None)
         if self.storage.states:
             self.storage.clear_slot(slot)
         return slot
 
     def finish(self, request_id: Hashable) -> None:
-        self.cache.finish(request_id)
+        self._synced.pop(self.cache.finish(request_id), None)
         self._last_graph_ids = None
 
     def reserve(self, request_id: Hashable, new_len: int) -> bool:
@@ -259,6 +270,7 @@ class ModelRunner:
                     ops.sample(rows, tokens, ctx.sample_temperature, ctx.sample_seed, ctx.sample_counter)
         for e in entries:
             self.cache.advance(e.request_id, self.cache.num_tokens(e.request_id) + len(e.tokens))
+            self._synced.pop(self.cache.slot_of(e.request_id), None)  # the device's record of the slot is behind
         self.steps_run += 1
         return StepResult(logits, tokens)
 
@@ -283,20 +295,33 @@ class ModelRunner:
         raise ValueError(n)
 
     def _graph_layout(self, b: int):
-        """Offsets (in int32 words) of the static metadata block of bucket ``b``."""
+        """Offsets (in int32 words) of the static block of bucket ``b``: first the command block
+        the host writes every step (csrc/slots.cu), then the lane-indexed words the kernels read,
+        which the first kernel of the graph fills from the slot records."""
         W, G = self.cache.max_pages_per_request, self.num_groups
-        names = (("tok", b), ("pos", b), ("req", b), ("ind", b + 1), ("kvb", b), ("slot", b), ("row", b),
-                 ("pad", (4 * b + 1 + 3 * b) & 1), ("seed", 2 * b), ("temp", b), ("count", b))
+        capacity = b * max(G, 1)  # table entries a step can add: one a lane and group
+        command = ops.slot_command_words(b, capacity)
+        names = (("command", command), ("pad0", command & 1), ("seed", 2 * b), ("tok", b), ("pos", b), ("req", b),
+                 ("ind", b + 1), ("kvb", b), ("slot", b), ("row", b), ("temp", b), ("count", b))
         layout, o = {}, 0
         for name, size in names:
             layout[name] = (o, size)
             o += size
         layout["tables"] = [(o + g * b * W, b * W) for g in range(G)]
+        layout["capacity"] = capacity
         return layout, o + G * b * W
+
+    def _slot_records(self):
+        if self._records is None:
+            S, W, G = self.config.max_decode_slots, self.cache.max_pages_per_request, self.num_groups
+            self._records = torch.zeros((ops.slot_record_rows(), S), dtype=torch.int32, device=self.device)
+            self._slot_tables = torch.zeros((max(G, 1), S, W), dtype=torch.int32, device=self.device)
+        return self._records, self._slot_tables
 
     def _capture_decode_graph(self, b: int):
         layout, words = self._graph_layout(b)
-        W = self.cache.max_pages_per_request
+        W, G, S = self.cache.max_pages_per_request, self.num_groups, self.config.max_decode_slots
+        records, slot_tables = self._slot_records()
         dev = torch.zeros(words, dtype=torch.int32, device=self.device)
         view = lambda name: dev[layout[name][0]:layout[name][0] + layout[name][1]]
         ctx = StepContext(self)
@@ -314,20 +339,27 @@ class ModelRunner:
         ctx.kv_before_host = np.zeros(b, dtype=np.int32)
         ctx.slots_host = np.zeros(b, dtype=np.int32)
         tables = [dev[o:o + size].view(b, W) for o, size in layout["tables"]]
+        lane_tables = dev[layout["tables"][0][0]:] if G else None
         caches = self.storage.layer_caches(tables)
-        # padding everywhere for the warm-up and the capture
+        # the words that never change, and a command block of padding lanes for warm-up and capture
         host = np.zeros(words, dtype=np.int32)
         host[layout["req"][0]:layout["req"][0] + b] = np.arange(b)
         host[layout["ind"][0]:layout["ind"][0] + b + 1] = np.arange(b + 1)
         host[layout["row"][0]:layout["row"][0] + b] = np.arange(b)
+        host[2:2 + b] = -1
         dev.copy_(torch.from_numpy(host))
+        command = view("command")
         logits = torch.empty((b, self.vocab_size), dtype=torch.float32, device=self.device)
         tokens = torch.empty(b, dtype=torch.int32, device=self.device)
 
         def body():
+            ops.slot_gather(command, b, G, S, W, self.cache.page_size, records, slot_tables, ctx.tokens, ctx.positions,
+                            ctx.kv_before, ctx.slots, ctx.sample_seed, ctx.sample_temperature, ctx.sample_counter,
+                            lane_tables)
             acc = self.model.forward(ctx, caches)
             self.model.logits(ctx, acc, ctx.logit_rows, logits)
             ops.sample(logits, tokens, ctx.sample_temperature, ctx.sample_seed, ctx.sample_counter)
+            ops.slot_advance(command, b, S, tokens, records)
 
         with torch.no_grad():
             side = torch.cuda.Stream(device=self.device)
@@ -341,8 +373,8 @@ class ModelRunner:
             with torch.cuda.graph(graph):
                 body()
             launched = ops.launch_count - launched
-        state = {"kernels": launched, "layout": layout, "words": words, "dev": dev, "graph": graph, "logits": logits, "tokens": tokens,
-                 "template": host}
+        state = {"kernels": launched, "layout": layout, "words": layout["command"][1], "dev": dev, "graph": graph,
+                 "logits": logits, "tokens": tokens}
         self._graphs[b] = state
         return state
 
@@ -371,13 +403,11 @@ class ModelRunner:
         b = self._bucket(n)
         state = self._graphs.get(b) or self._capture_decode_graph(b)
         layout, words = state["layout"], state["words"]
-        W = cache.max_pages_per_request
+        W, S = cache.max_pages_per_request, self.config.max_decode_slots
         ids = [e.request_id for e in entries]
         if len(set(ids)) != n:
             raise ValueError("a request appears twice in one step")
-        if feed_previous:
-            toks = 0  # placeholders; the device copy below puts the sampled tokens in
-        else:
+        if not feed_previous:
             toks = np.fromiter((e.tokens[0] for e in entries), dtype=np.int32, count=n)
             if n and (toks.min() < 0 or toks.max() >= self.vocab_size):
                 raise ValueError(f"token ids must lie in [0, {self.vocab_size})")
@@ -385,34 +415,79 @@ class ModelRunner:
         if not isinstance(room, tuple):
             raise OutOfPages(f"no pages left for request {ids[room]!r}")
         before, slots = room
-        host, _ = self._meta(words)
-        host[:words] = state["template"]
-        put = lambda name, values: host.__setitem__(slice(layout[name][0], layout[name][0] + n), values)
-        put("tok", toks)
-        put("pos", before)
-        put("kvb", before)
-        put("slot", slots)
-        o = layout["seed"][0]
-        host[o:o + 2 * n].view(np.int64)[:] = [e.sample.seed & 0x7FFFFFFFFFFFFFFF for e in entries]
-        o = layout["temp"][0]
-        host[o:o + n].view(np.float32)[:] = [e.sample.temperature for e in entries]
-        put("count", [e.sample.counter for e in entries])
-        for g, (o, size) in enumerate(layout["tables"]):
-            np.take(cache.table_arrays[g], slots, axis=0, out=host[o:o + n * W].reshape(n, W))
+        # which lanes' slots the device holds no current record (and tables) of
+        synced, wants, stale = self._synced, [], []
+        for i, e in enumerate(entries):
+            want = (e.request_id, int(before[i]), e.sample.counter, float(e.sample.temperature),
+                    e.sample.seed & 0x7FFFFFFFFFFFFFFF)
+            wants.append(want)
+            if synced.get(int(slots[i])) != want:
+                stale.append(i)
+        page_size, G = cache.page_size, self.num_groups
+        stale_words = sum(int(before[i]) // page_size + 1 for i in stale) * G
+        # The command block: which slot stands in which lane, and what the device does not know yet.
+        host, _ = self._meta(words + stale_words)
+        command = host[:words]
+        command[:] = 0
+        command[0] = n
+        lanes, flags = command[2:2 + b], command[2 + b:2 + 2 * b]
+        given = command[2 + 2 * b:2 + 8 * b].reshape(6, b)
+        pairs = command[2 + 8 * b:]
+        lanes[:] = -1
+        lanes[:n] = slots
+        for i in stale:
+            _, position, counter, temperature, seed = wants[i]
+            low = seed & 0xFFFFFFFF
+            flags[i] = 1
+            given[1, i], given[2, i] = position, counter
+            given[3, i] = int(np.float32(temperature).view(np.int32))
+            given[4, i], given[5, i] = low - (1 << 32) if low >= 1 << 31 else low, seed >> 32
+        for i, want in enumerate(wants):  # as the step will leave the records
+            synced[int(slots[i])] = (want[0], want[1] + 1, want[2] + 1, want[3], want[4])
+        if not feed_previous:
+            flags[:n] |= 2
+            given[0, :n] = toks
+        bytes_sent = words * 4
+        records, slot_tables = self._slot_records()
         turn = self._meta_turn
-        state["dev"].copy_(self._meta_host[turn][:words], non_blocking=True)
+        device_pages = self._device_pages
+        if stale:  # a slot that is new to the decode set: its whole table rows, by plain copies
+            pinned = self._meta_host[turn]
+            room_at = words
+            for i in stale:
+                slot, used = int(slots[i]), int(before[i]) // page_size + 1
+                for g in range(G):
+                    host[room_at:room_at + used] = cache.table_arrays[g][slot, :used]
+                    slot_tables[g, slot, :used].copy_(pinned[room_at:room_at + used], non_blocking=True)
+                    room_at += used
+                device_pages[slot] = used
+            bytes_sent += stale_words * 4
+        # table entries the lanes' slots have gained since their last step (a new page at most)
+        count = 0
+        used_now = before // page_size + 1
+        for i in np.nonzero(used_now > device_pages[slots])[0]:
+            slot = int(slots[i])
+            for index in range(int(device_pages[slot]), int(used_now[i])):
+                for g in range(G):
+                    if count >= layout["capacity"]:
+                        raise ValueError("more new table entries than a decode step can take")
+                    pairs[2 * count] = (g * S + slot) * W + index
+                    pairs[2 * count + 1] = cache.table_arrays[g][slot, index]
+                    count += 1
+        device_pages[slots] = used_now
+        command[1] = count
+        o = layout["command"][0]
+        state["dev"][o:o + words].copy_(self._meta_host[turn][:words], non_blocking=True)
         if self._meta_event[turn] is None:
             self._meta_event[turn] = torch.cuda.Event()
         self._meta_event[turn].record()
-        if feed_previous:  # the same graph sampled them into its token buffer one step ago
-            o = layout["tok"][0]
-            state["dev"][o:o + n].copy_(state["tokens"][:n])
         state["graph"].replay()
         ops.launch_count += state["kernels"]
         cache.end_decode(ids)
         self._last_graph_ids = ids
         self.steps_run += 1
         self.graph_steps += 1
+        self.h2d_bytes_last_step = bytes_sent
         return StepResult(state["logits"][:n], state["tokens"][:n])
 
     def _build(self, entries):

@@ -73,6 +73,13 @@ _SIGNATURES = {
         "tl_attention_tc_error": [],
         "tl_attention_tc_rows": [c_int],
     },
+    "slots": {
+        "tl_slot_gather": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
+        "tl_slot_advance": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
+        "tl_slot_command_words": [c_int, c_int],
+        "tl_slot_record_rows": [],
+    },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                       c_longlong, c_void_p],
@@ -231,6 +238,38 @@ def sample(logits, out, temperature=None, seed=None, counter=None) -> None:
         logits.data_ptr(), logits.stride(0), rows, vocab, _ptr(temperature), _ptr(seed), _ptr(counter),
         out.data_ptr(), _ptr(scratch), scratch.numel() * 4 if scratch is not None else 0, _stream())
     _check(code, "sample", 2 if chunks > 1 else 1)
+
+
+# ---------------------------------------------------------------- slot records
+def slot_record_rows() -> int:
+    return _fn("slots", "tl_slot_record_rows")()
+
+
+def slot_command_words(lanes: int, capacity: int) -> int:
+    """int32 words of the command block of a decode step (csrc/slots.cu)."""
+    return _fn("slots", "tl_slot_command_words")(lanes, capacity)
+
+
+def slot_gather(command, lanes: int, groups: int, max_slots: int, width: int, page_size: int, records, slot_tables,
+                token, position, kv_before, slot, seed, temperature, counter, lane_tables) -> None:
+    """From the slot records (and the command block's news) to the lane-indexed words a decode
+    step's kernels read: tokens, positions, sampling words, block-table rows."""
+    _need_cuda(command, records, slot_tables, token, position, kv_before, slot, seed, temperature, counter, lane_tables)
+    assert records.dtype == torch.int32 and records.is_contiguous() and records.shape[1] == max_slots
+    assert seed.dtype == torch.int64 and temperature.dtype == torch.float32
+    code = _fn("slots", "tl_slot_gather")(
+        command.data_ptr(), lanes, groups, max_slots, width, page_size, records.data_ptr(), _ptr(slot_tables),
+        token.data_ptr(), position.data_ptr(), kv_before.data_ptr(), slot.data_ptr(), seed.data_ptr(),
+        temperature.data_ptr(), counter.data_ptr(), _ptr(lane_tables), _stream())
+    _check(code, "slot_gather")
+
+
+def slot_advance(command, lanes: int, max_slots: int, sampled, records) -> None:
+    """After sampling: each live lane's slot takes the sampled token, position + 1, counter + 1."""
+    _need_cuda(command, sampled, records)
+    code = _fn("slots", "tl_slot_advance")(command.data_ptr(), lanes, max_slots, sampled.data_ptr(),
+                                           records.data_ptr(), _stream())
+    _check(code, "slot_advance")
 
 
 # ------------------------------------------------------- tensor-core products
