@@ -403,12 +403,28 @@ def main() -> int:
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration (named in config)")
     parser.add_argument("--skip-points", action="store_true", help="leave out prefill, batch 1/64 and e2e")
+    parser.add_argument("--workload", choices=["interleave14b", "stress05b"], default=None,
+                        help="instead of the headline line: the mixed step at Qwen2.5-14B layer sizes, or 256 requests "
+                             "arriving at Qwen2.5-0.5B layer sizes (torchlet_b200/benchmarks/workloads.py)")
     args = parser.parse_args()
     if args.gpus != 1:
         print("bench.py: this engine runs on one GPU only; --gpus must be 1")
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload:
+        from torchlet_b200.benchmarks import workloads
+
+        peaks, peak_source = load_peaks()
+        if args.workload == "interleave14b":
+            record = workloads.interleave14b(layers=args.layers or 48, peaks=peaks)
+            record.update(value=record["tok_s"], unit="tok/s")
+        else:
+            record = workloads.stress05b(layers=args.layers or 24)
+        record.update(n_gpus=1, higher_is_better=True, dtype="bf16", data="synthetic", impl="ours",
+                      peak_source=peak_source, peaks={k: peaks[k] for k in ("hbm_gbs", "bf16_tflops")})
+        print(json.dumps(record))
+        return 0
     if args.warmup < 3:
         args.warmup = 3
 

@@ -35,7 +35,7 @@ def test_embed(dtype):
     assert torch.equal(acc, table.float()[ids.long()])
 
 
-@pytest.mark.parametrize("hidden", [100, 96, 3584])
+@pytest.mark.parametrize("hidden", [100, 96, 3584, 5120, 8192, 8200])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_rms_norm(hidden, dtype):
     ops = _ops()

@@ -247,11 +247,13 @@ int tl_rms_norm(const float* acc, const float* weight, const int* rows, void* ou
   // never depends on the batch
   const bool aligned = ((reinterpret_cast<uintptr_t>(acc) | reinterpret_cast<uintptr_t>(weight)) & 15) == 0 &&
                        (reinterpret_cast<uintptr_t>(out) & 7) == 0;
-  if (out_dtype == TL_DTYPE_BF16 && hidden % 4 == 0 && hidden <= 4096 && aligned) {
+  if (out_dtype == TL_DTYPE_BF16 && hidden % 4 == 0 && hidden <= 8192 && aligned) {
     if (hidden <= 2048)
       tl::launch_kernel(rms_norm_vec_kernel<128>, num_rows, 128, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
-    else
+    else if (hidden <= 4096)
       tl::launch_kernel(rms_norm_vec_kernel<256>, num_rows, 256, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
+    else
+      tl::launch_kernel(rms_norm_vec_kernel<512>, num_rows, 512, 0, stream, acc, weight, rows, (__nv_bfloat16*)out, hidden, eps);
     return TL_LAUNCH_CHECK();
   }
   if (hidden <= 2048) {
