@@ -475,12 +475,13 @@ def test_sampling_over_a_vocabulary_scanned_by_several_blocks():
     ([4000], [300], 28, 4, 64, None, (0, 299, 7)),   # a far key that decides the last token
     ([1100], [150], 12, 4, 16, 300, (0, 20, 830)),   # a key just inside the window of token 1120: 821 and later
 ])
-def test_attention_tc(case):
-    """Prompt-portion attention on tcgen05 (head_dim 128) against the plain formula."""
+@pytest.mark.parametrize("d", [128, 64])
+def test_attention_tc(case, d):
+    """Prompt-portion attention on tcgen05 (head_dim 128 and 64) against the plain formula."""
     ops = _ops()
     before, q_lens, nh, nkv, page, window = case[:6]
     spike = case[6] if len(case) > 6 else None
-    d, group = 128, nh // nkv
+    group = nh // nkv
     assert ops.attention_tc_supported(d, group, page)
     x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=5, spike=spike)
     scale = 0.37 / math.sqrt(d)

@@ -1,5 +1,6 @@
 // Paged causal grouped-query attention for PROMPT PORTIONS on the 5th-generation tensor
-// cores (tcgen05), bfloat16, head_dim 128.
+// cores (tcgen05), bfloat16, head_dim 64 or 128 (a template parameter: an operand tile is one
+// or two 64-element slabs wide).
 //
 // One CTA takes two tiles of up to 128 PACKED ROWS of one (request, KV head): the pairs
 // (token of the step, query head of the KV head's group), token-major, so every key/value
@@ -7,13 +8,13 @@
 // over the keys in tiles of 128 absolute positions:
 //
 //   loader warps    one for K, one for V: TMA-load the tile's pages (one box of page_size x 64
-//                   elements per page and half of the head, 128-byte swizzle, one lane per
-//                   box) through the block table into a two-stage ring;
+//                   elements per page and 64-element slab of the head, 128-byte swizzle, one
+//                   lane per box) through the block table into a two-stage ring;
 //   MMA warp        for each row tile X in turn:  O_X += P_X V of the previous key tile
 //                   (P_X read from tensor memory, V as the MN-major operand from shared
 //                   memory), then S_X = Q_X K^T of this key tile (Q and K K-major in shared
 //                   memory).  S_X, P_X (in the first half of S_X's columns) and O_X live
-//                   in tensor memory: 2 x 128 + 2 x 128 columns, all 512;
+//                   in tensor memory: 2 x 128 + 2 x head_dim columns (all 512 for head_dim 128);
 //   softmax warps   four warps per row tile, one thread per row: read the row of S from
 //                   tensor memory, mask by position, keep the running max and sum in
 //                   float32, write P as bfloat16 over S, and rescale O in tensor memory
@@ -45,13 +46,13 @@ namespace {
 
 using namespace tc;
 
-constexpr int D = 128;          // head_dim
 constexpr int ROWS = 128;       // packed rows of a row tile (UMMA M)
 constexpr int QTILES = 2;       // row tiles a CTA
 constexpr int KEYS = 128;       // keys a tile (UMMA N of S, K of P V)
 constexpr int THREADS = 352;    // warps 0-3 softmax of row tile 0, 4-7 of row tile 1, 8 MMA, 9 and 10 loaders
 constexpr int SLAB = ROWS * 128;  // bytes of a [128 rows][64 bf16] swizzled slab
-constexpr int TILE_BYTES = 2 * SLAB;  // a 128 x 128 bf16 operand tile = two slabs
+// a 128 x D bf16 operand tile = D / 64 slabs
+template <int D> struct TileBytes { static constexpr int value = (D / 64) * SLAB; };
 constexpr float RESCALE_THRESHOLD = 8.f;  // log2 units
 
 __device__ int g_error_word = 0;
@@ -89,11 +90,11 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Instruction descriptor for O += P V: A (P) K-major, B (V) MN-major (bit 16).
-__device__ __forceinline__ uint32_t idesc_pv() { return idesc_bf16_f32(ROWS, D) | (1u << 16); }
+template <int D> __device__ __forceinline__ uint32_t idesc_pv() { return idesc_bf16_f32(ROWS, D) | (1u << 16); }
 
-// Shared-memory descriptor of the MN-major operand V: a tile is two slabs (halves of the
-// head) of [128 keys][64 elements]; 8 keys form a 1024-byte swizzle atom (stride byte
-// offset), the slabs are SLAB bytes apart (leading byte offset).
+// Shared-memory descriptor of the MN-major operand V: a tile is one or two slabs (64 elements
+// of the head each) of [128 keys][64 elements]; 8 keys form a 1024-byte swizzle atom (stride
+// byte offset), the slabs are SLAB bytes apart (leading byte offset).
 __device__ __forceinline__ uint64_t smem_desc_v(uint32_t saddr) {
   uint64_t desc = 0;
   desc |= (uint64_t)((saddr & 0x3FFFF) >> 4);
@@ -154,13 +155,16 @@ struct RowTile {
   int row_start, row_end, begin, end;
 };
 
+template <int D>
 __global__ void __launch_bounds__(THREADS, 1)
 attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) {
+  constexpr int TILE_BYTES = TileBytes<D>::value;
+  constexpr int SLABS = D / 64;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* q_tiles = smem;                      // 2 x 32 KB
-  uint8_t* k_tiles = smem + 2 * TILE_BYTES;     // 2 x 32 KB
-  uint8_t* v_tiles = smem + 4 * TILE_BYTES;     // 2 x 32 KB
+  uint8_t* q_tiles = smem;                      // 2 row tiles
+  uint8_t* k_tiles = smem + 2 * TILE_BYTES;     // 2 stages
+  uint8_t* v_tiles = smem + 4 * TILE_BYTES;     // 2 stages
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + 6 * TILE_BYTES);
   uint64_t* k_full = bars;        // [2 stages]
   uint64_t* v_full = bars + 2;    // [2 stages]
@@ -249,8 +253,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
 
   if (warp >= 9) {
     // ----------------------------------------------------------------- loaders
-    // Warp 9 copies K, warp 10 copies V.  Lane l copies half (l & 1) of page (l >> 1) of every
-    // tile: a box of page_size keys x 64 elements (page_size >= 8, so a tile has at most 16
+    // Warp 9 copies K, warp 10 copies V.  Lane l copies slab (l % SLABS) of page (l / SLABS) of
+    // every tile: a box of page_size keys x 64 elements (page_size >= 8, so a tile has at most 16
     // pages).  The copies of a tile cost their issue, not their bytes: thirty-two issued by
     // one thread take longer than the tile's arithmetic.
     const int is_v = warp - 9;
@@ -258,7 +262,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     uint64_t* full = is_v ? v_full : k_full;
     uint64_t* empty = is_v ? v_empty : k_empty;
     const int pages_per_tile = KEYS / p.page_size;
-    const int my_page = lane >> 1, my_half = lane & 1;
+    const int my_page = lane / SLABS, my_half = lane % SLABS;
     const bool active = my_page < pages_per_tile;
     for (int j = j_begin; j < j_end; ++j) {
       const int jj = j - j_begin, s = jj & 1;
@@ -273,10 +277,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
         tma_load_2d(tiles + offset, &map_kv, &full[s], my_half * 64, ((page * 2 + is_v) * p.nkv + kvh) * p.page_size);
       if (is_v && ((edge_first && j == j_begin) || (edge_last && j == j_end - 1))) {
         mbar_wait(&full[s], phase, abort_flag, &g_error_word, 10);  // the tile has landed
-        for (int i = lane; i < KEYS * 16; i += 32) {  // a key's row: 128 bytes in each of the two slabs
-          const int k = i >> 4, key = j * KEYS + k;
+        for (int i = lane; i < KEYS * SLABS * 8; i += 32) {  // a key's row: 128 bytes in each slab
+          const int k = i / (SLABS * 8), key = j * KEYS + k;
           if (key < cta_lo_key || key > cta_hi_key)
-            *reinterpret_cast<uint4*>(tiles + s * TILE_BYTES + ((i >> 3) & 1) * SLAB + k * 128 + (i & 7) * 16) =
+            *reinterpret_cast<uint4*>(tiles + s * TILE_BYTES + ((i >> 3) % SLABS) * SLAB + k * 128 + (i & 7) * 16) =
                 make_uint4(0u, 0u, 0u, 0u);
         }
         fence_proxy_async();  // the tensor core reads, and later copies overwrite, what these stores wrote
@@ -294,7 +298,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     // wait for its P.  The tiles take turns, which keeps one in its softmax while the other's
     // MMAs run.
     const uint32_t idesc_s = idesc_bf16_f32(ROWS, KEYS);
-    const uint32_t idesc_o = idesc_pv();
+    const uint32_t idesc_o = idesc_pv<D>();
     // Descriptors of the operands' first 16-wide slices; a later slice adds its byte offset / 16
     // to the address field (the tiles lie below 256 KB, so the field never carries).
     const uint64_t q_desc[QTILES] = {smem_desc_sw128(smem_addr(q_tiles)), smem_desc_sw128(smem_addr(q_tiles + TILE_BYTES))};
@@ -463,29 +467,42 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
 struct MapKey {
   const void* base;
   uint64_t rows;
-  uint32_t box_rows;
-  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && box_rows == o.box_rows; }
+  uint32_t cols, box_rows;
+  bool operator==(const MapKey& o) const { return base == o.base && rows == o.rows && cols == o.cols && box_rows == o.box_rows; }
 };
 struct MapKeyHash {
   size_t operator()(const MapKey& k) const {
-    return (reinterpret_cast<size_t>(k.base) * 1000003u ^ k.rows) * 1000003u ^ k.box_rows;
+    return ((reinterpret_cast<size_t>(k.base) * 1000003u ^ k.rows) * 1000003u ^ k.cols) * 1000003u ^ k.box_rows;
   }
 };
 
-bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t box_rows) {
+bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t cols, uint32_t box_rows) {
   static std::unordered_map<MapKey, CUtensorMap, MapKeyHash> cache;
   static std::mutex lock;
-  const MapKey key{base, rows, box_rows};
+  const MapKey key{base, rows, cols, box_rows};
   std::lock_guard<std::mutex> guard(lock);
   auto it = cache.find(key);
   if (it == cache.end()) {
     CUtensorMap map;
-    if (!tc_host::make_map_bf16(&map, base, rows, D, D, box_rows)) return false;
+    if (!tc_host::make_map_bf16(&map, base, rows, cols, cols, box_rows)) return false;
     if (cache.size() > 1024) cache.clear();
     it = cache.emplace(key, map).first;
   }
   *out = it->second;
   return true;
+}
+
+template <int D> int launch(const CUtensorMap& map_kv, const Params& p, int nkv, int tiles, cudaStream_t stream) {
+  constexpr int SMEM = 6 * TileBytes<D>::value + 1024 + 256;
+  static_assert(SMEM <= 232448, "shared memory of one CTA");
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+    if (err != cudaSuccess) return (int)err;
+    configured = true;
+  }
+  tl::launch_kernel(attention_tc_kernel<D>, dim3(nkv, tiles), THREADS, SMEM, stream, map_kv, p);
+  return TL_LAUNCH_CHECK();
 }
 
 }  // namespace
@@ -502,18 +519,18 @@ int tl_attention_tc_error() {
 // Packed rows a CTA takes for a group of ``group`` query heads: two row tiles of whole tokens.
 int tl_attention_tc_rows(int group) { return group > 0 && group <= ROWS ? QTILES * (ROWS / group) * group : 0; }
 
-// pages: one cache layer [num_pages][2][nkv][page_size][128] bf16.  tile_req / tile_row:
+// pages: one cache layer [num_pages][2][nkv][page_size][d] bf16, d 64 or 128.  tile_req / tile_row:
 // request and first packed row (a multiple of tl_attention_tc_rows(nh / nkv)) of each CTA.
 int tl_attention_tc(const void* q, long long q_stride, const void* pages, long long num_pages,
                     const int* block_table, int table_width, const int* req_indptr, const int* kv_before,
                     const int* tile_req, const int* tile_row, int tiles, void* out, long long out_stride, int nh,
                     int nkv, int d, int page_size, int window, float scale, cudaStream_t stream) {
   if (tiles <= 0) return 0;
-  if (d != D || nkv <= 0 || nh % nkv || nh / nkv > ROWS || page_size < 8 || page_size > KEYS || KEYS % page_size ||
-      q_stride % 8 || out_stride % 8 || tiles > 65535 || !tile_req || !tile_row)
+  if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || nh / nkv > ROWS || page_size < 8 || page_size > KEYS ||
+      KEYS % page_size || q_stride % 8 || out_stride % 8 || tiles > 65535 || !tile_req || !tile_row)
     return TL_ERR_UNSUPPORTED;
   CUtensorMap map_kv;
-  if (!cached_map(&map_kv, pages, (uint64_t)num_pages * 2 * nkv * page_size, (uint32_t)page_size))
+  if (!cached_map(&map_kv, pages, (uint64_t)num_pages * 2 * nkv * page_size, (uint32_t)d, (uint32_t)page_size))
     return TL_ERR_UNSUPPORTED;
   Params p;
   p.q = (const __nv_bfloat16*)q;
@@ -532,16 +549,7 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.window = window;
   p.rows_per_tile = tl_attention_tc_rows(nh / nkv) / QTILES;
   p.scale_log2 = scale * 1.4426950408889634f;
-  constexpr int SMEM = 6 * TILE_BYTES + 1024 + 256;
-  static_assert(SMEM <= 232448, "shared memory of one CTA");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
-    if (err != cudaSuccess) return (int)err;
-    configured = true;
-  }
-  tl::launch_kernel(attention_tc_kernel, dim3(nkv, tiles), THREADS, SMEM, stream, map_kv, p);
-  return TL_LAUNCH_CHECK();
+  return d == 128 ? launch<128>(map_kv, p, nkv, tiles, stream) : launch<64>(map_kv, p, nkv, tiles, stream);
 }
 
 }  // extern "C"

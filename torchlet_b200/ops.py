@@ -451,7 +451,7 @@ def attention_tc_rows(group: int) -> int:
 
 
 def attention_tc_supported(d: int, group: int, page_size: int) -> bool:
-    return d == 128 and 1 <= group <= 128 and 8 <= page_size <= 128 and 128 % page_size == 0
+    return d in (64, 128) and 1 <= group <= 128 and 8 <= page_size <= 128 and 128 % page_size == 0
 
 
 def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, nh, nkv, d,

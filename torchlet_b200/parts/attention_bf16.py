@@ -6,9 +6,9 @@ Requests that bring a single token (decode) run in tiles of 16 packed rows with 
 split over several CTAs, so that a few long requests still fill the GPU
 (csrc/attention_mma.cu).  Requests that bring a portion of a prompt run in row tiles planned
 here on the host, as the reference plans its prefill tiles
-(v10_triton_paged_gqa/layer/gqa.py:163-216): for head_dim 128 on the tcgen05 kernel
-(csrc/attention_tc.cu, two row tiles of whole tokens a CTA), else in tiles of 64 packed rows
-on the mma.sync kernel.
+(v10_triton_paged_gqa/layer/gqa.py:163-216): on the tcgen05 kernel (csrc/attention_tc.cu, two
+row tiles of whole tokens a CTA) where the page size suits its TMA boxes (8 to 128 tokens,
+dividing 128), else in tiles of 64 packed rows on the mma.sync kernel.
 """
 from __future__ import annotations
 
@@ -80,7 +80,7 @@ def forward(mixer, ctx, qkv, cache, out) -> bool:
     group = nh // nkv
     if d not in (64, 128) or group > 16 or qkv.stride(0) % 8:
         return False
-    # prompt portions: the tcgen05 kernel for head_dim 128, else the mma.sync kernel
+    # prompt portions: the tcgen05 kernel where it takes the page size, else the mma.sync kernel
     use_tc = (not ctx.decode_only) and ops.attention_tc_supported(d, group, cache.page_size)
     plan = _plan(ctx, group, ops.attention_tc_rows(group) if use_tc else ROWS)
     common = dict(out=out, tokens=ctx.num_tokens, nh=nh, nkv=nkv, d=d, page_size=cache.page_size,
