@@ -30,7 +30,7 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
                          const int* __restrict__ block_table, int table_width,
                          const int* __restrict__ token_req, const int* __restrict__ positions,
                          T* __restrict__ out, int out_stride, int tokens, int nh, int nkv, int d,
-                         int page_size, int window, float scale) {
+                         int page_size, int window, float scale, int num_pages) {
   tl::pdl_wait();               // everything before us in the stream is complete and visible
   tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
@@ -63,7 +63,10 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
     float s = -INFINITY;
     size_t row_off = 0;
     if (valid) {
-      row_off = (size_t)table[key / page_size] * page_elems + (size_t)(key % page_size) * d;
+      int page = 0;  // a key whose table entry fails a debug-build check is read from the reserved page 0
+      if (TL_DEBUG_OK(key / page_size < table_width, TL_DEBUG_POSITION, key)) page = table[key / page_size];
+      if (!TL_DEBUG_OK(page >= 0 && page < num_pages, TL_DEBUG_PAGE, page)) page = 0;
+      row_off = (size_t)page * page_elems + (size_t)(key % page_size) * d;
       const T* krow = pages + row_off + k_off;
       float dot = 0.f;
       for (int i = 0; i < d; i += 8) {
@@ -105,11 +108,13 @@ attention_generic_kernel(const T* __restrict__ q, int q_stride, const T* __restr
 
 }  // namespace
 
+TL_DEBUG_READER(tl_attention_generic_debug_error)
+
 extern "C" int tl_attention_generic(const void* q, int q_stride, const void* pages, int dtype,
                                     const int* block_table, int table_width, const int* token_req,
                                     const int* positions, void* out, int out_stride, int tokens,
                                     int nh, int nkv, int d, int page_size, int window, float scale,
-                                    cudaStream_t stream) {
+                                    int num_pages, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d <= 0 || d > MAX_D || d % 8 || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8)
     return TL_ERR_UNSUPPORTED;
@@ -118,11 +123,11 @@ extern "C" int tl_attention_generic(const void* q, int q_stride, const void* pag
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(attention_generic_kernel<float>, blocks, WARPS * 32, 0, stream, 
         (const float*)q, q_stride, (const float*)pages, block_table, table_width, token_req,
-        positions, (float*)out, out_stride, tokens, nh, nkv, d, page_size, window, scale);
+        positions, (float*)out, out_stride, tokens, nh, nkv, d, page_size, window, scale, num_pages);
   else
     tl::launch_kernel(attention_generic_kernel<__nv_bfloat16>, blocks, WARPS * 32, 0, stream, 
         (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)pages, block_table, table_width,
         token_req, positions, (__nv_bfloat16*)out, out_stride, tokens, nh, nkv, d, page_size, window,
-        scale);
+        scale, num_pages);
   return TL_LAUNCH_CHECK();
 }

@@ -61,6 +61,7 @@ struct Params {
   float* part_ml;   // [tiles*nh][splits][2]
   int* arrivals;    // [tiles*nkv] zero between launches: splits of a (tile, KV head) that have written (null: a second kernel merges)
   int nh, nkv, page_size, window, splits;
+  int num_pages;   // pages in the pool (checked in the debug build)
   int page_shift;  // log2(page_size) when it is a power of two, else -1
   int overlap_max_tiles;  // host only: overlapped launch up to this many row tiles
   float scale_log2;  // scale * log2(e)
@@ -160,7 +161,10 @@ __device__ __forceinline__ void load_kv_tile(const Params& p, const int* table, 
       index = key / p.page_size;
       within = key - index * p.page_size;
     }
-    page[k] = valid ? table[index] : -1;
+    // debug build: a key beyond the table or a page outside the pool is skipped (zero-filled) and recorded
+    const bool in_table = TL_DEBUG_OK(!valid || index < p.table_width, TL_DEBUG_POSITION, key);
+    page[k] = (valid && in_table) ? table[index] : -1;
+    if (page[k] >= 0 && !TL_DEBUG_OK(page[k] < p.num_pages, TL_DEBUG_PAGE, page[k])) page[k] = -1;
     slot[k] = within;
   }
 #pragma unroll
@@ -743,6 +747,8 @@ int launch_for(const Params& p, long long num_pages, int tiles, bool rows16, cud
 
 }  // namespace
 
+TL_DEBUG_READER(tl_attention_mma_debug_error)
+
 extern "C" {
 
 // Bytes of float32 workspace for ``splits`` key splits of ``tiles`` decode tiles.
@@ -797,6 +803,7 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   p.nh = nh;
   p.nkv = nkv;
   p.page_size = page_size;
+  p.num_pages = (int)num_pages;
   p.overlap_max_tiles = 32;
   p.page_shift = -1;
   for (int b = 0; b < 20; ++b)

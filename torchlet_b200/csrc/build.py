@@ -37,6 +37,14 @@ NVCC_FLAGS = [
     "-fvisibility=default",
 ]
 
+# TORCHLET_B200_DEBUG=1: the debug build, whose kernels check the indices they are given (token
+# ids, positions, page ids, slots), record the first bad one and skip the access (common.cuh).
+# Its libraries are built beside the ordinary ones under other names.
+DEBUG_BUILD = os.environ.get("TORCHLET_B200_DEBUG", "") not in ("", "0")
+if DEBUG_BUILD:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DTL_DEBUG"]
+_SUFFIX = ".debug" if DEBUG_BUILD else ""
+
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
@@ -114,15 +122,15 @@ def ensure_built(name: str) -> Path:
     wanted = _source_hash(name)
     candidates = [SOURCE_DIR / "_build", build_dir()]
     for folder in candidates:
-        lib, stamp = folder / f"lib{name}.so", folder / f"lib{name}.hash"
+        lib, stamp = folder / f"lib{name}{_SUFFIX}.so", folder / f"lib{name}{_SUFFIX}.hash"
         try:
             if lib.is_file() and stamp.is_file() and stamp.read_text().strip() == wanted:
                 return lib
         except OSError:
             continue
     folder = build_dir()
-    lib, stamp = folder / f"lib{name}.so", folder / f"lib{name}.hash"
-    tmp = folder / f"lib{name}.{os.getpid()}.tmp.so"
+    lib, stamp = folder / f"lib{name}{_SUFFIX}.so", folder / f"lib{name}{_SUFFIX}.hash"
+    tmp = folder / f"lib{name}{_SUFFIX}.{os.getpid()}.tmp.so"
     cmd = [find_nvcc(), *NVCC_FLAGS, "-I", str(SOURCE_DIR), "-o", str(tmp), str(source)]
     _say(f"compiling {name}.cu for sm_100a ...")
     start = time.time()

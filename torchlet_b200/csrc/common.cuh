@@ -17,6 +17,43 @@
 
 #define TL_LAUNCH_CHECK() ((int)cudaGetLastError())
 
+// ------------------------------------------------------------------ debug build
+// Built with -DTL_DEBUG (environment: TORCHLET_B200_DEBUG=1) the kernels check the indices they
+// are handed before they use them: a token id against the vocabulary, a position against the
+// width of its block table, a page id against the pool, a slot against the slot range.  A check
+// that fails records (code, offending value) in the library's two debug words -- the first
+// failure wins -- and the kernel SKIPS the access, so nothing faults; the host reads the words
+// with the library's tl_<name>_debug_error() and raises.  (The stand-in for a memory checker on
+// machines where none may run.)  Without the flag the checks cost nothing.
+#define TL_DEBUG_TOKEN 1     // token id outside [0, vocabulary)
+#define TL_DEBUG_POSITION 2  // position beyond the request's block table
+#define TL_DEBUG_PAGE 3      // page id outside [0, pages in the pool)
+#define TL_DEBUG_SLOT 4      // slot outside [0, slots)
+#ifdef TL_DEBUG
+__device__ int g_tl_debug_words[2] = {0, 0};
+#define TL_DEBUG_OK(condition, code, value) tl_debug_ok((condition), (code), (int)(value))
+__device__ __forceinline__ bool tl_debug_ok(bool condition, int code, int value) {
+  if (!condition && atomicCAS(&g_tl_debug_words[0], 0, code) == 0) g_tl_debug_words[1] = value;
+  return condition;
+}
+// Defines the library's reader: returns the code (0: none) and stores the value; reading clears.
+#define TL_DEBUG_READER(name)                                                                       \
+  extern "C" int name(int* value) {                                                                 \
+    int words[2] = {0, 0}, zero[2] = {0, 0};                                                        \
+    if (cudaMemcpyFromSymbol(words, g_tl_debug_words, sizeof(words)) != cudaSuccess) return -1;     \
+    if (words[0]) cudaMemcpyToSymbol(g_tl_debug_words, zero, sizeof(zero));                         \
+    if (value) *value = words[1];                                                                   \
+    return words[0];                                                                                \
+  }
+#else
+#define TL_DEBUG_OK(condition, code, value) true
+#define TL_DEBUG_READER(name)             \
+  extern "C" int name(int* value) {       \
+    if (value) *value = 0;                \
+    return 0;                             \
+  }
+#endif
+
 #include <stdlib.h>
 
 namespace tl {

@@ -23,7 +23,8 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ partial, int sp
                                        const int* __restrict__ positions, const int* __restrict__ token_req,
                                        const int* __restrict__ block_table, int table_width,
                                        __nv_bfloat16* __restrict__ pages, const float* __restrict__ inv_freq,
-                                       int tokens, int nh, int nkv, int d, int page_size, int write_kv) {
+                                       int tokens, int nh, int nkv, int d, int page_size, int write_kv,
+                                       int num_pages) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
 
@@ -37,7 +38,9 @@ __global__ void finish_qkv_rope_kernel(const float* __restrict__ partial, int sp
   if (h >= nh) {
     if (!write_kv) return;
     const int kvh = is_v ? h - nh - nkv : h - nh;
+    if (!TL_DEBUG_OK(pos >= 0 && pos / page_size < table_width, TL_DEBUG_POSITION, pos)) return;
     const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+    if (!TL_DEBUG_OK(page >= 0 && page < num_pages, TL_DEBUG_PAGE, page)) return;
     dst = pages + ((((size_t)page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + pos % page_size) * d;
   }
   const float* src = partial + (size_t)t * N + (size_t)h * d;
@@ -140,12 +143,14 @@ finish_accum_norm_kernel(const float* __restrict__ partial, int splits, const fl
 
 }  // namespace
 
+TL_DEBUG_READER(tl_decode_fused_debug_error)
+
 extern "C" {
 
 int tl_finish_qkv_rope(const float* partial, int splits, const float* bias, void* qkv, const int* positions,
                        const int* token_req, const int* block_table, int table_width, void* pages,
                        const float* inv_freq, int tokens, int nh, int nkv, int d, int page_size, int write_kv,
-                       cudaStream_t stream) {
+                       int num_pages, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d % 2 || splits < 1) return TL_ERR_UNSUPPORTED;
   const int heads = write_kv ? nh + 2 * nkv : nh;
@@ -154,7 +159,7 @@ int tl_finish_qkv_rope(const float* partial, int splits, const float* bias, void
   if (nt > 128) nt = 128;
   tl::launch_kernel(finish_qkv_rope_kernel, dim3(tokens, heads), nt, 0, stream, 
       partial, splits, bias, (__nv_bfloat16*)qkv, positions, token_req, block_table, table_width,
-      (__nv_bfloat16*)pages, inv_freq, tokens, nh, nkv, d, page_size, write_kv);
+      (__nv_bfloat16*)pages, inv_freq, tokens, nh, nkv, d, page_size, write_kv, num_pages);
   return TL_LAUNCH_CHECK();
 }
 

@@ -22,6 +22,7 @@ __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict_
   const int t = blockIdx.x;
   int id = ids[t];
   const bool ok = id >= 0 && id < vocab;
+  TL_DEBUG_OK(ok, TL_DEBUG_TOKEN, id);  // (an id outside the vocabulary reads as a zero row either way)
   const T* row = table + (size_t)(ok ? id : 0) * hidden;
   float* out = acc + (size_t)t * hidden;
   for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[j] = ok ? to_float(row[j]) : 0.f;
@@ -120,7 +121,7 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
                                const int* __restrict__ token_req,
                                const int* __restrict__ block_table, int table_width,
                                T* __restrict__ pages, const float* __restrict__ inv_freq, int nh,
-                               int nkv, int d, int page_size, int write_kv) {
+                               int nkv, int d, int page_size, int write_kv, int num_pages) {
   tl::pdl_launch_dependents();  // the next kernel may start its prologue (it waits for us before it reads our output)
   tl::pdl_wait();               // everything before us in the stream is complete and visible
 
@@ -134,7 +135,9 @@ __global__ void rope_kv_kernel(T* __restrict__ qkv, const int* __restrict__ posi
   if (h >= nh) {
     if (!write_kv) return;
     const int kvh = is_v ? h - nh - nkv : h - nh;
+    if (!TL_DEBUG_OK(pos >= 0 && pos / page_size < table_width, TL_DEBUG_POSITION, pos)) return;
     const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+    if (!TL_DEBUG_OK(page >= 0 && page < num_pages, TL_DEBUG_PAGE, page)) return;
     dst = pages + ((((size_t)page * 2 + (is_v ? 1 : 0)) * nkv + kvh) * page_size + pos % page_size) * d;
   }
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
@@ -162,14 +165,16 @@ __global__ void __launch_bounds__(256)
 rope_kv_vec_kernel(__nv_bfloat16* __restrict__ qkv, const int* __restrict__ positions,
                    const int* __restrict__ token_req, const int* __restrict__ block_table, int table_width,
                    __nv_bfloat16* __restrict__ pages, const float* __restrict__ inv_freq, int nh, int nkv, int d,
-                   int page_size, int heads) {
+                   int page_size, int heads, int num_pages) {
   tl::pdl_launch_dependents();
   tl::pdl_wait();
   const int t = blockIdx.x;
   const int half = d >> 1;
   const int per_head = half >> 3;  // threads a head
   const int pos = positions[t];
+  if (!TL_DEBUG_OK(pos >= 0 && pos / page_size < table_width, TL_DEBUG_POSITION, pos)) return;
   const int page = block_table[(size_t)token_req[t] * table_width + pos / page_size];
+  if (!TL_DEBUG_OK(page >= 0 && page < num_pages, TL_DEBUG_PAGE, page)) return;
   const int slot = pos % page_size;
   for (int item = threadIdx.x; item < heads * per_head; item += blockDim.x) {
     const int h = item / per_head, i = (item % per_head) * 8;
@@ -227,6 +232,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 
 }  // namespace
 
+TL_DEBUG_READER(tl_elementwise_debug_error)
+
 extern "C" {
 
 int tl_embed(const void* table, int dtype, const int* ids, float* acc, int tokens, int hidden,
@@ -272,7 +279,7 @@ int tl_rms_norm(const float* acc, const float* weight, const int* rows, void* ou
 
 int tl_rope_kv(void* qkv, int dtype, const int* positions, const int* token_req,
                const int* block_table, int table_width, void* pages, const float* inv_freq,
-               int tokens, int nh, int nkv, int d, int page_size, int write_kv,
+               int tokens, int nh, int nkv, int d, int page_size, int write_kv, int num_pages,
                cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (d % 2) return TL_ERR_UNSUPPORTED;
@@ -284,18 +291,18 @@ int tl_rope_kv(void* qkv, int dtype, const int* positions, const int* token_req,
     const int items = heads * (d / 16);
     const int threads = items >= 256 ? 256 : ((items + 31) / 32) * 32;
     tl::launch_kernel(rope_kv_vec_kernel, tokens, threads, 0, stream, (__nv_bfloat16*)qkv, positions, token_req,
-                      block_table, table_width, (__nv_bfloat16*)pages, inv_freq, nh, nkv, d, page_size, heads);
+                      block_table, table_width, (__nv_bfloat16*)pages, inv_freq, nh, nkv, d, page_size, heads, num_pages);
     return TL_LAUNCH_CHECK();
   }
   dim3 grid(tokens, heads);
   if (dtype == TL_DTYPE_F32)
     tl::launch_kernel(rope_kv_kernel<float>, grid, nt, 0, stream, (float*)qkv, positions, token_req, block_table,
                                                    table_width, (float*)pages, inv_freq, nh, nkv, d,
-                                                   page_size, write_kv);
+                                                   page_size, write_kv, num_pages);
   else
     tl::launch_kernel(rope_kv_kernel<__nv_bfloat16>, grid, nt, 0, stream, 
         (__nv_bfloat16*)qkv, positions, token_req, block_table, table_width, (__nv_bfloat16*)pages,
-        inv_freq, nh, nkv, d, page_size, write_kv);
+        inv_freq, nh, nkv, d, page_size, write_kv, num_pages);
   return TL_LAUNCH_CHECK();
 }
 

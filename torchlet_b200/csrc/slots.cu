@@ -44,6 +44,7 @@ slot_gather_kernel(const int* __restrict__ command, int b, int groups, int max_s
   const int* given = flags + b;  // six rows of b words
   const int* pairs = given + 6 * b;
   const int slot = lanes[lane];
+  TL_DEBUG_OK(slot >= -1 && slot < max_slots, TL_DEBUG_SLOT, slot);  // -1 is the padding mark
   if (slot < 0 || slot >= max_slots) {  // padding: token 0 at position 0 of the reserved page 0
     if (tid == 0) {
       lane_token[lane] = 0;
@@ -75,6 +76,7 @@ slot_gather_kernel(const int* __restrict__ command, int b, int groups, int max_s
   }
   __syncthreads();
   const int position = records[1 * max_slots + slot];
+  TL_DEBUG_OK(position >= 0 && position / page_size < width, TL_DEBUG_POSITION, position);
   if (tid == 0) {
     lane_token[lane] = records[0 * max_slots + slot];
     lane_position[lane] = position;
@@ -108,6 +110,8 @@ __global__ void slot_advance_kernel(const int* __restrict__ command, int b, int 
 }
 
 }  // namespace
+
+TL_DEBUG_READER(tl_slots_debug_error)
 
 extern "C" {
 

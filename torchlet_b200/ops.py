@@ -13,7 +13,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from .csrc.build import load_library
+from .csrc.build import DEBUG_BUILD, load_library
 
 F32, BF16 = 0, 1
 _UNSUPPORTED = 10001
@@ -36,7 +36,8 @@ _SIGNATURES = {
         "tl_embed": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "tl_rms_norm": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
         "tl_rope_kv": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
-                       c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_elementwise_debug_error": [c_void_p],
         "tl_swiglu": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
     },
     "gemm_simt": {
@@ -45,7 +46,8 @@ _SIGNATURES = {
     },
     "attention_generic": {
         "tl_attention_generic": [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+                                 c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "tl_attention_generic_debug_error": [c_void_p],
     },
     "gemm_tc": {
         "tl_gemm_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_longlong,
@@ -59,10 +61,12 @@ _SIGNATURES = {
                              c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
                              c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p],
         "tl_attention_mma_error": [],
+        "tl_attention_mma_debug_error": [c_void_p],
     },
     "decode_fused": {
         "tl_finish_qkv_rope": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
-                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+                               c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "tl_decode_fused_debug_error": [c_void_p],
         "tl_finish_accum_norm": [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
                                  c_void_p],
     },
@@ -79,6 +83,7 @@ _SIGNATURES = {
         "tl_slot_advance": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
         "tl_slot_command_words": [c_int, c_int],
         "tl_slot_record_rows": [],
+        "tl_slots_debug_error": [c_void_p],
     },
     "sampling": {
         "tl_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
@@ -171,7 +176,7 @@ def rope_kv(qkv, positions, token_req, block_table, pages, inv_freq, nh, nkv, d,
     code = _fn("elementwise", "tl_rope_kv")(
         qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), token_req.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], pages.data_ptr(), inv_freq.data_ptr(), tokens, nh, nkv,
-        d, page_size, 1 if write_kv else 0, _stream())
+        d, page_size, 1 if write_kv else 0, pages.shape[0], _stream())
     _check(code, "rope_kv")
 
 
@@ -183,7 +188,7 @@ def store_kv(qkv, positions, token_req, block_table, pages, nh, nkv, d, page_siz
     code = _fn("elementwise", "tl_rope_kv")(
         qkv.data_ptr(), dtype_code(qkv.dtype), positions.data_ptr(), token_req.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], pages.data_ptr(), None, qkv.shape[0], nh, nkv,
-        d, page_size, 1, _stream())
+        d, page_size, 1, pages.shape[0], _stream())
     _check(code, "store_kv")
 
 
@@ -221,7 +226,7 @@ def attention_generic(q, q_stride, pages, block_table, token_req, positions, out
     code = _fn("attention_generic", "tl_attention_generic")(
         q.data_ptr(), q_stride, pages.data_ptr(), dtype_code(q.dtype), block_table.data_ptr(),
         block_table.shape[1], token_req.data_ptr(), positions.data_ptr(), out.data_ptr(), out.stride(0),
-        tokens, nh, nkv, d, page_size, int(window or 0), float(scale), _stream())
+        tokens, nh, nkv, d, page_size, int(window or 0), float(scale), pages.shape[0], _stream())
     _check(code, "attention_generic")
 
 
@@ -371,7 +376,7 @@ def finish_qkv_rope(partials, splits, bias, qkv, positions, token_req, block_tab
     code = _fn("decode_fused", "tl_finish_qkv_rope")(
         partials.data_ptr(), splits, _ptr(bias), qkv.data_ptr(), positions.data_ptr(), token_req.data_ptr(),
         block_table.data_ptr(), block_table.shape[1], pages.data_ptr(), inv_freq.data_ptr(), qkv.shape[0], nh, nkv,
-        d, page_size, 1 if write_kv else 0, _stream())
+        d, page_size, 1 if write_kv else 0, pages.shape[0], _stream())
     _check(code, "finish_qkv_rope")
 
 
@@ -482,9 +487,28 @@ def attention_tc_error() -> int:
     return _fn("attention_tc", "tl_attention_tc_error")()
 
 
+_DEBUG_CODES = {1: "a token id outside the vocabulary", 2: "a position beyond its request's block table",
+                3: "a page id outside the pool", 4: "a slot outside the slot range"}
+
+
+def debug_errors() -> list:
+    """What the debug build's index checks have caught since the last call: (library, meaning,
+    offending value) for every loaded library whose check failed; reading clears.  Always empty
+    in the ordinary build (``TORCHLET_B200_DEBUG`` unset), whose kernels carry no checks."""
+    found = []
+    for library in ("elementwise", "attention_generic", "attention_mma", "decode_fused", "slots"):
+        if any(name in _functions for name in _SIGNATURES[library]):
+            value = ctypes.c_int(0)
+            code = _fn(library, f"tl_{library}_debug_error")(ctypes.byref(value))
+            if code:
+                found.append((library, _DEBUG_CODES.get(code, f"code {code}"), value.value))
+    return found
+
+
 def raise_on_wait_errors() -> None:
     """Raises if a bounded wait inside a tensor-core kernel has given up since the last call
-    (the kernel then ran to its end with whatever it had, so its output is not to be used).
+    (the kernel then ran to its end with whatever it had, so its output is not to be used), or,
+    in the debug build, if an index check inside a kernel has failed.
     Only libraries that are loaded are asked.  The read is a blocking copy on the default
     stream, so it sees every kernel launched before it."""
     for library, read in (("gemm_tc", gemm_tc_error), ("attention_tc", attention_tc_error),
@@ -494,3 +518,7 @@ def raise_on_wait_errors() -> None:
             if code:
                 raise KernelError(f"{library}: a bounded wait gave up inside a kernel (code {code}); "
                                   "the results of this step are invalid")
+    if DEBUG_BUILD:
+        for library, meaning, value in debug_errors():
+            raise KernelError(f"{library} (debug build): {meaning}: {value}; the access was skipped, "
+                              "the results of this step are invalid")
