@@ -119,6 +119,20 @@ class ClockSampler:
                 "span": span, "period_ms": self.PERIOD_MS}
 
 
+def config_record(cfg: dict, layers: int, batch: int, context: int) -> dict:
+    """The ``config`` of the JSON line; both arms print the same keys."""
+    return {
+        "model": "Qwen2.5-7B layer sizes, random weights seed 4", "global_batch": batch, "seq_len": context,
+        "parallelism": "single GPU", "layers": layers, "layers_of_configuration": cfg["num_hidden_layers"],
+        "hidden_size": cfg["hidden_size"], "intermediate_size": cfg["intermediate_size"],
+        "num_attention_heads": cfg["num_attention_heads"], "num_key_value_heads": cfg["num_key_value_heads"],
+        "head_dim": cfg["hidden_size"] // cfg["num_attention_heads"], "vocab_size": cfg["vocab_size"],
+        "kv_page_size": 16, "prefill_tokens": 2048, "cuda_graph": True,
+        "l2": "each step reads 15 GB of weights, larger than L2; no flush",
+        "context": "cached keys/values are seeded random numbers (ours); prompts of seeded random ids (reference)",
+    }
+
+
 def model_numbers(cfg: dict, layers: int):
     """Parameters a decode step reads, KV bytes per token, and flops of a prefill."""
     H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
@@ -253,10 +267,17 @@ def time_e2e(model, batch: int, context: int, steps: int, warmup: int):
     # every request gets exactly ``steps`` more tokens, so the timed call is ``steps`` full decode steps
     for r in requests:
         r.params.max_new_tokens = len(r.output_tokens) + steps
-    start = time.perf_counter()
-    engine.run()  # the loop behind LLM.generate: schedule, step, tokens back to the host, until all are done
-    torch.cuda.synchronize()
-    seconds = time.perf_counter() - start
+    import gc
+
+    gc.collect()
+    gc.disable()  # a collection inside a timed region of a few dozen milliseconds would be most of it
+    try:
+        start = time.perf_counter()
+        engine.run()  # the loop behind LLM.generate: schedule, step, tokens back to the host, until all are done
+        torch.cuda.synchronize()
+        seconds = time.perf_counter() - start
+    finally:
+        gc.enable()
     produced = sum(len(r.output_tokens) for r in requests) - produced
     graph_steps = engine.runner.graph_steps - graph_before
     if produced != batch * steps:
@@ -381,10 +402,9 @@ def reference_arm(args) -> int:
         "value": round(tok_s, 1), "unit": "tok/s", "n_gpus": 1, "steps": steps, "warmup": args.warmup,
         "ms_per_step": round(seconds * 1e3 / steps, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"model": "Qwen2.5-7B layer sizes, random weights seed 4", "global_batch": batch, "seq_len": context,
-                   "parallelism": "single GPU", "layers": layers, "layers_of_configuration": cfg["num_hidden_layers"],
-                   "how": "difference of two generate() calls with the same prompts",
-                   "modelscope": "stand-in module returning a local folder (no network)"},
+        "config": config_record(cfg, layers, batch, context),
+        "notes": {"how": "difference of two generate() calls with the same prompts",
+                  "modelscope": "stand-in module returning a local folder (no network)"},
         "e2e": {"value": round(tok_s, 1), "unit": "tok/s", "h2d_bytes_per_step": None, "d2h_bytes_per_step": None},
         "prefill": {"value": round(2048 / t_prefill, 1), "tokens": 2048, "ms": round(t_prefill * 1e3, 2),
                     "note": "one generate() call of 1 new token, tokenizer included"},
@@ -451,16 +471,7 @@ def main() -> int:
         "value": round(main_run["tok_s"], 1), "unit": "tok/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "impl": "ours",
-        "config": {
-            "model": "Qwen2.5-7B layer sizes, random weights seed 4", "global_batch": args.batch,
-            "seq_len": args.context, "parallelism": "single GPU", "layers": layers,
-            "layers_of_configuration": cfg["num_hidden_layers"], "hidden_size": cfg["hidden_size"],
-            "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
-            "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": 128, "vocab_size": cfg["vocab_size"],
-            "kv_page_size": 16, "prefill_tokens": 2048, "cuda_graph": True,
-            "l2": "each step reads 15 GB of weights, larger than L2; no flush",
-            "context": "cached keys/values are seeded random numbers",
-        },
+        "config": config_record(cfg, layers, args.batch, args.context),
         "gpu_launches": main_run["launches"],
         "clocks": main_run["clocks"],
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
@@ -484,6 +495,18 @@ def main() -> int:
             points[f"decode_b{batch}"] = round(run["tok_s"], 1)
             bytes_b = weight_bytes + kv_per_token * run["mean_context"] * batch
             points[f"decode_b{batch}_hbm_frac"] = round(bytes_b / (run["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+        # further sizes: decode at other contexts, prefill of other lengths (tok/s and fraction of the peak)
+        for context in (1024, 16384):
+            for batch in (1, 8, 64):
+                run = time_decode(model, batch, context, min(args.steps, 32), args.warmup)
+                bytes_b = weight_bytes + kv_per_token * run["mean_context"] * batch
+                points[f"decode_b{batch}_ctx{context}"] = round(run["tok_s"], 1)
+                points[f"decode_b{batch}_ctx{context}_hbm_frac"] = round(
+                    bytes_b / (run["ms_per_step"] / 1e3) / 1e9 / peaks["hbm_gbs"], 4)
+        for tokens in (512, 8192):
+            ms = time_prefill(model, tokens, repeats=2)
+            points[f"prefill_{tokens}"] = round(tokens / (ms / 1e3), 1)
+            points[f"prefill_{tokens}_frac"] = round(prefill_flops(tokens) / (ms / 1e3) / 1e12 / peaks["bf16_tflops"], 4)
         record["points"] = points
         e2e = time_e2e(model, args.batch, args.context, args.steps, args.warmup)
         record["e2e"] = {"value": round(e2e["tok_s"], 1), "unit": "tok/s", "h2d_bytes_per_step": e2e["h2d_bytes"],

@@ -65,6 +65,10 @@ def _sizes(cfg: dict, layers: int):
 # ------------------------------------------------------------------ interleave14b
 def interleave14b(layers: int = 48, decoders: int = 32, prompts: int = 8, prompt_len: int = 4096, portion: int = 512,
                   decoder_context: int = 2048, peaks: dict | None = None) -> dict:
+    """Two token budgets are timed: ``decoders + portion`` (every step holds a full 512-token
+    portion beside the 32 decode tokens: 544 rows, which the 128-row tiles of the products cover
+    as 640) and ``portion`` (the step's tokens fill whole tiles: 480-token portions beside the
+    32 decode tokens)."""
     from ..config import EngineConfig
     from ..engine.engine import Engine
     from ..engine.scheduler import Request
@@ -73,80 +77,87 @@ def interleave14b(layers: int = 48, decoders: int = 32, prompts: int = 8, prompt
     cfg = QWEN25_14B
     model = _model(cfg, layers, seed=6)
     page, context = 16, 8192
-    steps_wanted = prompts * (prompt_len // portion)
-    tokens_held = decoders * (decoder_context + steps_wanted + 64) + prompts * (prompt_len + 64)
+    budgets = {"full_portions": decoders + portion, "whole_tiles": portion}
+    decode_steps = sum(prompts * -(-prompt_len // (b - decoders)) for b in budgets.values()) + 64
+    tokens_held = decoders * (decoder_context + decode_steps + 64) + prompts * (prompt_len + 64)
     engine = Engine(model, EngineConfig(
         dtype="bfloat16", max_decode_slots=decoders + prompts, kv_block_size=page, max_seq_len=context,
         max_num_blocks=tokens_held // page + decoders + prompts + 1, max_num_batched_tokens=4096))
     generator = torch.Generator().manual_seed(6)
     draw = lambda n: torch.randint(0, cfg["vocab_size"], (n,), generator=generator).tolist()
-    running = [Request(draw(decoder_context), SamplingParams(max_new_tokens=steps_wanted + 48, ignore_eos=True))
+    running = [Request(draw(decoder_context), SamplingParams(max_new_tokens=decode_steps, ignore_eos=True))
                for _ in range(decoders)]
     engine.add_requests(running)
     while any(r.num_computed < decoder_context for r in running):  # their prompts, untimed
         engine.step()
     for _ in range(4):  # decode-only steps: warm-up, graph capture
         engine.step()
-    # now the token budget of a step: every decoder's token and ONE portion of a prompt
-    engine.scheduler.max_num_batched_tokens = decoders + portion
-    # a prompt is done with its first sampled token, so the decoders stay 32
-    fresh = [Request(draw(prompt_len), SamplingParams(max_new_tokens=1, ignore_eos=True)) for _ in range(prompts)]
-    engine.add_requests(fresh)
-    engine.step()  # the first mixed step is the warm-up of its shapes
-    torch.cuda.synchronize()
-    times, mixes = [], []
-    stats = engine.scheduler.stats
-    while any(r.num_computed < prompt_len for r in fresh):
-        before = (stats.prefill_tokens, stats.decode_tokens)
-        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record()
-        engine.step()
-        end.record()
-        torch.cuda.synchronize()
-        mix = (stats.prefill_tokens - before[0], stats.decode_tokens - before[1])
-        if mix == (portion, decoders):
-            times.append(begin.elapsed_time(end))
-        mixes.append(mix)
-    if not times:
-        raise RuntimeError(f"no step held {decoders} decode tokens beside a {portion}-token portion: {mixes[:8]}")
-    times.sort()
-    ms = times[len(times) // 2]  # the median step
-    # what such a step must read and compute
     sizes = _sizes(cfg, layers)
-    decode_context = decoder_context + steps_wanted / 2  # the decoders' cached tokens, mid-run
-    portion_context = prompt_len / 2  # a portion's cached prefix, on average
-    weight_bytes = 2 * (layers * sizes["layer_matrices"] + sizes["head"])
-    kv_bytes = sizes["kv_bytes_per_token"] * (decoders * decode_context + portion_context + portion)
-    tokens = decoders + portion
-    gemm_flops = 2.0 * tokens * layers * sizes["layer_matrices"] + 2.0 * (decoders + 0) * sizes["head"]
-    attention_flops = layers * 4.0 * sizes["nh"] * sizes["d"] * (
-        decoders * decode_context + portion * (portion_context + portion / 2))
-    flops = gemm_flops + attention_flops
-    record = {
-        "workload": "interleave14b", "metric": "mixed step: 32 decode tokens beside a 512-token prompt portion",
-        "ms_per_step": round(ms, 3), "timed_steps": len(times), "steps": len(mixes),
-        "decode_tok_s": round(decoders / (ms / 1e3), 1), "prefill_tok_s": round(portion / (ms / 1e3), 1),
-        "tok_s": round(tokens / (ms / 1e3), 1),
-        "bytes_per_step": int(weight_bytes + kv_bytes), "flops_per_step": flops,
-        "achieved_gbs": round((weight_bytes + kv_bytes) / (ms / 1e3) / 1e9, 1),
-        "achieved_tflops": round(flops / (ms / 1e3) / 1e12, 1),
-        "config": {"model": "Qwen2.5-14B layer sizes, random weights seed 6", "layers": layers,
-                   "layers_of_configuration": cfg["num_hidden_layers"], "hidden_size": cfg["hidden_size"],
-                   "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
-                   "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": sizes["d"],
-                   "vocab_size": cfg["vocab_size"], "context": context, "kv_page_size": page, "decoders": decoders,
-                   "decoder_context": int(decode_context), "prompts": prompts, "prompt_len": prompt_len,
-                   "portion": portion, "dtype": "bf16", "data": "synthetic"},
-    }
-    if peaks:
-        record["hbm_frac"] = round(record["achieved_gbs"] / peaks["hbm_gbs"], 4)
-        record["tensor_frac"] = round(record["achieved_tflops"] / peaks["bf16_tflops"], 4)
-        # the step can be no faster than the slower of its two bounds
-        bound_ms = max((weight_bytes + kv_bytes) / peaks["hbm_gbs"] / 1e6, flops / peaks["bf16_tflops"] / 1e9)
-        record["roofline_frac"] = round(bound_ms / ms, 4)
+    stats = engine.scheduler.stats
+    record = {"workload": "interleave14b",
+              "metric": "mixed step: 32 decode tokens beside a portion of a 4,096-token prompt (Qwen2.5-14B layer sizes)"}
+    everyone = list(running)
+    for name, budget in budgets.items():
+        # the token budget of a step: every decoder's token and ONE portion of a prompt
+        engine.scheduler.max_num_batched_tokens = budget
+        cut = budget - decoders
+        # a prompt is done with its first sampled token, so the decoders stay 32
+        fresh = [Request(draw(prompt_len), SamplingParams(max_new_tokens=1, ignore_eos=True)) for _ in range(prompts)]
+        everyone += fresh
+        engine.add_requests(fresh)
+        engine.step()  # the first mixed step is the warm-up of its shapes
+        torch.cuda.synchronize()
+        times, mixes, contexts = [], [], []
+        while any(r.num_computed < prompt_len for r in fresh):
+            before = (stats.prefill_tokens, stats.decode_tokens)
+            begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            begin.record()
+            engine.step()
+            end.record()
+            torch.cuda.synchronize()
+            mix = (stats.prefill_tokens - before[0], stats.decode_tokens - before[1])
+            if mix == (cut, decoders):
+                times.append(begin.elapsed_time(end))
+                contexts.append(sum(r.num_tokens for r in running) / decoders)
+            mixes.append(mix)
+        if not times:
+            raise RuntimeError(f"no step held {decoders} decode tokens beside a {cut}-token portion: {mixes[:8]}")
+        ms = sorted(times)[len(times) // 2]  # the median step
+        # what such a step must read and compute
+        decode_context = sum(contexts) / len(contexts)  # the decoders' cached tokens, on average
+        portion_context = (prompt_len - cut) / 2  # a portion's cached prefix, on average
+        weight_bytes = 2 * (layers * sizes["layer_matrices"] + sizes["head"])
+        kv_bytes = sizes["kv_bytes_per_token"] * (decoders * decode_context + portion_context + cut)
+        tokens = decoders + cut
+        gemm_flops = 2.0 * tokens * layers * sizes["layer_matrices"] + 2.0 * decoders * sizes["head"]
+        attention_flops = layers * 4.0 * sizes["nh"] * sizes["d"] * (
+            decoders * decode_context + cut * (portion_context + cut / 2))
+        flops = gemm_flops + attention_flops
+        entry = {"token_budget": budget, "portion": cut, "ms_per_step": round(ms, 3), "timed_steps": len(times),
+                 "steps": len(mixes), "decode_tok_s": round(decoders / (ms / 1e3), 1),
+                 "prefill_tok_s": round(cut / (ms / 1e3), 1), "tok_s": round(tokens / (ms / 1e3), 1),
+                 "decoder_context": int(decode_context), "bytes_per_step": int(weight_bytes + kv_bytes),
+                 "flops_per_step": flops, "achieved_gbs": round((weight_bytes + kv_bytes) / (ms / 1e3) / 1e9, 1),
+                 "achieved_tflops": round(flops / (ms / 1e3) / 1e12, 1)}
+        if peaks:
+            entry["hbm_frac"] = round(entry["achieved_gbs"] / peaks["hbm_gbs"], 4)
+            entry["tensor_frac"] = round(entry["achieved_tflops"] / peaks["bf16_tflops"], 4)
+            # the step can be no faster than the slower of its two bounds
+            bound_ms = max((weight_bytes + kv_bytes) / peaks["hbm_gbs"] / 1e6, flops / peaks["bf16_tflops"] / 1e9)
+            entry["roofline_frac"] = round(bound_ms / ms, 4)
+        record[name] = entry
+    record["tok_s"] = record["full_portions"]["tok_s"]
+    record["config"] = {"model": "Qwen2.5-14B layer sizes, random weights seed 6", "layers": layers,
+                        "layers_of_configuration": cfg["num_hidden_layers"], "hidden_size": cfg["hidden_size"],
+                        "intermediate_size": cfg["intermediate_size"], "num_attention_heads": cfg["num_attention_heads"],
+                        "num_key_value_heads": cfg["num_key_value_heads"], "head_dim": sizes["d"],
+                        "vocab_size": cfg["vocab_size"], "context": context, "kv_page_size": page, "decoders": decoders,
+                        "prompts": prompts, "prompt_len": prompt_len, "portion": portion, "dtype": "bf16",
+                        "data": "synthetic"}
+    engine.scheduler.max_num_batched_tokens = 4096
     engine.run()  # let everything finish; every page and slot must come back
     engine.runner.cache.check()
-    record["all_finished"] = all(r.error is None for r in running + fresh) and not engine.runner.cache.live_requests()
+    record["all_finished"] = all(r.error is None for r in everyone) and not engine.runner.cache.live_requests()
     return record
 
 
