@@ -32,6 +32,7 @@
 #include <math.h>
 
 #include <mutex>
+#include <type_traits>
 #include <unordered_map>
 
 #include "common.cuh"
@@ -335,7 +336,12 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
   }
   __syncthreads();  // stage 1 may now be overwritten by key/value tiles
 
-  for (int tile = tile_begin; tile < tile_end; ++tile) {
+  // the only tiles that can hold rows of keys outside [lo_key, hi_key]
+  const int edge_hi_tile = hi_key / BLOCK_N, edge_lo_tile = lo_key > 0 ? lo_key / BLOCK_N : -1;
+  // One key tile.  EDGE: the tile may hold rows of keys outside [lo_key, hi_key] (only the first
+  // and the last tile of a request can); the common tiles run a body without that code.
+  auto process_tile = [&](const int tile, auto edge_tag) {
+    constexpr bool EDGE = decltype(edge_tag)::value;
     const int index = tile - tile_begin;
     const int stage = index % STAGES;
     __nv_bfloat16* ks_tile = kv + stage * STAGE_ELEMS;
@@ -358,15 +364,17 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       // Whole pages were copied: value rows of keys outside [lo_key, hi_key] hold whatever the page
       // held before (another request's values, page 0).  Their weights are exactly 0, but 0 x NaN
       // is NaN, so the warp clears those of its own 16 rows before it multiplies.
-      const int key_first = tile * BLOCK_N + warp * 16;
-      if (key_first + 15 > hi_key || key_first < lo_key) {
-        for (int i = lane; i < 16 * (D / 8); i += 32) {
-          const int r = i / (D / 8), c = i % (D / 8);
-          if (key_first + r > hi_key || key_first + r < lo_key)
-            *reinterpret_cast<uint4*>(kv_at<D, true>(vs_tile, warp * 16 + r, c)) = make_uint4(0u, 0u, 0u, 0u);
+      if constexpr (EDGE) {
+        const int key_first = tile * BLOCK_N + warp * 16;
+        if (key_first + 15 > hi_key || key_first < lo_key) {
+          for (int i = lane; i < 16 * (D / 8); i += 32) {
+            const int r = i / (D / 8), c = i % (D / 8);
+            if (key_first + r > hi_key || key_first + r < lo_key)
+              *reinterpret_cast<uint4*>(kv_at<D, true>(vs_tile, warp * 16 + r, c)) = make_uint4(0u, 0u, 0u, 0u);
+          }
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // a later TMA copy may refill the stage
+          __syncwarp();
         }
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // a later TMA copy may refill the stage
-        __syncwarp();
       }
     } else {
       cp_async_commit();
@@ -463,6 +471,12 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       }
     }
     __syncthreads();  // the stage may be overwritten by the load after next
+  };
+  for (int tile = tile_begin; tile < tile_end; ++tile) {
+    if (TMA && (tile == edge_hi_tile || tile == edge_lo_tile))
+      process_tile(tile, std::true_type{});
+    else
+      process_tile(tile, std::false_type{});
   }
   cp_async_wait<0>();
 
