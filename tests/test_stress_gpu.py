@@ -1,7 +1,8 @@
 """Continuous batching under load: many requests of random lengths arriving while others
 run, greedy and temperature sampling mixed, a page pool too small for all of them.  Every
-request must finish, every page and slot must come back, and in float32 every output must
-equal the same request run alone (Qwen2.5-0.5B head geometry: 14 heads in 2 groups of 7,
+request must finish, every page and slot must come back, every produced token must be what the
+plain implementation gives for the tokens before it (in both dtypes), and in float32 every output
+must equal the same request run alone (Qwen2.5-0.5B head geometry: 14 heads in 2 groups of 7,
 head_dim 64, so the tensor-core kernels run in the bfloat16 case)."""
 import random
 
@@ -27,6 +28,31 @@ def build(dtype, **engine):
     weights = tiny_configs.make_weights(CONFIG, seed=5, std=0.02, norm_std=0.01, dtype=torch.bfloat16)
     model = build_model(Qwen2Config.from_dict(CONFIG), weights, dtype)
     return Engine(model, EngineConfig(dtype=dtype, max_seq_len=256, **engine))
+
+
+def check_against_plain(requests, dtype):
+    """Every produced token against the plain implementation, given the tokens before it: the
+    greedy ones must be the plain argmax (within rounding of it in bfloat16), the sampled ones
+    the argmax of the plain scores with the request's own noise."""
+    import plain_model
+
+    weights = {k: v.float() for k, v in tiny_configs.make_weights(CONFIG, seed=5, std=0.02, norm_std=0.01,
+                                                                   dtype=torch.bfloat16).items()}
+    slack = 0.0 if dtype == "float32" else 2.5e-2
+    for request in requests:
+        ids = request.prompt_tokens + request.output_tokens
+        logits = plain_model.forward_logits(CONFIG, weights, ids)
+        first = len(request.prompt_tokens) - 1
+        temperature = request.params.temperature
+        for k, token in enumerate(request.output_tokens):
+            row = logits[first + k]
+            room = slack * float(row.abs().max()) + 1e-5
+            if temperature == 0:
+                assert float(row[token]) >= float(row.max()) - room, (request.request_id, k)
+            else:
+                scores = plain_model.temperature_scores(row, temperature, request.seed, k)
+                # (the kernel takes its logarithms in float32, the plain restatement in float64)
+                assert scores[token] >= max(scores) - room / temperature - 1e-3, (request.request_id, k)
 
 
 def make_requests(count, seed):
@@ -65,6 +91,7 @@ def test_many_requests_arriving_while_others_run(dtype):
     assert all(r.error is None and len(r.output_tokens) == r.params.max_new_tokens for r in requests)
     assert engine.runner.cache.live_requests() == []
     assert engine.runner.cache.pools[0].num_free == 40 and engine.runner.cache.num_free_slots == 8
+    check_against_plain(requests, dtype)
     if dtype == "float32":
         alone = build(dtype, max_decode_slots=1, kv_block_size=16, max_num_batched_tokens=512)
         again = make_requests(count, seed=1)
@@ -108,6 +135,7 @@ def test_run_with_a_tight_pool_and_stop_tokens(dtype):
     assert all(t not in stops for r in requests for t in r.output_tokens)
     assert engine.runner.cache.live_requests() == []
     assert engine.runner.cache.pools[0].num_free == 30 and engine.runner.cache.num_free_slots == 6
+    check_against_plain(requests, dtype)
     if dtype == "float32":
         alone = build(dtype, max_decode_slots=1, kv_block_size=16, max_num_batched_tokens=512)
         for request, fresh in zip(requests, make()):
