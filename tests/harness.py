@@ -121,6 +121,7 @@ class KernelCalls:
 
         self.counts = {name: 0 for name in self.NAMES}
         self.decode_splits = []
+        self.prompt_splits = []
         self._saved = {name: getattr(ops, name) for name in self.NAMES}
         for name, fn in self._saved.items():
             setattr(ops, name, self._wrap(name, fn))
@@ -131,6 +132,8 @@ class KernelCalls:
             self.counts[name] += 1
             if name == "attention_mma" and kwargs.get("rows16"):
                 self.decode_splits.append(kwargs.get("splits", 1))
+            if name == "attention_tc":
+                self.prompt_splits.append(kwargs.get("splits", 1))
             return fn(*args, **kwargs)
 
         return counted

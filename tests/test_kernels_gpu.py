@@ -500,6 +500,18 @@ def test_attention_tc(case, d):
     torch.cuda.synchronize()
     assert ops.attention_tc_error() == 0
     assert (out.float().cpu() - want).abs().max() <= 1.5e-2 * want.abs().max()
+    # the key tiles shared by two, three and five CTAs, merged by the second kernel (a workspace full of NaN first:
+    # a split that sees no key of a row writes no output for it, and the merge must leave that alone)
+    for splits in (2, 3, 5):
+        ops._workspace(("attention", x["qkv"].device), x["T"] * nh * splits * (d + 2) * 4).fill_(float("nan"))
+        split_out = torch.full((x["T"], nh * d), 7.0, device=DEV, dtype=torch.bfloat16)
+        ops.attention_tc(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(tile_req), to(tile_row),
+                         len(tile_req), split_out, nh, nkv, d, page, window, scale, splits=splits,
+                         token_req=x["token_req"])
+        torch.cuda.synchronize()
+        assert ops.attention_tc_error() == 0
+        assert torch.isfinite(split_out.float()).all()
+        assert (split_out.float().cpu() - want).abs().max() <= 1.5e-2 * want.abs().max(), splits
     if spike is not None:  # the spiked head's output is that key's value, in the kernel as in the formula
         token = sum(q_lens[:spike[0]]) + spike[1]
         v_spike = x["dense"][spike[0]][2][spike[2], 0].float()

@@ -192,6 +192,33 @@ def test_first_tokens_of_a_sequence(name, dtype):
         assert_close(got, want, dtype, f"{name} first tokens {cuts}")
 
 
+def test_portions_behind_a_long_prefix_share_their_key_tiles():
+    """A portion of a prompt behind 1,200 cached tokens has few row tiles for the whole GPU: its
+    key tiles are shared by several CTAs and merged (csrc/attention_tc.cu), beside a request that
+    decodes.  Tiny D, bfloat16, against the plain implementation."""
+    from torchlet_b200.engine import StepEntry
+
+    runner = make_runner("D", "bfloat16", num_pages=160, budget=2048)
+    ids, want = plain_logits("D", 1500, 31)
+    other, want_other = plain_logits("D", 300, 32)
+    runner.admit("long"); runner.admit("short")
+    got, got_other = [], []
+    with harness.KernelCalls() as calls:
+        plan = [(1200, 280), (150, 1), (2, 1), (148, 1)]
+        a = b = 0
+        for n_long, n_short in plan:
+            entries = [StepEntry("long", ids[a:a + n_long], list(range(n_long))),
+                       StepEntry("short", other[b:b + n_short], list(range(n_short)))]
+            logits = runner.step(entries).cpu()
+            got.append(logits[:n_long].clone()); got_other.append(logits[n_long:].clone())
+            a += n_long; b += n_short
+    assert max(calls.prompt_splits) > 1, "no portion's key tiles were ever shared"
+    assert_close(torch.cat(got), want, "bfloat16", "portions behind a long prefix")
+    assert_close(torch.cat(got_other), want_other[:b], "bfloat16", "the request beside them")
+    runner.finish("long"); runner.finish("short")
+    runner.cache.check()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_schedule_runs_a_layer_twice_and_shares_a_cache(dtype):
     schedule = ((0, None), (1, None), (0, None), (1, 1))

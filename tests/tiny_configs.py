@@ -68,7 +68,7 @@ TINY_D = {
     "num_hidden_layers": 2,
     "num_attention_heads": 6,
     "num_key_value_heads": 2,
-    "max_position_embeddings": 1024,
+    "max_position_embeddings": 2048,
     "rope_theta": 1000000.0,
     "rms_norm_eps": 1e-6,
     "attention_bias": True,

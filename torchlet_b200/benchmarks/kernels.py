@@ -89,10 +89,14 @@ def bench_attention(args) -> None:
         tiles = sorted(((r, s) for r in range(n) for s in range(0, q_len * group, rows)), key=lambda t: -t[1])
         tile_req = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
         tile_row = torch.tensor([t[1] for t in tiles], dtype=torch.int32, device="cuda")
+        from ..parts.attention_bf16 import prompt_splits
+
+        splits = args.splits or prompt_splits(len(tiles) * nkv, total)
+        token_req = torch.arange(n, dtype=torch.int32, device="cuda").repeat_interleave(q_len)
         run = lambda i: ops.attention_tc(qkv, pages, table, indptr, kv_before, tile_req, tile_row, len(tiles), out,
-                                         nh, nkv, d, page, None, scale)
+                                         nh, nkv, d, page, None, scale, splits=splits, token_req=token_req)
         kv_bytes = n * total * 2 * nkv * d * 2
-        what = f"prompt (tcgen05) tiles={len(tiles)}"
+        what = f"prompt (tcgen05) tiles={len(tiles)} key splits={splits}"
     else:
         tiles = [(r, s) for r in range(n) for s in range(0, q_len * group, ROWS)]
         tile_req = torch.tensor([t[0] for t in tiles], dtype=torch.int32, device="cuda")
@@ -125,6 +129,8 @@ def main(argv=None) -> int:
     attention.add_argument("--kv-heads", type=int, default=4)
     attention.add_argument("--head-dim", type=int, default=128)
     attention.add_argument("--page-size", type=int, default=16)
+    attention.add_argument("--splits", type=int, default=0,
+                           help="prompt portions on tcgen05: CTAs that share a row tile's key tiles (0: the engine's choice)")
     attention.add_argument("--kernel", choices=["tc", "mma"], default="tc",
                            help="prompt portions: tcgen05 kernel (head_dim 128) or the mma.sync kernel")
     for p in (gemm, attention):

@@ -69,6 +69,9 @@ struct Params {
   __nv_bfloat16* out;
   long long out_stride;
   int nh, nkv, page_size, window, rows_per_tile;
+  int splits;       // CTAs (blockIdx.z) that share the key tiles of one (row tiles, KV head)
+  float* part_acc;  // splits > 1: [tokens * nh][splits][D] unnormalized outputs
+  float* part_ml;   //             [tokens * nh][splits][2] reference max (log2 units) and sum
   float scale_log2;
 };
 
@@ -204,13 +207,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       cta_hi_key = before + last_tok;
     }
   }
-  // Later rows need later keys, so the CTA's key tiles are [first of tile 0, last of the last tile)
-  const int j_begin = tile[0].begin;
-  const int j_end = max(tile[0].end, tile[1].end);
+  // Later rows need later keys, so the row tiles' key tiles are [first of tile 0, last of the last tile)
+  const int all_begin = tile[0].begin;
+  const int all_end = max(tile[0].end, tile[1].end);
+  // With key splits (a small grid: few row tiles for the whole GPU) this CTA takes its share of
+  // them and leaves partial results for the merge kernel.
+  int j_begin = all_begin, j_end = all_end;
+  const int split = blockIdx.z;
+  if (p.splits > 1) {
+    const int per = (all_end - all_begin + p.splits - 1) / p.splits;
+    j_begin = min(all_end, all_begin + split * per);
+    j_end = min(all_end, j_begin + per);
+#pragma unroll
+    for (int x = 0; x < QTILES; ++x) {
+      tile[x].begin = min(max(tile[x].begin, j_begin), j_end);
+      tile[x].end = max(min(tile[x].end, j_end), tile[x].begin);
+    }
+  }
   // Whole pages are copied, so the first and the last key tile may hold rows of keys outside
   // [cta_lo_key, cta_hi_key]: whatever the pages held before.  Their weights are exactly 0, but
   // 0 x NaN is NaN, so the V loader clears those value rows before the tensor core reads them.
-  const bool edge_first = cta_lo_key % KEYS != 0, edge_last = cta_hi_key % KEYS != KEYS - 1;
+  const bool edge_first = cta_lo_key % KEYS != 0 && j_begin == all_begin && j_begin < j_end;
+  const bool edge_last = cta_hi_key % KEYS != KEYS - 1 && j_end == all_end && j_begin < j_end;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 2; ++i) {
@@ -427,8 +445,30 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
       __syncwarp();
       if (lane == 0) mbar_arrive(&p_full[x]);
     }
-    // ---- output: O / l
-    if (num_tiles > 0) {
+    // ---- output.  With key splits: the unnormalized O with its reference max and sum, for the merge
+    if (p.splits > 1) {
+      const size_t item = row_valid ? ((size_t)(tok0 + row / g) * p.nh + kvh * g + row % g) * p.splits + split : 0;
+      if (num_tiles > 0) {
+        mbar_wait(&o_done[x], 0, abort_flag, &g_error_word, 9);
+        fence_after_sync();
+        float* dst = p.part_acc + item * D;
+#pragma unroll 1
+        for (int c = 0; c < D; c += 32) {
+          uint32_t o[32];
+          tmem_ld_32(tmem_o + c, o);
+          tmem_ld_wait();
+          if (row_valid) {
+#pragma unroll
+            for (int q4 = 0; q4 < 8; ++q4)
+              *reinterpret_cast<uint4*>(dst + c + 4 * q4) = make_uint4(o[4 * q4], o[4 * q4 + 1], o[4 * q4 + 2], o[4 * q4 + 3]);
+          }
+        }
+      }
+      if (row_valid) {  // a split that saw no key of this row says so: the merge leaves its O alone
+        p.part_ml[item * 2] = num_tiles > 0 ? m_ref : -INFINITY;
+        p.part_ml[item * 2 + 1] = num_tiles > 0 ? l_sum : 0.f;
+      }
+    } else if (num_tiles > 0) {
       mbar_wait(&o_done[x], 0, abort_flag, &g_error_word, 9);
       fence_after_sync();
       const float inv = l_sum > 0.f ? 1.f / l_sum : 0.f;
@@ -463,6 +503,42 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
   }
 }
 
+// Merges the key splits of every (token, head) of the requests that brought more than one token:
+// out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M).  One warp an item; a lane owns D / 32 elements.
+template <int D>
+__global__ void __launch_bounds__(128)
+attention_tc_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                          const int* __restrict__ token_req, const int* __restrict__ req_indptr,
+                          __nv_bfloat16* __restrict__ out, long long out_stride, int tokens, int nh, int splits) {
+  tl::pdl_launch_dependents();
+  tl::pdl_wait();
+  const int item = blockIdx.x * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (item >= tokens * nh) return;
+  const int token = item / nh, head = item % nh;
+  const int req = token_req[token];
+  if (req_indptr[req + 1] - req_indptr[req] < 2) return;  // a single token: the decode kernel's row
+  const float* ml = part_ml + (size_t)item * splits * 2;
+  float m_all = -INFINITY;
+  for (int s = 0; s < splits; ++s) m_all = fmaxf(m_all, ml[2 * s]);
+  constexpr int PER = D / 32;
+  float acc[PER], total = 0.f;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    const float m = ml[2 * s];
+    if (m == -INFINITY) continue;  // that split saw no key of this row and wrote no O
+    const float f = exp2f(m - m_all);
+    total = fmaf(ml[2 * s + 1], f, total);
+    const float* src = part_acc + ((size_t)item * splits + s) * D + lane * PER;
+#pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = fmaf(src[i], f, acc[i]);
+  }
+  const float inv = total > 0.f ? 1.f / total : 0.f;
+  __nv_bfloat16* dst = out + (size_t)token * out_stride + (size_t)head * D + lane * PER;
+#pragma unroll
+  for (int i = 0; i < PER; ++i) dst[i] = __float2bfloat16_rn(acc[i] * inv);
+}
+
 // ------------------------------------------------------------------ host side
 struct MapKey {
   const void* base;
@@ -492,7 +568,9 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t cols
   return true;
 }
 
-template <int D> int launch(const CUtensorMap& map_kv, const Params& p, int nkv, int tiles, cudaStream_t stream) {
+template <int D>
+int launch(const CUtensorMap& map_kv, const Params& p, int nkv, int tiles, const int* token_req, int tokens,
+           cudaStream_t stream) {
   constexpr int SMEM = 6 * TileBytes<D>::value + 1024 + 256;
   static_assert(SMEM <= 232448, "shared memory of one CTA");
   static bool configured = false;
@@ -501,7 +579,11 @@ template <int D> int launch(const CUtensorMap& map_kv, const Params& p, int nkv,
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
-  tl::launch_kernel(attention_tc_kernel<D>, dim3(nkv, tiles), THREADS, SMEM, stream, map_kv, p);
+  tl::launch_kernel(attention_tc_kernel<D>, dim3(nkv, tiles, p.splits), THREADS, SMEM, stream, map_kv, p);
+  const int rc = TL_LAUNCH_CHECK();
+  if (rc || p.splits == 1) return rc;
+  tl::launch_kernel(attention_tc_merge_kernel<D>, (tokens * p.nh + 3) / 4, 128, 0, stream, (const float*)p.part_acc,
+                    (const float*)p.part_ml, token_req, p.req_indptr, p.out, p.out_stride, tokens, p.nh, p.splits);
   return TL_LAUNCH_CHECK();
 }
 
@@ -519,13 +601,28 @@ int tl_attention_tc_error() {
 // Packed rows a CTA takes for a group of ``group`` query heads: two row tiles of whole tokens.
 int tl_attention_tc_rows(int group) { return group > 0 && group <= ROWS ? QTILES * (ROWS / group) * group : 0; }
 
+// Bytes of float32 workspace for ``splits`` key splits over the ``tokens`` tokens of a step.
+long long tl_attention_tc_workspace(int tokens, int nh, int d, int splits) {
+  return splits > 1 ? (long long)tokens * nh * splits * (d + 2) * 4 : 0;
+}
+
 // pages: one cache layer [num_pages][2][nkv][page_size][d] bf16, d 64 or 128.  tile_req / tile_row:
-// request and first packed row (a multiple of tl_attention_tc_rows(nh / nkv)) of each CTA.
+// request and first packed row (a multiple of tl_attention_tc_rows(nh / nkv)) of each CTA; the
+// tiles cover every request of the step that brings more than one token.
+// splits > 1 (for grids that would leave most of the GPU idle): that many CTAs share the key
+// tiles of each (row tiles, KV head) and a second kernel merges their partial results, which
+// live in ``workspace`` (tl_attention_tc_workspace bytes); token_req [tokens] names each token's
+// request.
 int tl_attention_tc(const void* q, long long q_stride, const void* pages, long long num_pages,
                     const int* block_table, int table_width, const int* req_indptr, const int* kv_before,
                     const int* tile_req, const int* tile_row, int tiles, void* out, long long out_stride, int nh,
-                    int nkv, int d, int page_size, int window, float scale, cudaStream_t stream) {
+                    int nkv, int d, int page_size, int window, float scale, int splits, const int* token_req,
+                    int tokens, void* workspace, long long workspace_bytes, cudaStream_t stream) {
   if (tiles <= 0) return 0;
+  if (splits < 1 || splits > 64) return TL_ERR_UNSUPPORTED;
+  if (splits > 1 && (!token_req || tokens <= 0 || !workspace ||
+                     workspace_bytes < tl_attention_tc_workspace(tokens, nh, d, splits)))
+    return TL_ERR_UNSUPPORTED;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || nh / nkv > ROWS || page_size < 8 || page_size > KEYS ||
       KEYS % page_size || q_stride % 8 || out_stride % 8 || tiles > 65535 || !tile_req || !tile_row)
     return TL_ERR_UNSUPPORTED;
@@ -549,7 +646,11 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.window = window;
   p.rows_per_tile = tl_attention_tc_rows(nh / nkv) / QTILES;
   p.scale_log2 = scale * 1.4426950408889634f;
-  return d == 128 ? launch<128>(map_kv, p, nkv, tiles, stream) : launch<64>(map_kv, p, nkv, tiles, stream);
+  p.splits = splits;
+  p.part_acc = (float*)workspace;
+  p.part_ml = p.part_acc + (size_t)(splits > 1 ? tokens : 0) * nh * splits * d;
+  return d == 128 ? launch<128>(map_kv, p, nkv, tiles, token_req, tokens, stream)
+                  : launch<64>(map_kv, p, nkv, tiles, token_req, tokens, stream);
 }
 
 }  // extern "C"

@@ -73,7 +73,7 @@ _SIGNATURES = {
     "attention_tc": {
         "tl_attention_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
-                            c_void_p],
+                            c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p],
         "tl_attention_tc_error": [],
         "tl_attention_tc_rows": [c_int],
     },
@@ -460,16 +460,22 @@ def attention_tc_supported(d: int, group: int, page_size: int) -> bool:
 
 
 def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, nh, nkv, d,
-                 page_size, window, scale) -> None:
+                 page_size, window, scale, splits: int = 1, token_req=None) -> None:
     """Prompt-portion attention on tcgen05 (csrc/attention_tc.cu): tiles of packed rows
-    (``tile_row`` multiples of ``attention_tc_rows(nh // nkv)``)."""
-    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
+    (``tile_row`` multiples of ``attention_tc_rows(nh // nkv)``) that cover every request of the
+    step with more than one token.  ``splits`` > 1: that many CTAs share the key tiles of each
+    (row tiles, KV head) and a second kernel merges them (``token_req``: each token's request)."""
+    _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out, token_req)
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16 and pages.is_contiguous()
+    tokens = qkv.shape[0]
+    need = tokens * nh * splits * (d + 2) * 4 if splits > 1 else 0
+    ws = _workspace(("attention", qkv.device), need) if need else None
     code = _fn("attention_tc", "tl_attention_tc")(
         qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),
         block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), tile_req.data_ptr(), tile_row.data_ptr(),
-        tiles, out.data_ptr(), out.stride(0), nh, nkv, d, page_size, int(window or 0), float(scale), _stream())
-    _check(code, "attention_tc")
+        tiles, out.data_ptr(), out.stride(0), nh, nkv, d, page_size, int(window or 0), float(scale), splits,
+        _ptr(token_req), tokens, _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
+    _check(code, "attention_tc", 2 if splits > 1 else 1)
 
 
 def attention_mma_error() -> int:

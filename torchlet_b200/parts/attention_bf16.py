@@ -41,6 +41,20 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int, device=
     return max(1, min(room, -(-max_kv_len // 128), 64))
 
 
+def prompt_splits(ctas: int, max_kv_len: int, device=None) -> int:
+    """Key splits of the tcgen05 prompt attention.  A portion of a prompt beside decoding requests
+    has few row tiles (a 512-token portion at 4 KV heads: 60 CTAs for 148 SMs) and each walks the
+    whole cached prefix, one key tile after the other.  Where two to four times as many CTAs still
+    fit ONE wave, that many share the key tiles of a (row tiles, KV head) and a second kernel
+    merges their partial results: 71 -> 51 us for such a portion behind 3,584 cached tokens.  A
+    second wave, or a grid that fills the GPU anyway, loses more to the partial results' trip
+    through memory than the shorter walk gains (88 CTAs: 74 us whole, 77-90 us split; a whole
+    2,048-token prompt: 47 -> 88 us), and so do contexts of fewer than eight key tiles."""
+    index = torch.cuda.current_device() if device is None or device.index is None else device.index
+    key_tiles = -(-max_kv_len // 128)
+    return max(1, min(4, _sm_count(index) // max(1, ctas), key_tiles // 4))
+
+
 def _plan(ctx, group_size: int, rows_per_tile: int = ROWS):
     """Which requests decode, and the row tiles of the others (uploaded once a step)."""
     key = ("attention_mma", group_size, rows_per_tile)
@@ -93,7 +107,8 @@ def forward(mixer, ctx, qkv, cache, out) -> bool:
     if plan["prefill"] is not None and use_tc:
         tile_req, tile_row, count = plan["prefill"]
         ops.attention_tc(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row, count,
-                         out, nh, nkv, d, cache.page_size, mixer.window, mixer.scale)
+                         out, nh, nkv, d, cache.page_size, mixer.window, mixer.scale,
+                         splits=prompt_splits(count * nkv, ctx.max_kv_len, qkv.device), token_req=ctx.token_req)
     elif plan["prefill"] is not None:
         tile_req, tile_row, count = plan["prefill"]
         ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row,
