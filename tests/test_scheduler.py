@@ -188,6 +188,7 @@ def test_random_workloads_finish_and_return_all_pages(seed):
             assert r.output_tokens == [1000 + n + i for i in range(r.params.max_new_tokens)]
     assert runner.cache.live_requests() == []
     assert runner.cache.pools[0].num_free == runner.cache.pools[0].num_pages - 1
+    assert 0 < sched.stats.peak_pages <= runner.cache.pools[0].num_pages - 1  # the pool's high-water mark
 
 
 def test_state_only_model_schedules_by_slots_alone():

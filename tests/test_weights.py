@@ -61,7 +61,7 @@ def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
     folder = write_random_model(tmp_path / "m", cfg, seed=9, std=0.03, norm_std=0.02)
     assert load_config(folder) == Qwen2Config.from_dict(json.loads((folder / "config.json").read_text()))
     tensors = load_checkpoint(folder, _expected(tiny_configs.TINY_B))
-    assert all(t.dtype == torch.bfloat16 for t in tensors.values())
+    assert all(tensors[name].dtype == torch.bfloat16 for name in tensors)
     again = random_tensors(cfg, seed=9, std=0.03, norm_std=0.02)
     other = random_tensors(cfg, seed=10, std=0.03, norm_std=0.02)
     name = "model.layers.2.mlp.down_proj.weight"
@@ -74,3 +74,36 @@ def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
 def test_missing_files(tmp_path):
     with pytest.raises(FileNotFoundError):
         load_checkpoint(tmp_path, [])
+
+
+def test_sharded_checkpoint_with_an_index_and_errors_found_without_reading(tmp_path):
+    """Two shards and the table of contents that names them; a stray file the index does not list
+    is not read; shapes are checked from the files' headers, tensors are read one at a time."""
+    from safetensors.torch import save_file
+
+    from torchlet_b200.weights import LazyCheckpoint
+
+    cfg, init = tiny_configs.ALL["A"]
+    weights = tiny_configs.make_weights(cfg, dtype=torch.bfloat16, **init)
+    names = sorted(weights)
+    shards = {"model-00001-of-00002.safetensors": names[: len(names) // 2],
+              "model-00002-of-00002.safetensors": names[len(names) // 2:]}
+    for file, part in shards.items():
+        save_file({n: weights[n].contiguous() for n in part}, str(tmp_path / file))
+    save_file({"stray.tensor": torch.zeros(3)}, str(tmp_path / "leftover.safetensors"))
+    index = {"metadata": {}, "weight_map": {n: file for file, part in shards.items() for n in part}}
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    tensors = load_checkpoint(tmp_path, _expected(cfg))
+    assert isinstance(tensors, LazyCheckpoint) and set(tensors) == set(names)
+    assert tensors.meta("model.embed_tokens.weight") == ((256, 64), torch.bfloat16)
+    assert all(torch.equal(tensors[n], weights[n]) for n in names)
+    # without the index every file counts, and the stray tensor is reported
+    (tmp_path / "model.safetensors.index.json").unlink()
+    with pytest.raises(WeightsError) as info:
+        load_checkpoint(tmp_path, _expected(cfg))
+    assert info.value.unexpected == ["stray.tensor"]
+    # an index that names a file that is not there says so
+    index["weight_map"][names[0]] = "model-00003-of-00002.safetensors"
+    (tmp_path / "model.safetensors.index.json").write_text(json.dumps(index))
+    with pytest.raises(FileNotFoundError, match="00003"):
+        load_checkpoint(tmp_path, _expected(cfg))

@@ -225,7 +225,8 @@ def stress05b(layers: int = 24, count: int = 256, sample: int = 6, check_float32
                  "total_tok_s": round((stats.prefill_tokens + stats.decode_tokens) / run["seconds"], 1),
                  "preemptions": stats.preemptions, "recomputed_tokens": stats.prefill_tokens - sum(
                      len(r.prompt_tokens) for r in requests),
-                 "peak_running": stats.peak_running, "graph_steps": engine.runner.graph_steps}
+                 "peak_running": stats.peak_running, "peak_pages": stats.peak_pages,
+                 "graph_steps": engine.runner.graph_steps}
         if dtype == "float32":  # a sample of the requests, each run alone: the very same tokens
             alone = Engine(model, EngineConfig(dtype=dtype, max_decode_slots=1, kv_block_size=page, max_seq_len=context,
                                                max_num_batched_tokens=2048, cuda_graph=False))

@@ -48,6 +48,7 @@ class PagePool:
         self.num_pages = num_pages
         self._free = list(range(num_pages - 1, 0, -1))  # pop() hands out 1, 2, ...
         self._held = [False] * num_pages
+        self.peak_held = 0  # the most pages that were ever held at once (the pool's high-water mark)
 
     @property
     def num_free(self) -> int:
@@ -59,6 +60,7 @@ class PagePool:
         pages = [self._free.pop() for _ in range(count)]
         for page in pages:
             self._held[page] = True
+        self.peak_held = max(self.peak_held, self.num_pages - 1 - len(self._free))
         return pages
 
     def give_back(self, pages) -> None:

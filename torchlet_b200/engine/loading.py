@@ -24,7 +24,10 @@ def build_model(config, tensors: dict, dtype, device="cuda:0") -> LayeredModel:
     tensors = check_and_normalise(tensors, expected_tensors(spec))
     torch_dtype = TORCH_DTYPES[dtype] if isinstance(dtype, str) else dtype
     if torch_dtype == torch.bfloat16:
-        wide = [n for n, t in tensors.items() if t.dim() >= 2 and t.dtype == torch.float32]
+        if hasattr(tensors, "meta"):  # a lazy checkpoint: shapes and dtypes without reading anything
+            wide = [n for n in tensors if len(tensors.meta(n)[0]) >= 2 and tensors.meta(n)[1] == torch.float32]
+        else:
+            wide = [n for n, t in tensors.items() if t.dim() >= 2 and t.dtype == torch.float32]
         if wide:
             logger.warning("%d matrices stored in 32-bit are rounded to bfloat16 for the bfloat16 kernels", len(wide))
     model = LayeredModel(spec)

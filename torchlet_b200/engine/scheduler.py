@@ -101,6 +101,7 @@ class SchedulerStats:
     failed: int = 0
     finished: int = 0
     peak_running: int = 0
+    peak_pages: int = 0  # the most pages held at once, over all pools
 
 
 class Scheduler:
@@ -239,6 +240,7 @@ class Scheduler:
 
         plan.portions = list(scheduled.values())
         self.stats.peak_running = max(self.stats.peak_running, len(self.running))
+        self.stats.peak_pages = sum(pool.peak_held for pool in self.cache.pools)
         return plan
 
     # ---------------------------------------------------------------- update
