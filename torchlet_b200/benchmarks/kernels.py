@@ -79,7 +79,7 @@ def bench_attention(args) -> None:
     scale = d ** -0.5
     group = nh // nkv
     if q_len == 1:
-        splits = decode_splits(n, nkv, total)
+        splits = args.splits or decode_splits(n, nkv, total)
         run = lambda i: ops.attention_mma(qkv, pages, table, indptr, kv_before, None, None, n, out, n, nh, nkv, d, page,
                                           None, scale, rows16=True, splits=splits)
         kv_bytes = n * total * 2 * nkv * d * 2
@@ -130,7 +130,7 @@ def main(argv=None) -> int:
     attention.add_argument("--head-dim", type=int, default=128)
     attention.add_argument("--page-size", type=int, default=16)
     attention.add_argument("--splits", type=int, default=0,
-                           help="prompt portions on tcgen05: CTAs that share a row tile's key tiles (0: the engine's choice)")
+                           help="CTAs that share the key tiles of a (request or row tiles, KV head) (0: the engine's choice)")
     attention.add_argument("--kernel", choices=["tc", "mma"], default="tc",
                            help="prompt portions: tcgen05 kernel (head_dim 128) or the mma.sync kernel")
     for p in (gemm, attention):
