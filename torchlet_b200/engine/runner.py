@@ -252,6 +252,12 @@ class ModelRunner:
             return self._run_decode_graph(entries, feed_previous=True)
         if self._graphable(entries):
             return self._run_decode_graph(entries)
+        if self._graphable_for_logits(entries):
+            # single tokens whose logits are asked for and nothing sampled (trace replay): the same
+            # captured decode step; its sampling lane runs greedily and its token is not handed out
+            sampled = [StepEntry(e.request_id, e.tokens, sample=SampleSpec(0.0, 0, self.cache.num_tokens(e.request_id)))
+                       for e in entries]
+            return StepResult(self._run_decode_graph(sampled).logits, None)
         self._last_graph_ids = None
         ctx, caches = self._build(entries)
         with torch.no_grad():
@@ -287,6 +293,13 @@ class ModelRunner:
         if len(entries) > min(self.config.max_decode_slots, self.GRAPH_BUCKETS[-1]):
             return False
         return all(len(e.tokens) == 1 and e.sample is not None and not e.want for e in entries)
+
+    def _graphable_for_logits(self, entries) -> bool:
+        if not self.config.cuda_graph or not self._graph_safe:
+            return False
+        if len(entries) > min(self.config.max_decode_slots, self.GRAPH_BUCKETS[-1]):
+            return False
+        return all(len(e.tokens) == 1 and e.sample is None and list(e.want) == [0] for e in entries)
 
     def _bucket(self, n: int) -> int:
         for b in self.GRAPH_BUCKETS:

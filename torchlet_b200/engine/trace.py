@@ -63,7 +63,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
         max_num_blocks=num_pages + 1,
         max_seq_len=min(max_tokens, max_pos),
         max_num_batched_tokens=max(2048, min(max_tokens, max_pos)),
-        cuda_graph=False,
+        cuda_graph=True,  # steps of single tokens replay the captured decode step, as serving does
     )
     runner = ModelRunner(model, config)
     print("[trace_run] ready", file=sys.stderr, flush=True)
