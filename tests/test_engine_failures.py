@@ -120,3 +120,31 @@ def test_without_a_failure_both_loops_agree():
         assert all(r.error is None for r in requests)
         outputs.append([r.output_tokens for r in requests])
     assert outputs[0] == outputs[1]
+
+
+def test_the_loop_serves_requests_that_arrive_while_others_run():
+    """``Engine.run(poll)``: requests handed in by the poll callable between steps are admitted in
+    order of arrival; the loop ends when the source is exhausted and everything is finished."""
+    engine = _engine(FailingRunner())
+    requests = _requests() + [Request(list(range(6)), SamplingParams(max_new_tokens=3))]
+    schedule = {0: requests[:1], 3: requests[1:3], 4: [], 9: requests[3:]}
+    calls = [0]
+
+    def poll():
+        turn = calls[0]
+        calls[0] += 1
+        if turn > 9:
+            return None
+        return schedule.get(turn, [])
+
+    ended = engine.run(poll)
+    assert calls[0] >= 11 and {id(r) for r in ended} == {id(r) for r in requests}
+    assert all(r.error is None and r.state is RequestState.FINISHED for r in requests)
+    assert [r.output_tokens for r in requests][-1] == [1006, 1007, 1008]
+    assert engine.runner.cache.live_requests() == []
+    # an idle loop keeps asking until the source says that nothing more will come
+    idle = _engine(FailingRunner())
+    late = Request(list(range(4)), SamplingParams(max_new_tokens=2))
+    answers = iter([[], [], [late], [], None])
+    idle.run(lambda: next(answers))
+    assert late.output_tokens == [1004, 1005]

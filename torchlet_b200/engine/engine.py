@@ -112,13 +112,26 @@ class Engine:
             return None
         return StepPlan(portions, [], []), entries
 
-    def run(self) -> list:
-        """Step until no request is waiting or running; returns all that ended."""
+    def run(self, poll=None) -> list:
+        """Step until no request is waiting or running; returns all that ended.
+
+        ``poll``: a callable asked before every scheduling decision for the requests that have
+        arrived since the last call (a list, possibly empty), as the reference's loop drains its
+        queue every iteration (v10_triton_paged_gqa/scheduler.py:122-128); it returns None once
+        no more will come.  With it the loop serves requests that arrive while others run."""
         scheduler, runner = self.scheduler, self.runner
         ended = []
         ahead = None  # (plan, pinned tokens, event) of a step that is launched but not yet applied
         try:
-            while ahead is not None or scheduler.has_work():
+            while ahead is not None or scheduler.has_work() or poll is not None:
+                if poll is not None:
+                    arrived = poll()
+                    if arrived is None:
+                        poll = None
+                    elif arrived:
+                        self.add_requests(arrived)
+                    if ahead is None and not scheduler.has_work():
+                        continue
                 if ahead is None:
                     plan = scheduler.schedule()
                     ended += plan.failed
