@@ -122,6 +122,7 @@ class KernelCalls:
         self.counts = {name: 0 for name in self.NAMES}
         self.decode_splits = []
         self.prompt_splits = []
+        self.side_by_side = 0  # decode attention launched beside the prompt portions' kernel
         self._saved = {name: getattr(ops, name) for name in self.NAMES}
         for name, fn in self._saved.items():
             setattr(ops, name, self._wrap(name, fn))
@@ -132,6 +133,7 @@ class KernelCalls:
             self.counts[name] += 1
             if name == "attention_mma" and kwargs.get("rows16"):
                 self.decode_splits.append(kwargs.get("splits", 1))
+                self.side_by_side += bool(kwargs.get("late_wait"))
             if name == "attention_tc":
                 self.prompt_splits.append(kwargs.get("splits", 1))
             return fn(*args, **kwargs)

@@ -503,7 +503,7 @@ def test_attention_tc(case, d):
     # the key tiles shared by two, three and five CTAs, merged by the second kernel (a workspace full of NaN first:
     # a split that sees no key of a row writes no output for it, and the merge must leave that alone)
     for splits in (2, 3, 5):
-        ops._workspace(("attention", x["qkv"].device), x["T"] * nh * splits * (d + 2) * 4).fill_(float("nan"))
+        ops._workspace(("attention_tc", x["qkv"].device), x["T"] * nh * splits * (d + 2) * 4).fill_(float("nan"))
         split_out = torch.full((x["T"], nh * d), 7.0, device=DEV, dtype=torch.bfloat16)
         ops.attention_tc(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], to(tile_req), to(tile_row),
                          len(tile_req), split_out, nh, nkv, d, page, window, scale, splits=splits,
@@ -517,6 +517,46 @@ def test_attention_tc(case, d):
         v_spike = x["dense"][spike[0]][2][spike[2], 0].float()
         assert (want[token, :d] - v_spike).abs().max() < 0.05 * v_spike.abs().max()
         assert (out[token, :d].float().cpu() - v_spike).abs().max() < 0.05 * v_spike.abs().max()
+
+
+@pytest.mark.parametrize("d", [128, 64])
+@pytest.mark.parametrize("tc_splits", [1, 3])
+def test_prompt_and_decode_attention_side_by_side(d, tc_splits):
+    """A mixed step as the engine launches it: the prompt portions' kernel, the decode kernel right
+    behind it with its wait moved to its end (it starts on the SMs the first one leaves idle), then
+    the portions' deferred merge.  Every row against the plain formula, several times over, with
+    the decode keys unsplit, merged inside the kernel and merged by the second kernel."""
+    ops = _ops()
+    nh, nkv, page = 14, 2, 16
+    group = nh // nkv
+    before, q_lens = [700, 0, 1500, 40, 333, 2600], [1, 90, 1, 37, 1, 1]
+    x = paged_inputs(before, q_lens, nh, nkv, d, page, torch.bfloat16, seed=21)
+    scale = 0.37 / math.sqrt(d)
+    want = plain_attention(x["dense"], before, nh, nkv, None, scale)
+    rows = ops.attention_tc_rows(group)
+    tile_req, tile_row = [], []
+    for r, q in enumerate(q_lens):
+        if q > 1:
+            for start in range(0, q * group, rows):
+                tile_req.append(r)
+                tile_row.append(start)
+    to = lambda v: torch.tensor(v, dtype=torch.int32, device=DEV)
+    tile_req, tile_row, decoders = to(tile_req), to(tile_row), to([0, 2, 4, 5])
+    for decode_splits in (1, 4, 20):
+        for _ in range(4):
+            out = torch.full((x["T"], nh * d), float("nan"), device=DEV, dtype=torch.bfloat16)
+            merge = ops.attention_tc(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], tile_req, tile_row,
+                                     tile_req.numel(), out, nh, nkv, d, page, None, scale, splits=tc_splits,
+                                     token_req=x["token_req"], defer_merge=True)
+            ops.attention_mma(x["qkv"], x["pages"], x["table"], x["indptr"], x["before"], decoders, None, 4, out,
+                              x["T"], nh, nkv, d, page, None, scale, rows16=True, splits=decode_splits, late_wait=True)
+            assert (merge is None) == (tc_splits == 1)
+            if merge is not None:
+                merge()
+            host = out.float().cpu()
+            assert ops.attention_tc_error() == 0 and ops.attention_mma_error() == 0
+            assert torch.isfinite(host).all(), (decode_splits, "a row was left unwritten")
+            assert (host - want).abs().max() <= 1.5e-2 * want.abs().max(), decode_splits
 
 
 # -------------------------------------------- what a kernel must leave alone, or must not be hurt by

@@ -139,6 +139,7 @@ def test_mixed_batches_with_pages_used_again(name, dtype):
     check_kernels(calls, name, dtype, prompt=True, decode=True)
     if (name, dtype) in TENSOR_CORE:
         assert max(calls.decode_splits) > 1, "the keys of a decode step were never split over CTAs"
+        assert calls.side_by_side >= 10, "the decode attention never ran beside the prompt portions' kernel"
 
 
 @pytest.mark.parametrize("name, dtype", CASES)

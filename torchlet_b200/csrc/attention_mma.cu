@@ -65,6 +65,7 @@ struct Params {
   int num_pages;   // pages in the pool (checked in the debug build)
   int page_shift;  // log2(page_size) when it is a power of two, else -1
   int overlap_max_tiles;  // host only: overlapped launch up to this many row tiles
+  int late_wait;  // the kernel before this one has itself waited for q, keys and values: start at once, wait for it at the end
   float scale_log2;  // scale * log2(e)
 };
 
@@ -281,7 +282,10 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       ++issued;
     }
   }
-  tl::pdl_wait();               // q and this step's keys and values are now written and visible
+  // q and this step's keys and values are written and visible after the wait.  With late_wait the
+  // kernel before this one is the prompt portions' attention, which is independent of this one and
+  // whose every CTA had waited for them before this grid could start: the wait moves to the end.
+  if (!p.late_wait) tl::pdl_wait();
   tl::pdl_launch_dependents();  // the next kernel may start its own prologue
 
   // ---- Q rows into shared memory (zero for rows past the tile's end)
@@ -603,6 +607,8 @@ attention_mma_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p)
       }
     }
   }
+  // this grid is complete only when the one before it is: the next kernel waits for this one alone
+  if (p.late_wait) tl::pdl_wait();
 }
 
 // Merges the key splits of every (decode tile, head) in a kernel of its own (used when the caller
@@ -707,7 +713,7 @@ int launch(const CUtensorMap& map_kv, const Params& p, int tiles, cudaStream_t s
   // grids are launched WITHOUT overlap: CTAs that start while the small kernel before them
   // still occupies the SMs are placed unevenly, and a bandwidth-bound grid's time is set by
   // its most loaded SM (measured: batch 64 decode lost 9% with an overlapped launch).
-  tl::launch_kernel_opt(ROWS16 && tiles <= p.overlap_max_tiles, attention_mma_kernel<D, ROWS16, TMA, STAGES>, grid, THREADS,
+  tl::launch_kernel_opt(ROWS16 && (tiles <= p.overlap_max_tiles || p.late_wait), attention_mma_kernel<D, ROWS16, TMA, STAGES>, grid, THREADS,
                         SMEM, stream, map_kv, p);
   return TL_LAUNCH_CHECK();
 }
@@ -786,13 +792,16 @@ int tl_attention_mma_error() {
 // uses as many of them as its length warrants.  ``arrivals``: tiles * nkv ints, zero before the
 // call and zero again after it: the split that finishes last merges (one kernel); null: a second
 // kernel merges.
+// late_wait != 0 (16-row tiles only): the kernel launched just before on this stream is the prompt
+// portions' attention (tl_attention_tc), which neither reads nor writes anything this call writes;
+// this grid then starts beside it on the SMs it leaves idle and waits for it only at its end.
 // pages: one cache layer [num_pages][2][nkv][page_size][d].
 int tl_attention_mma(const void* q, long long q_stride, const void* pages, long long num_pages, const int* block_table,
                      int table_width,
                      const int* req_indptr, const int* kv_before, const int* tile_req, const int* tile_row,
                      int tiles, void* out, long long out_stride, int tokens, int nh, int nkv, int d, int page_size,
                      int window, float scale, int rows16, int splits, void* workspace, long long workspace_bytes,
-                     int* arrivals, cudaStream_t stream) {
+                     int* arrivals, int late_wait, cudaStream_t stream) {
   if (tiles <= 0 || tokens <= 0) return 0;
   if ((d != 64 && d != 128) || nkv <= 0 || nh % nkv || page_size <= 0 || q_stride % 8 || out_stride % 4)
     return TL_ERR_UNSUPPORTED;
@@ -819,6 +828,7 @@ int tl_attention_mma(const void* q, long long q_stride, const void* pages, long 
   p.page_size = page_size;
   p.num_pages = (int)num_pages;
   p.overlap_max_tiles = 32;
+  p.late_wait = (late_wait && rows16) ? 1 : 0;
   p.page_shift = -1;
   for (int b = 0; b < 20; ++b)
     if ((1 << b) == page_size) p.page_shift = b;

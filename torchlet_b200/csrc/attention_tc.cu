@@ -35,6 +35,7 @@
 // Every mbarrier wait is bounded (tcgen05.cuh); a wait that gives up records a code that
 // tl_attention_tc_error() returns, and the CTA still runs to its end and frees its TMEM.
 #include <math.h>
+#include <string.h>
 
 #include <mutex>
 #include <unordered_map>
@@ -249,8 +250,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_kv, const Params p) 
     tmem_alloc<512>(tmem_slot);
     tmem_relinquish();
   }
+  // First the wait, then the signal: when the next kernel starts, every CTA of this one has seen
+  // the preceding kernels' q, keys and values complete.  A decode attention launched right behind
+  // may therefore start on the SMs this grid leaves idle without a wait of its own at its start
+  // (csrc/attention_mma.cu, ``late_wait``).
+  tl::pdl_wait();
   tl::pdl_launch_dependents();
-  tl::pdl_wait();  // q and this step's keys and values come from the preceding kernels
 
   // ---- Q rows into shared memory in the K-major swizzled layout (all threads)
   for (int i = threadIdx.x; i < QTILES * ROWS * (D / 8); i += THREADS) {
@@ -569,8 +574,15 @@ bool cached_map(CUtensorMap* out, const void* base, uint64_t rows, uint32_t cols
 }
 
 template <int D>
+int launch_merge(const Params& p, const int* token_req, int tokens, cudaStream_t stream) {
+  tl::launch_kernel(attention_tc_merge_kernel<D>, (tokens * p.nh + 3) / 4, 128, 0, stream, (const float*)p.part_acc,
+                    (const float*)p.part_ml, token_req, p.req_indptr, p.out, p.out_stride, tokens, p.nh, p.splits);
+  return TL_LAUNCH_CHECK();
+}
+
+template <int D>
 int launch(const CUtensorMap& map_kv, const Params& p, int nkv, int tiles, const int* token_req, int tokens,
-           cudaStream_t stream) {
+           bool defer_merge, cudaStream_t stream) {
   constexpr int SMEM = 6 * TileBytes<D>::value + 1024 + 256;
   static_assert(SMEM <= 232448, "shared memory of one CTA");
   static bool configured = false;
@@ -581,10 +593,8 @@ int launch(const CUtensorMap& map_kv, const Params& p, int nkv, int tiles, const
   }
   tl::launch_kernel(attention_tc_kernel<D>, dim3(nkv, tiles, p.splits), THREADS, SMEM, stream, map_kv, p);
   const int rc = TL_LAUNCH_CHECK();
-  if (rc || p.splits == 1) return rc;
-  tl::launch_kernel(attention_tc_merge_kernel<D>, (tokens * p.nh + 3) / 4, 128, 0, stream, (const float*)p.part_acc,
-                    (const float*)p.part_ml, token_req, p.req_indptr, p.out, p.out_stride, tokens, p.nh, p.splits);
-  return TL_LAUNCH_CHECK();
+  if (rc || p.splits == 1 || defer_merge) return rc;
+  return launch_merge<D>(p, token_req, tokens, stream);
 }
 
 }  // namespace
@@ -612,12 +622,13 @@ long long tl_attention_tc_workspace(int tokens, int nh, int d, int splits) {
 // splits > 1 (for grids that would leave most of the GPU idle): that many CTAs share the key
 // tiles of each (row tiles, KV head) and a second kernel merges their partial results, which
 // live in ``workspace`` (tl_attention_tc_workspace bytes); token_req [tokens] names each token's
-// request.
+// request.  defer_merge != 0: the merge is left to a later tl_attention_tc_merge on the same stream
+// (so that another kernel may run between the two; the workspace must stay untouched meanwhile).
 int tl_attention_tc(const void* q, long long q_stride, const void* pages, long long num_pages,
                     const int* block_table, int table_width, const int* req_indptr, const int* kv_before,
                     const int* tile_req, const int* tile_row, int tiles, void* out, long long out_stride, int nh,
                     int nkv, int d, int page_size, int window, float scale, int splits, const int* token_req,
-                    int tokens, void* workspace, long long workspace_bytes, cudaStream_t stream) {
+                    int tokens, void* workspace, long long workspace_bytes, int defer_merge, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (splits < 1 || splits > 64) return TL_ERR_UNSUPPORTED;
   if (splits > 1 && (!token_req || tokens <= 0 || !workspace ||
@@ -649,8 +660,29 @@ int tl_attention_tc(const void* q, long long q_stride, const void* pages, long l
   p.splits = splits;
   p.part_acc = (float*)workspace;
   p.part_ml = p.part_acc + (size_t)(splits > 1 ? tokens : 0) * nh * splits * d;
-  return d == 128 ? launch<128>(map_kv, p, nkv, tiles, token_req, tokens, stream)
-                  : launch<64>(map_kv, p, nkv, tiles, token_req, tokens, stream);
+  return d == 128 ? launch<128>(map_kv, p, nkv, tiles, token_req, tokens, defer_merge != 0, stream)
+                  : launch<64>(map_kv, p, nkv, tiles, token_req, tokens, defer_merge != 0, stream);
+}
+
+// The merge that a tl_attention_tc call with defer_merge left undone: same out, sizes, splits,
+// token_req and workspace as that call.
+int tl_attention_tc_merge(const int* req_indptr, void* out, long long out_stride, int nh, int d, int splits,
+                          const int* token_req, int tokens, void* workspace, long long workspace_bytes,
+                          cudaStream_t stream) {
+  if (splits <= 1 || tokens <= 0) return 0;
+  if ((d != 64 && d != 128) || !token_req || !workspace || out_stride % 8 ||
+      workspace_bytes < tl_attention_tc_workspace(tokens, nh, d, splits))
+    return TL_ERR_UNSUPPORTED;
+  Params p;
+  memset(&p, 0, sizeof(p));
+  p.req_indptr = req_indptr;
+  p.out = (__nv_bfloat16*)out;
+  p.out_stride = out_stride;
+  p.nh = nh;
+  p.splits = splits;
+  p.part_acc = (float*)workspace;
+  p.part_ml = p.part_acc + (size_t)tokens * nh * splits * d;
+  return d == 128 ? launch_merge<128>(p, token_req, tokens, stream) : launch_merge<64>(p, token_req, tokens, stream);
 }
 
 }  // extern "C"

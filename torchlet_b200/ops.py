@@ -59,7 +59,7 @@ _SIGNATURES = {
     "attention_mma": {
         "tl_attention_mma": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                              c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-                             c_int, c_int, c_void_p, c_longlong, c_void_p, c_void_p],
+                             c_int, c_int, c_void_p, c_longlong, c_void_p, c_int, c_void_p],
         "tl_attention_mma_error": [],
         "tl_attention_mma_debug_error": [c_void_p],
     },
@@ -73,7 +73,9 @@ _SIGNATURES = {
     "attention_tc": {
         "tl_attention_tc": [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
                             c_void_p, c_int, c_void_p, c_longlong, c_int, c_int, c_int, c_int, c_int, c_float,
-                            c_int, c_void_p, c_int, c_void_p, c_longlong, c_void_p],
+                            c_int, c_void_p, c_int, c_void_p, c_longlong, c_int, c_void_p],
+        "tl_attention_tc_merge": [c_void_p, c_void_p, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+                                  c_longlong, c_void_p],
         "tl_attention_tc_error": [],
         "tl_attention_tc_rows": [c_int],
     },
@@ -426,12 +428,14 @@ _merge_in_kernel = os.environ.get("TORCHLET_B200_DECODE_MERGE", "") != "kernel"
 
 
 def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, tokens, nh, nkv,
-                  d, page_size, window, scale, rows16: bool, splits: int = 1) -> None:
+                  d, page_size, window, scale, rows16: bool, splits: int = 1, late_wait: bool = False) -> None:
     """Tensor-core paged attention (csrc/attention_mma.cu).  ``tile_req``/``tile_row`` None:
     tile i is request i from its first packed row.  With ``splits`` > 1 every tile is a request
     that brings one token; only those tokens' rows of ``out`` are written.  ``splits`` is the
     number of CTAs the grid holds for a request's keys; the kernel uses as many as the request's
-    own length warrants."""
+    own length warrants.  ``late_wait`` (16-row tiles): the launch just before this one on the
+    stream was ``attention_tc`` for the other requests of the same step; this grid starts beside
+    it and waits for it at its end instead of at its start."""
     _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out)
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16
     # key splits: float32 partial results of every (decode tile, head, split); the split that finishes last merges
@@ -446,7 +450,7 @@ def attention_mma(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile
         block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), _ptr(tile_req), _ptr(tile_row), tiles,
         out.data_ptr(), out.stride(0), tokens, nh, nkv, d, page_size, int(window or 0), float(scale),
         1 if rows16 else 0, splits,
-        _ptr(ws), ws.numel() * 4 if ws is not None else 0, _ptr(arrivals), _stream())
+        _ptr(ws), ws.numel() * 4 if ws is not None else 0, _ptr(arrivals), 1 if late_wait else 0, _stream())
     _check(code, "attention_mma", 2 if splits > 1 and arrivals is None else 1)
 
 
@@ -460,22 +464,37 @@ def attention_tc_supported(d: int, group: int, page_size: int) -> bool:
 
 
 def attention_tc(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, tiles, out, nh, nkv, d,
-                 page_size, window, scale, splits: int = 1, token_req=None) -> None:
+                 page_size, window, scale, splits: int = 1, token_req=None, defer_merge: bool = False):
     """Prompt-portion attention on tcgen05 (csrc/attention_tc.cu): tiles of packed rows
     (``tile_row`` multiples of ``attention_tc_rows(nh // nkv)``) that cover every request of the
     step with more than one token.  ``splits`` > 1: that many CTAs share the key tiles of each
-    (row tiles, KV head) and a second kernel merges them (``token_req``: each token's request)."""
+    (row tiles, KV head) and a second kernel merges them (``token_req``: each token's request).
+    ``defer_merge``: that second kernel is not launched; the call returns a function that launches
+    it (None when there is nothing to merge), so that the decode attention may run between the two.
+    The partial results have a workspace of their own."""
     _need_cuda(qkv, pages, block_table, req_indptr, kv_before, tile_req, tile_row, out, token_req)
     assert qkv.dtype == pages.dtype == out.dtype == torch.bfloat16 and pages.is_contiguous()
     tokens = qkv.shape[0]
     need = tokens * nh * splits * (d + 2) * 4 if splits > 1 else 0
-    ws = _workspace(("attention", qkv.device), need) if need else None
+    ws = _workspace(("attention_tc", qkv.device), need) if need else None
+    ws_bytes = ws.numel() * 4 if ws is not None else 0
+    defer = defer_merge and splits > 1
     code = _fn("attention_tc", "tl_attention_tc")(
         qkv.data_ptr(), qkv.stride(0), pages.data_ptr(), pages.shape[0], block_table.data_ptr(),
         block_table.shape[1], req_indptr.data_ptr(), kv_before.data_ptr(), tile_req.data_ptr(), tile_row.data_ptr(),
         tiles, out.data_ptr(), out.stride(0), nh, nkv, d, page_size, int(window or 0), float(scale), splits,
-        _ptr(token_req), tokens, _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream())
-    _check(code, "attention_tc", 2 if splits > 1 else 1)
+        _ptr(token_req), tokens, _ptr(ws), ws_bytes, 1 if defer else 0, _stream())
+    _check(code, "attention_tc", 2 if splits > 1 and not defer else 1)
+    if not defer:
+        return None
+
+    def merge() -> None:
+        code = _fn("attention_tc", "tl_attention_tc_merge")(
+            req_indptr.data_ptr(), out.data_ptr(), out.stride(0), nh, d, splits, token_req.data_ptr(), tokens,
+            ws.data_ptr(), ws_bytes, _stream())
+        _check(code, "attention_tc_merge", 1)
+
+    return merge
 
 
 def attention_mma_error() -> int:

@@ -18,8 +18,12 @@ import torch
 from .. import ops
 
 import functools
+import os
 
 ROWS = 64
+# TORCHLET_B200_ATTENTION_BESIDE=0: in a mixed step the decode attention waits for the prompt
+# portions' kernel to end before it starts (for measurements)
+SIDE_BY_SIDE = os.environ.get("TORCHLET_B200_ATTENTION_BESIDE", "1") != "0"
 
 
 @functools.lru_cache(maxsize=None)
@@ -55,6 +59,26 @@ def prompt_splits(ctas: int, max_kv_len: int, device=None) -> int:
     return max(1, min(4, _sm_count(index) // max(1, ctas), key_tiles // 4))
 
 
+def side_by_side(prompt_splits_chosen: int, prompt_kv_len: int, head_dim: int) -> bool:
+    """Whether, in a mixed step, the decode kernel is launched right behind the prompt portions'
+    kernel with its wait at its end, so that its CTAs start on the SMs the portions leave idle (few
+    row tiles, or the last of several waves) instead of after the portions' last CTA.  Measured on
+    the two kernels of one layer, one after the other -> side by side, same key splits: 32 decoding
+    requests at 2,100 tokens beside a 512-token portion behind 1,792, 8 KV heads of 5 query heads,
+    97 -> 94 us, beside a 1,024-token portion 111 -> 92 us; 8 requests at 4,000 tokens 74 -> 65 us;
+    4 KV heads of 7: 72 -> 65 us beside 1,024 tokens, 48 -> 38 us for 4 requests at 600.  Where the
+    portions' keys are split the merge of their partial results has to wait for both kernels, which
+    costs 3-5 us: that is taken only where the portions' kernel runs some 15 us or more (a 128-key
+    tile takes it about 2.4 us at head_dim 128), else short kernels lose (2 KV heads at head_dim
+    64, four splits: 31 -> 35 us)."""
+    if not SIDE_BY_SIDE:
+        return False
+    if prompt_splits_chosen == 1:
+        return True
+    tiles = -(-prompt_kv_len // 128)
+    return 2.4 * tiles / prompt_splits_chosen * head_dim / 128 >= 15.0
+
+
 def _plan(ctx, group_size: int, rows_per_tile: int = ROWS):
     """Which requests decode, and the row tiles of the others (uploaded once a step)."""
     key = ("attention_mma", group_size, rows_per_tile)
@@ -78,6 +102,7 @@ def _plan(ctx, group_size: int, rows_per_tile: int = ROWS):
         if decode.size:
             plan["decode"] = (ctx.upload(decode), int(decode.size))
         if others.size:
+            plan["prefill_kv_len"] = int((ctx.kv_before_host[others] + q_lens[others]).max())
             req, row = np.concatenate(tile_req), np.concatenate(tile_row)
             # tiles that see the most keys first: the last CTAs to start are the short ones
             keys_seen = ctx.kv_before_host[req] + row // group_size
@@ -99,17 +124,24 @@ def forward(mixer, ctx, qkv, cache, out) -> bool:
     plan = _plan(ctx, group, ops.attention_tc_rows(group) if use_tc else ROWS)
     common = dict(out=out, tokens=ctx.num_tokens, nh=nh, nkv=nkv, d=d, page_size=cache.page_size,
                   window=mixer.window, scale=mixer.scale)
+    # A mixed step: the prompt portions first (few CTAs that walk long contexts), the decoding
+    # requests' kernel right behind it on the SMs it leaves idle; the two touch different rows.
+    merge_portions, beside = None, False
+    if plan["prefill"] is not None and use_tc:
+        tile_req, tile_row, count = plan["prefill"]
+        splits = prompt_splits(count * nkv, plan["prefill_kv_len"], qkv.device)
+        beside = plan["decode"] is not None and side_by_side(splits, plan["prefill_kv_len"], d)
+        merge_portions = ops.attention_tc(
+            qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row, count, out, nh, nkv,
+            d, cache.page_size, mixer.window, mixer.scale, splits=splits, token_req=ctx.token_req, defer_merge=beside)
     if plan["decode"] is not None:
         tile_req, count = plan["decode"]
         splits = decode_splits(count, nkv, ctx.max_kv_len, qkv.device)
         ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, None,
-                          count, rows16=True, splits=splits, **common)
-    if plan["prefill"] is not None and use_tc:
-        tile_req, tile_row, count = plan["prefill"]
-        ops.attention_tc(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row, count,
-                         out, nh, nkv, d, cache.page_size, mixer.window, mixer.scale,
-                         splits=prompt_splits(count * nkv, ctx.max_kv_len, qkv.device), token_req=ctx.token_req)
-    elif plan["prefill"] is not None:
+                          count, rows16=True, splits=splits, late_wait=beside, **common)
+    if merge_portions is not None:
+        merge_portions()
+    if plan["prefill"] is not None and not use_tc:
         tile_req, tile_row, count = plan["prefill"]
         ops.attention_mma(qkv, cache.pages, cache.block_table, ctx.req_indptr, ctx.kv_before, tile_req, tile_row,
                           count, rows16=False, splits=1, **common)
