@@ -148,3 +148,109 @@ def test_the_loop_serves_requests_that_arrive_while_others_run():
     answers = iter([[], [], [late], [], None])
     idle.run(lambda: next(answers))
     assert late.output_tokens == [1004, 1005]
+
+
+# ------------------------------------------------------------- the loop as an asyncio task
+def _expected(prompt_len, new_tokens):
+    return [1000 + prompt_len + k for k in range(new_tokens)]
+
+
+def test_coroutines_hand_in_requests_while_the_loop_runs():
+    """The reference's manner of use (v10_triton_paged_gqa/llm.py:113-140): several coroutines
+    that start at different times await their requests; one loop, an asyncio task, serves them
+    all, and ``shutdown`` ends it."""
+    import asyncio
+
+    engine = _engine(FailingRunner())
+
+    async def caller(delay, lengths, new_tokens):
+        await asyncio.sleep(delay)
+        requests = [Request(list(range(n)), SamplingParams(max_new_tokens=new_tokens)) for n in lengths]
+        assert await engine.submit(requests) is requests
+        return requests
+
+    async def main():
+        try:
+            groups = await asyncio.gather(caller(0.0, (20, 3), 6), caller(0.01, (9,), 4), caller(0.02, (30, 5, 7), 3))
+            task = engine._task
+            assert task is not None and not task.done()  # the loop idles, it has not ended
+            late = await caller(0.0, (11,), 2)  # ... and serves a later caller with the same task
+            assert engine._task is task
+            return groups + [late]
+        finally:
+            await engine.shutdown()
+
+    groups = asyncio.run(main())
+    for group in groups:
+        for request in group:
+            assert request.error is None and request.state is RequestState.FINISHED
+            assert request.output_tokens == _expected(len(request.prompt_tokens), request.params.max_new_tokens)
+    assert engine._task is None and not engine._waiting_callers and not engine._inbox
+    engine.runner.cache.check()
+    assert engine.runner.cache.live_requests() == [] and engine.runner.cache.num_free_slots == 3
+
+
+def test_shutdown_ends_live_requests_and_the_engine_starts_again():
+    import asyncio
+
+    engine = _engine(FailingRunner())
+    long = [Request(list(range(n)), SamplingParams(max_new_tokens=200)) for n in (20, 9, 4, 6)]
+
+    async def main():
+        waiting = asyncio.create_task(engine.submit(long))
+        for _ in range(50):  # let the loop run some steps
+            await asyncio.sleep(0)
+        assert any(r.output_tokens for r in long) and not waiting.done()
+        await engine.shutdown()
+        assert (await waiting) is long  # the caller is released, its requests carry the reason
+        fresh = [Request(list(range(11)), SamplingParams(max_new_tokens=4))]
+        await engine.submit(fresh)  # a new task serves the next caller
+        await engine.shutdown()
+        return fresh
+
+    fresh = asyncio.run(main())
+    import asyncio as _a
+    assert all(isinstance(r.error, _a.CancelledError) and r.state is RequestState.FINISHED for r in long)
+    assert fresh[0].error is None and fresh[0].output_tokens == _expected(11, 4)
+    engine.runner.cache.check()
+    assert engine.runner.cache.live_requests() == [] and engine.runner.cache.num_free_slots == 3
+    assert engine.runner.cache.pools[0].num_free == engine.runner.cache.pools[0].num_pages - 1
+
+
+def test_a_failed_step_releases_every_waiting_coroutine():
+    import asyncio
+
+    engine = _engine(FailingRunner(fail_at=3))
+
+    async def main():
+        first = [Request(list(range(n)), SamplingParams(max_new_tokens=8)) for n in (20, 3)]
+        second = [Request(list(range(9)), SamplingParams(max_new_tokens=8))]
+        await asyncio.gather(engine.submit(first), engine.submit(second))
+        assert engine._task.done()  # the loop ended with the failure ...
+        third = [Request(list(range(5)), SamplingParams(max_new_tokens=3))]
+        await engine.submit(third)  # ... and the next caller gets a new one
+        await engine.shutdown()
+        return first + second, third
+
+    failed, third = asyncio.run(main())
+    assert all(r.state is RequestState.FINISHED for r in failed)
+    assert any(isinstance(r.error, RuntimeError) for r in failed)
+    assert all(isinstance(r.error, RuntimeError) or len(r.output_tokens) == 8 for r in failed)
+    assert third[0].error is None and third[0].output_tokens == _expected(5, 3)
+    engine.runner.cache.check()
+    assert engine.runner.cache.live_requests() == []
+
+
+def test_submit_refuses_a_bad_request_before_anything_is_handed_in():
+    import asyncio
+
+    engine = _engine(FailingRunner())
+
+    async def main():
+        good = Request(list(range(5)), SamplingParams(max_new_tokens=2))
+        with pytest.raises(ValueError):
+            await engine.submit([good, Request([], SamplingParams(max_new_tokens=2))])
+        assert not engine._inbox and not engine._waiting_callers and good.state is RequestState.WAITING
+        await engine.shutdown()
+
+    asyncio.run(main())

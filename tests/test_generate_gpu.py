@@ -69,6 +69,42 @@ def test_graph_decode_equals_eager_decode(tmp_path, dtype):
         assert same >= 0.8 * sum(len(x) for x in outs[0])
 
 
+def test_coroutines_that_arrive_one_after_the_other(tmp_path):
+    """``await llm.agenerate(...)`` from three coroutines that start at different times, the
+    reference's own demonstration (v10_triton_paged_gqa/llm.py:113-140): one engine loop serves
+    them together, and in float32 every output equals the synchronous ``generate`` of the same
+    prompt alone; ``shutdown`` ends the loop with nothing held."""
+    import asyncio
+
+    from torchlet_b200 import LLM, SamplingParams
+
+    folder = model_dir(tmp_path, "B")
+    prompts = prompts_for("B")
+    params = [SamplingParams(max_new_tokens=14 + 3 * i, temperature=t, seed=21 + i)
+              for i, t in enumerate((0.0, 0.8, 0.0, 1.1))]
+    llm = LLM(folder, max_decode_slots=3, kv_block_size=8, dtype="float32", max_seq_len=128)
+    alone = [llm.generate([p], sampling_params=[sp])[0] for p, sp in zip(prompts, params)]
+
+    async def main():
+        try:
+            tasks = []
+            for prompt, sp in zip(prompts, params):
+                tasks.append(asyncio.create_task(llm.agenerate([prompt], sampling_params=[sp])))
+                await asyncio.sleep(0.002)
+            return await asyncio.gather(*tasks)
+        finally:
+            await llm.shutdown()
+
+    before = llm.engine.scheduler.stats.steps
+    together = asyncio.run(main())
+    assert [out[0] for out in together] == alone
+    stats = llm.engine.scheduler.stats
+    assert stats.steps - before < sum(sp.max_new_tokens for sp in params), "the coroutines' requests never shared a step"
+    assert stats.peak_running == 3  # four callers, three slots: one waited its turn
+    llm.engine.runner.cache.check()
+    assert llm.engine.runner.cache.live_requests() == [] and llm.engine._task is None
+
+
 def test_sampling_does_not_depend_on_the_batch(tmp_path):
     from torchlet_b200 import LLM, SamplingParams
 

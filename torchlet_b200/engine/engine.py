@@ -6,9 +6,16 @@ finished (the reference's loop: v10_triton_paged_gqa/engine.py:101-135, 204-217)
 (see ``_next_decode``).  A failure inside a step ends every live request with that error
 and gives all pages and slots back, as the reference's ``fail_all`` does
 (engine.py:215-217).
+
+The reference is used from coroutines: its loop is an asyncio task that ``start()`` creates,
+callers ``await`` their requests while it runs, ``shutdown()`` cancels it
+(engine.py:77-99, llm.py:84-110).  ``start`` / ``submit`` / ``shutdown`` here do the same around
+the very loop that ``run`` drives: between two iterations the task yields to the other
+coroutines, which is when they hand in requests.
 """
 from __future__ import annotations
 
+import asyncio
 from typing import Optional
 
 from .. import ops
@@ -28,6 +35,11 @@ class Engine:
         self.runner = runner if runner is not None else ModelRunner(model, self.config)
         self.scheduler = Scheduler(self.runner, self.config.max_num_batched_tokens, self.config.max_seq_len)
         self.steps_ahead = 0  # decode steps launched before the tokens of the step before were read
+        # the loop as an asyncio task: requests handed in and not yet seen by the loop, who waits for which
+        self._task = None
+        self._inbox: list = []
+        self._waiting_callers: dict = {}
+        self._wake = None
 
     def add_requests(self, requests: list) -> None:
         for request in requests:
@@ -112,6 +124,8 @@ class Engine:
             return None
         return StepPlan(portions, [], []), entries
 
+    IDLE = object()  # what the loop yields when it has nothing to do and its source nothing to give
+
     def run(self, poll=None) -> list:
         """Step until no request is waiting or running; returns all that ended.
 
@@ -119,11 +133,21 @@ class Engine:
         arrived since the last call (a list, possibly empty), as the reference's loop drains its
         queue every iteration (v10_triton_paged_gqa/scheduler.py:122-128); it returns None once
         no more will come.  With it the loop serves requests that arrive while others run."""
-        scheduler, runner = self.scheduler, self.runner
         ended = []
+        for chunk in self._loop(poll):
+            if chunk is not Engine.IDLE:
+                ended += chunk
+        return ended
+
+    def _loop(self, poll):
+        """The loop itself, as a generator: after every iteration it yields the requests that
+        ended in it (``IDLE`` when there was nothing to do), so that its driver may do something
+        between two iterations.  A failed step fails every live request and is raised."""
+        scheduler, runner = self.scheduler, self.runner
         ahead = None  # (plan, pinned tokens, event) of a step that is launched but not yet applied
         try:
             while ahead is not None or scheduler.has_work() or poll is not None:
+                ended = []
                 if poll is not None:
                     arrived = poll()
                     if arrived is None:
@@ -131,17 +155,21 @@ class Engine:
                     elif arrived:
                         self.add_requests(arrived)
                     if ahead is None and not scheduler.has_work():
+                        if poll is not None:
+                            yield Engine.IDLE
                         continue
                 if ahead is None:
                     plan = scheduler.schedule()
                     ended += plan.failed
                     if not plan.portions:
                         scheduler.drain_finished()
+                        yield ended
                         continue
                     result = runner.run(self._entries(plan))
                     if result.tokens is None:  # portions of prompts that sample nothing
                         scheduler.update(plan, [])
                         scheduler.drain_finished()
+                        yield ended
                         continue
                     ahead = (plan, *runner.tokens_to_host(result))
                 plan, tokens, event = ahead
@@ -166,12 +194,89 @@ class Engine:
                     ops.raise_on_wait_errors()  # nothing is handed back before the kernels' error words are read
                     ended += done
                 scheduler.drain_finished()
+                yield ended
         except Exception as exc:  # a failed step fails every live request
-            ended += self._fail_everything(exc)
+            self._fail_everything(exc)
             raise
-        return ended
 
     def generate(self, requests: list) -> list:
         self.add_requests(requests)
         self.run()
         return requests
+
+    # ------------------------------------------------------------ the loop as an asyncio task
+    def start(self) -> None:
+        """Start the loop as a task of the running event loop unless it is running already
+        (the reference: engine.py:77-79)."""
+        if self._task is None or self._task.done():
+            self._wake = asyncio.Event()
+            self._task = asyncio.get_running_loop().create_task(self._serve())
+
+    async def submit(self, requests: list) -> list:
+        """Hand requests to the running loop (started if need be) and wait until every one of
+        them has ended; returns them (``error`` set on those that failed).  Several coroutines
+        may wait at the same time: their requests share the loop's batches."""
+        for request in requests:
+            self.scheduler.validate(request)
+        self.start()
+        loop = asyncio.get_running_loop()
+        futures = []
+        for request in requests:
+            futures.append(loop.create_future())
+            self._waiting_callers[request] = futures[-1]
+        self._inbox.extend(requests)
+        self._wake.set()
+        await asyncio.gather(*futures)
+        return requests
+
+    async def shutdown(self) -> None:
+        """Cancel the loop; whatever is live or handed in ends with ``asyncio.CancelledError`` as
+        its error, and every page and slot comes back (the reference: engine.py:81-96)."""
+        task, self._task = self._task, None
+        if task is None:
+            return
+        if not task.done():
+            task.cancel()
+            try:
+                await task
+            except asyncio.CancelledError:
+                pass
+        self._end_everything(asyncio.CancelledError())
+
+    def _end_everything(self, exc: BaseException) -> None:
+        """After the loop has stopped: what the scheduler still holds and what it never saw ends
+        with ``exc``; every waiting caller is released."""
+        self.scheduler.fail_all(exc)
+        self.scheduler.drain_finished()
+        for request in self._inbox:
+            request.error, request.state = exc, RequestState.FINISHED
+        self._inbox = []
+        self._release(list(self._waiting_callers))
+
+    def _release(self, requests: list) -> None:
+        for request in requests:
+            future = self._waiting_callers.pop(request, None)
+            if future is not None and not future.done():
+                future.set_result(request)
+
+    async def _serve(self) -> None:
+        def poll():
+            arrived, self._inbox = self._inbox, []
+            return arrived  # never None: the task lives until it is cancelled
+
+        loop = self._loop(poll)
+        try:
+            for ended in loop:
+                if ended is Engine.IDLE:
+                    self._wake.clear()
+                    if not self._inbox:
+                        await self._wake.wait()
+                    continue
+                self._release(ended)
+                await asyncio.sleep(0)  # the other coroutines' turn: this is when requests arrive
+        except asyncio.CancelledError:
+            loop.close()
+            raise
+        except Exception as exc:  # the loop has failed everything it held; the task ends, start() makes a new one
+            self._end_everything(exc)
+

@@ -7,8 +7,11 @@ list[str]`` (v10_triton_paged_gqa/llm.py:20-110), run as
 (llm.py:113-140).  Same names and meanings here: ``max_decode_slots`` is the most
 requests live at a time, ``kv_block_size`` the tokens per cache page, ``max_num_blocks``
 the size of the page pool including the reserved page 0.  Differences: the model comes
-from a local folder, ``generate`` is synchronous, prompts may also be lists of token
-ids (returned as token ids), and sampling options can be given.
+from a local folder, prompts may also be lists of token ids (returned as token ids), and
+sampling options can be given.  ``generate`` is synchronous; ``agenerate`` is the reference's
+coroutine: several may run at once, each handing its requests to the one engine loop, which is
+an asyncio task until ``await llm.shutdown()``.  Run without prompts, the command line does what
+the reference's does: three ``agenerate`` tasks that start a tenth of a second apart.
 
     python -m torchlet_b200.llm --model DIR --prompt "hello" --max-new-tokens 64
     python -m torchlet_b200.llm --model DIR --prompt-ids 1,2,3 --temperature 0.8 --seed 7
@@ -97,17 +100,9 @@ class LLM:
             ]
         return self.tokenizer(list(texts), padding=False)["input_ids"]
 
-    def generate(self, inputs: Sequence, max_new_tokens: int = 128,
-                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> list:
-        """Generate for every input.  Text inputs give text outputs, token-id inputs give
-        lists of token ids.  ``sampling_params`` (one for all, or one per input)
-        overrides ``max_new_tokens``."""
+    def _requests(self, inputs: Sequence, max_new_tokens: int, sampling_params) -> list:
         from .engine.scheduler import Request
 
-        if not inputs:
-            return []
-        if max_new_tokens <= 0 and sampling_params is None:
-            return ["" if isinstance(i, str) else [] for i in inputs]
         as_text = isinstance(inputs[0], str)
         token_lists = self._encode(inputs) if as_text else [list(i) for i in inputs]
         requests = []
@@ -121,7 +116,9 @@ class LLM:
             if not params.stop_token_ids and not params.ignore_eos:
                 params.stop_token_ids = tuple(sorted(self.stop_ids))
             requests.append(Request(tokens, params, prompt=inputs[i] if as_text else ""))
-        self.engine.generate(requests)
+        return requests
+
+    def _outputs(self, requests: list, as_text: bool) -> list:
         for request in requests:
             if request.error is not None:
                 raise request.error
@@ -131,6 +128,60 @@ class LLM:
                 request.output = text
             return list(outputs)
         return [list(r.output_tokens) for r in requests]
+
+    def generate(self, inputs: Sequence, max_new_tokens: int = 128,
+                 sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> list:
+        """Generate for every input.  Text inputs give text outputs, token-id inputs give
+        lists of token ids.  ``sampling_params`` (one for all, or one per input)
+        overrides ``max_new_tokens``."""
+        if not inputs:
+            return []
+        if max_new_tokens <= 0 and sampling_params is None:
+            return ["" if isinstance(i, str) else [] for i in inputs]
+        requests = self._requests(inputs, max_new_tokens, sampling_params)
+        self.engine.generate(requests)
+        return self._outputs(requests, isinstance(inputs[0], str))
+
+    async def agenerate(self, inputs: Sequence, max_new_tokens: int = 128,
+                        sampling_params: Union[SamplingParams, Sequence[SamplingParams], None] = None) -> list:
+        """``generate`` as a coroutine, the reference's form (llm.py:84-110): the requests join the
+        engine loop, which runs as an asyncio task and batches them with those of every other
+        ``agenerate`` that is waiting; returns when these have ended.  Not to be mixed with a
+        synchronous ``generate`` while the task lives (``await llm.shutdown()`` ends it)."""
+        if not inputs:
+            return []
+        if max_new_tokens <= 0 and sampling_params is None:
+            return ["" if isinstance(i, str) else [] for i in inputs]
+        requests = self._requests(inputs, max_new_tokens, sampling_params)
+        await self.engine.submit(requests)
+        return self._outputs(requests, isinstance(inputs[0], str))
+
+    async def shutdown(self) -> None:
+        """Ends the engine loop's task; requests still live end with ``asyncio.CancelledError``."""
+        await self.engine.shutdown()
+
+
+def _three_arrivals(llm: "LLM", params: SamplingParams) -> int:
+    """The reference's own demonstration (llm.py:113-140): its three built-in prompts as three
+    coroutines that start a tenth of a second apart, served by one engine loop."""
+    import asyncio
+
+    prompts = ["hello, do a simple introduction", "what's the nearest star", "write a short haiku about GPUs"]
+
+    async def arrive() -> list:
+        try:
+            tasks = []
+            for prompt in prompts:
+                tasks.append(asyncio.create_task(llm.agenerate([prompt], sampling_params=params)))
+                await asyncio.sleep(0.1)
+            return await asyncio.gather(*tasks)
+        finally:
+            await llm.shutdown()
+
+    for i, outputs in enumerate(asyncio.run(arrive()), start=1):
+        print(f"batch {i}:")
+        print(outputs)
+    return 0
 
 
 def main(argv=None) -> int:
@@ -168,8 +219,7 @@ def main(argv=None) -> int:
     elif args.prompt:
         prompts = args.prompt
     else:
-        # the reference's three built-in prompts (llm.py:118-130)
-        prompts = ["hello, do a simple introduction", "what's the nearest star", "write a short haiku about GPUs"]
+        return _three_arrivals(llm, params)
     outputs = llm.generate(prompts, sampling_params=params)
     for i, output in enumerate(outputs, start=1):
         print(f"output {i}:")
