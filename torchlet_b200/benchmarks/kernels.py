@@ -4,6 +4,7 @@ profiled with ncu for ``profiles/``).
     python -m torchlet_b200.benchmarks.kernels gemm --m 8 --n 37888 --k 3584 --epilogue swiglu
     python -m torchlet_b200.benchmarks.kernels attention --batch 8 --context 4096 --q-len 1
     python -m torchlet_b200.benchmarks.kernels attention --batch 1 --context 0 --q-len 2048
+    python -m torchlet_b200.benchmarks.kernels attention --batch 32 --context 2100 --portion 2016 --heads 40 --kv-heads 8
 
 Weights rotate through several copies so that together they exceed the 126 MB L2; each
 line reports the mean time of ``--iters`` launches after ``--warmup``.
@@ -111,6 +112,60 @@ def bench_attention(args) -> None:
           f"{flops / ms / 1e9:.1f} TFLOP/s, KV {kv_bytes / ms / 1e6:.0f} GB/s")
 
 
+def bench_mixed_attention(args) -> None:
+    """The two attention kernels of a mixed step (``--batch`` requests that decode at
+    ``--context`` tokens beside one ``--portion``-token portion of a prompt behind
+    ``--portion-context`` cached tokens): the decode kernel after the portion's kernel has ended,
+    and beside it (its wait moved to its end), with the engine's key splits."""
+    from ..parts.attention_bf16 import decode_splits, prompt_splits, side_by_side
+
+    nh, nkv, d, page = args.heads, args.kv_heads, args.head_dim, args.page_size
+    n, before, portion, behind = args.batch, args.context, args.portion, args.portion_context
+    group = nh // nkv
+    lengths = [before + 1] * n + [behind + portion]
+    widths = [-(-length // page) for length in lengths]
+    num_pages = sum(widths) + 1
+    pages = (torch.randn(num_pages, 2, nkv, page, d, device="cuda") * 0.5).bfloat16()
+    order = torch.randperm(num_pages - 1, device="cuda").to(torch.int32) + 1
+    table = torch.zeros(n + 1, max(widths), dtype=torch.int32, device="cuda")
+    start = 0
+    for i, w in enumerate(widths):
+        table[i, :w] = order[start:start + w]
+        start += w
+    tokens = n + portion
+    qkv = torch.randn(tokens, (nh + 2 * nkv) * d, device="cuda").bfloat16()
+    out = torch.zeros(tokens, nh * d, device="cuda", dtype=torch.bfloat16)
+    to = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    indptr, kv_before = to(list(range(n + 1)) + [tokens]), to([before] * n + [behind])
+    rows = ops.attention_tc_rows(group)
+    starts = list(range(0, portion * group, rows))[::-1]  # the tiles that see the most keys first
+    tile_req, tile_row, decoders = to([n] * len(starts)), to(starts), to(list(range(n)))
+    token_req = to(list(range(n)) + [n] * portion)
+    scale = d ** -0.5
+    p_splits = prompt_splits(len(starts) * nkv, behind + portion)
+    d_splits = decode_splits(n, nkv, max(lengths))
+
+    def run(beside: bool) -> None:
+        merge = ops.attention_tc(qkv, pages, table, indptr, kv_before, tile_req, tile_row, len(starts), out, nh, nkv, d,
+                                 page, None, scale, splits=p_splits, token_req=token_req, defer_merge=beside)
+        ops.attention_mma(qkv, pages, table, indptr, kv_before, decoders, None, n, out, tokens, nh, nkv, d, page, None,
+                          scale, rows16=True, splits=d_splits, late_wait=beside)
+        if merge is not None:
+            merge()
+
+    spacer = torch.zeros(1024, device="cuda")  # an ordinary launch between iterations: nothing overlaps across them
+
+    def timed(fn) -> float:
+        return _time(lambda i: (spacer.add_(1), fn()), args.iters, args.warmup)
+
+    empty = timed(lambda: None)
+    in_turn, beside = timed(lambda: run(False)) - empty, timed(lambda: run(True)) - empty
+    print(f"mixed attention: {n} decoding at {before} beside {portion} tokens behind {behind}, heads={nh}/{nkv} d={d}, "
+          f"portion CTAs {len(starts) * nkv} x {p_splits} key splits, decode key splits {d_splits}: in turn "
+          f"{in_turn * 1e3:.1f} us, side by side {beside * 1e3:.1f} us (the engine's choice: "
+          f"{'side by side' if side_by_side(p_splits, behind + portion, d) else 'in turn'})")
+
+
 def main(argv=None) -> int:
     parser = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     sub = parser.add_subparsers(dest="what", required=True)
@@ -133,6 +188,9 @@ def main(argv=None) -> int:
                            help="CTAs that share the key tiles of a (request or row tiles, KV head) (0: the engine's choice)")
     attention.add_argument("--kernel", choices=["tc", "mma"], default="tc",
                            help="prompt portions: tcgen05 kernel (head_dim 128) or the mma.sync kernel")
+    attention.add_argument("--portion", type=int, default=0,
+                           help="a mixed step: the --batch requests decode beside one portion of this many prompt tokens")
+    attention.add_argument("--portion-context", type=int, default=0, help="cached tokens before that portion")
     for p in (gemm, attention):
         p.add_argument("--iters", type=int, default=20)
         p.add_argument("--warmup", type=int, default=3)
@@ -141,6 +199,9 @@ def main(argv=None) -> int:
     args = parser.parse_args(argv)
     global USE_GRAPH
     USE_GRAPH = args.graph
+    if args.what == "attention" and args.portion > 0:
+        bench_mixed_attention(args)
+        return 0
     {"gemm": bench_gemm, "attention": bench_attention}[args.what](args)
     return 0
 

@@ -63,14 +63,15 @@ def side_by_side(prompt_splits_chosen: int, prompt_kv_len: int, head_dim: int) -
     """Whether, in a mixed step, the decode kernel is launched right behind the prompt portions'
     kernel with its wait at its end, so that its CTAs start on the SMs the portions leave idle (few
     row tiles, or the last of several waves) instead of after the portions' last CTA.  Measured on
-    the two kernels of one layer, one after the other -> side by side, same key splits: 32 decoding
-    requests at 2,100 tokens beside a 512-token portion behind 1,792, 8 KV heads of 5 query heads,
-    97 -> 94 us, beside a 1,024-token portion 111 -> 92 us; 8 requests at 4,000 tokens 74 -> 65 us;
-    4 KV heads of 7: 72 -> 65 us beside 1,024 tokens, 48 -> 38 us for 4 requests at 600.  Where the
-    portions' keys are split the merge of their partial results has to wait for both kernels, which
-    costs 3-5 us: that is taken only where the portions' kernel runs some 15 us or more (a 128-key
-    tile takes it about 2.4 us at head_dim 128), else short kernels lose (2 KV heads at head_dim
-    64, four splits: 31 -> 35 us)."""
+    the two kernels of one layer, one after the other -> side by side, same key splits
+    (``benchmarks.kernels attention --portion``): 32 decoding requests at 2,100 tokens beside a
+    1,024-token portion behind 1,024, 8 KV heads of 5 query heads, 108 -> 93 us; beside 2,016 tokens
+    at 4 KV heads of 7, 75 -> 72 us; at 2 KV heads of 7 and head_dim 64, 43 -> 38 us; nothing where
+    unsplit decode CTAs last as long as the portions' and do not all fit beside them (beside 512
+    tokens behind 1,792 at 8 KV heads: 92 us either way).  Where the portions' keys are split, the
+    merge of their partial results has to wait for both kernels, which costs 3-5 us: that is taken
+    only where the portions' kernel runs some 15 us or more (a 128-key tile takes it about 2.4 us
+    at head_dim 128), else short kernels lose (2 KV heads at head_dim 64, four splits: 32 -> 36 us)."""
     if not SIDE_BY_SIDE:
         return False
     if prompt_splits_chosen == 1:
