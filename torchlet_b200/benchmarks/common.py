@@ -1,5 +1,6 @@
-"""What the benchmarks share: the benchmark model (Qwen2.5-7B layer sizes, random bfloat16
-weights made on the GPU) and a cache filled with random keys and values."""
+"""What the benchmarks share: the layer sizes of Qwen2.5-7B (the benchmark model), 14B and 0.5B,
+a model of them with random bfloat16 weights made on the GPU, and a cache filled with random keys
+and values."""
 from __future__ import annotations
 
 import torch
@@ -9,6 +10,19 @@ QWEN25_7B = {
     "num_hidden_layers": 28, "num_attention_heads": 28, "num_key_value_heads": 4, "max_position_embeddings": 32768,
     "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
 }
+
+
+QWEN25_14B = {
+    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 152064, "hidden_size": 5120, "intermediate_size": 13824,
+    "num_hidden_layers": 48, "num_attention_heads": 40, "num_key_value_heads": 8, "max_position_embeddings": 32768,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
+}
+QWEN25_05B = {
+    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 151936, "hidden_size": 896, "intermediate_size": 4864,
+    "num_hidden_layers": 24, "num_attention_heads": 14, "num_key_value_heads": 2, "max_position_embeddings": 32768,
+    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
+}
+SIZES = {"7b": (QWEN25_7B, 4), "14b": (QWEN25_14B, 6), "0.5b": (QWEN25_05B, 5)}  # layer sizes and the seed of their weights
 
 
 def build_model(cfg: dict, layers: int, seed: int):

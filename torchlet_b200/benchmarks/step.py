@@ -1,9 +1,9 @@
 """What each kernel class costs inside the running decode step.
 
-    python -m torchlet_b200.benchmarks.step [--batch 8] [--context 4096] [--steps 64] [--layers 28]
-                                            [--max-seq-len N] [--only-full]
+    python -m torchlet_b200.benchmarks.step [--model 7b|14b|0.5b] [--batch 8] [--context 4096] [--steps 64]
+                                            [--layers N] [--max-seq-len N] [--only-full]
 
-Builds a model of Qwen2.5-7B layer sizes with random bfloat16 weights, gives ``batch``
+Builds a model of Qwen2.5-7B (14B, 0.5B) layer sizes with random bfloat16 weights, gives ``batch``
 requests a cached context of random keys and values, and times the decode step (CUDA events
 around replays of its CUDA graph) once as it is and once with each kernel class replaced by
 nothing.  The difference is that class's cost in place, overlap with its neighbours included.
@@ -19,7 +19,7 @@ from .. import ops
 from ..config import EngineConfig
 from ..engine import ModelRunner, StepEntry
 from ..sampling import SampleSpec
-from .common import QWEN25_7B, build_model, fill_context
+from .common import SIZES, build_model, fill_context
 
 CLASSES = ("attention_mma", "finish_accum_norm", "finish_qkv_rope")
 
@@ -61,14 +61,18 @@ def main(argv=None) -> int:
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=4096)
     parser.add_argument("--steps", type=int, default=64)
-    parser.add_argument("--layers", type=int, default=28)
+    parser.add_argument("--model", choices=sorted(SIZES), default="7b", help="whose layer sizes")
+    parser.add_argument("--layers", type=int, default=None, help="fewer layers than the configuration has")
     parser.add_argument("--max-seq-len", type=int, default=None,
                         help="the engine's length limit, if it is to differ from the context")
     parser.add_argument("--only-full", action="store_true", help="time the step as it is and stop")
     args = parser.parse_args(argv)
-    model = build_model(QWEN25_7B, args.layers, seed=4)
+    cfg, seed = SIZES[args.model]
+    args.layers = args.layers or cfg["num_hidden_layers"]
+    model = build_model(cfg, args.layers, seed=seed)
     full = time_step(model, args.batch, args.context, args.steps, max_seq_len=args.max_seq_len)
-    print(f"batch {args.batch}, context {args.context}, {args.layers} layers, length limit {args.max_seq_len or args.context}")
+    print(f"Qwen2.5-{args.model} layer sizes, batch {args.batch}, context {args.context}, {args.layers} layers, "
+          f"length limit {args.max_seq_len or args.context}")
     print(f"{'full step':32s} {full:9.1f} us")
     for name in () if args.only_full else CLASSES:
         original = getattr(ops, name)

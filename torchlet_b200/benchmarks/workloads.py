@@ -28,16 +28,7 @@ import time
 
 import torch
 
-QWEN25_14B = {
-    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 152064, "hidden_size": 5120, "intermediate_size": 13824,
-    "num_hidden_layers": 48, "num_attention_heads": 40, "num_key_value_heads": 8, "max_position_embeddings": 32768,
-    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": False,
-}
-QWEN25_05B = {
-    "architectures": ["Qwen2ForCausalLM"], "vocab_size": 151936, "hidden_size": 896, "intermediate_size": 4864,
-    "num_hidden_layers": 24, "num_attention_heads": 14, "num_key_value_heads": 2, "max_position_embeddings": 32768,
-    "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "attention_bias": True, "tie_word_embeddings": True,
-}
+from .common import QWEN25_05B, QWEN25_14B
 
 
 def _model(cfg: dict, layers: int, seed: int, dtype: str = "bfloat16"):
