@@ -12,12 +12,13 @@ from harness import assert_close, changing_cuts, make_runner, plain_logits, repl
 pytestmark = pytest.mark.gpu
 
 # A and B: the two tiny configurations (SIMT kernels in both dtypes: head_dim 16 and 32).  D and E
-# (head_dim 128 with 3 heads a KV head, head_dim 64 with 7): in bfloat16 every cut below runs
+# (head_dim 128 with 3 heads a KV head, head_dim 64 with 7) and F (head_dim 128, a window of 150 on two
+# of three layers): in bfloat16 every cut below runs
 # through the tensor-core attention kernels, the tcgen05 products and the fused finishing kernels.
 CASES = [(name, dtype) for name in ("A", "B") for dtype in ("float32", "bfloat16")] + [
-    ("D", "bfloat16"), ("E", "bfloat16"), ("E", "float32")]
-TENSOR_CORE = {("D", "bfloat16"), ("E", "bfloat16")}
-LENGTHS = {"A": (5, 17, 33, 90), "B": (1, 9, 24, 40, 131), "D": (3, 40, 200), "E": (1, 70, 259)}
+    ("D", "bfloat16"), ("E", "bfloat16"), ("E", "float32"), ("F", "bfloat16"), ("F", "float32")]
+TENSOR_CORE = {("D", "bfloat16"), ("E", "bfloat16"), ("F", "bfloat16")}
+LENGTHS = {"A": (5, 17, 33, 90), "B": (1, 9, 24, 40, 131), "D": (3, 40, 200), "E": (1, 70, 259), "F": (2, 149, 151, 420)}
 
 
 def check_kernels(calls, name, dtype, prompt: bool, decode: bool):

@@ -94,7 +94,28 @@ TINY_E = {
 }
 TINY_E_INIT = {"seed": 8, "std": 0.02, "norm_std": 0.02, "page_size": 16}
 
-ALL = {"A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT),
+# head_dim 128 with 4 query heads a KV head AND a window on the second and third layer (two cache
+# groups): the window's edge, and the pages it gives back, through the tensor-core attention kernels
+TINY_F = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 280,
+    "hidden_size": 512,
+    "intermediate_size": 272,
+    "num_hidden_layers": 3,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 1,
+    "max_position_embeddings": 1024,
+    "rope_theta": 500000.0,
+    "rms_norm_eps": 1e-5,
+    "attention_bias": True,
+    "tie_word_embeddings": False,
+    "use_sliding_window": True,
+    "sliding_window": 150,
+    "max_window_layers": 1,
+}
+TINY_F_INIT = {"seed": 9, "std": 0.02, "norm_std": 0.02, "page_size": 16}
+
+ALL = {"F": (TINY_F, TINY_F_INIT), "A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT),
        "E": (TINY_E, TINY_E_INIT)}
 
 
