@@ -23,3 +23,21 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords:
             item.add_marker(skip)
+
+
+@pytest.fixture(autouse=True)
+def no_index_check_failed(request):
+    """In the debug build (TORCHLET_B200_DEBUG=1) every GPU test also asserts that no kernel's index
+    check has fired: page ids, positions, slots and token ids stayed inside their ranges."""
+    yield
+    if "gpu" not in request.keywords:
+        return
+    from torchlet_b200.csrc.build import DEBUG_BUILD
+
+    if DEBUG_BUILD:
+        import torch
+
+        from torchlet_b200 import ops
+
+        torch.cuda.synchronize()
+        assert ops.debug_errors() == []

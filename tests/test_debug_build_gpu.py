@@ -2,7 +2,8 @@
 first bad index and SKIP the access, so nothing faults.  It stands in for a memory checker.  Run
 in child processes, because the build variant is chosen when the package is imported:
 
-* the engine's own parity tests of the two tiny configurations pass under it, with no check
+* the engine's own parity tests pass under it (the two tiny configurations, and the ones that
+  run the tensor-core kernels, a window among them; seeded random schedules), with no check
   failing (page ids, positions, slots and token ids stay inside their ranges);
 * a kernel handed a page id outside the pool, a position beyond its table, a token id outside
   the vocabulary or a slot outside the range reports it, skips the access, and the process goes on.
@@ -25,8 +26,10 @@ def _run(code_or_args, timeout=900):
 
 
 def test_parity_tests_pass_in_the_debug_build_and_no_check_fails():
+    # (tests/conftest.py asserts after every test of a debug build that no check has fired)
     proc = _run(["-m", "pytest", "-q", "-x", "-m", "gpu", "tests/test_replay_gpu.py", "tests/test_slot_records_gpu.py",
-                 "-k", "A-float32 or B-bfloat16 or B-float32", "-p", "no:cacheprovider"])
+                 "tests/test_random_schedules_gpu.py", "-k",
+                 "A-float32 or B-bfloat16 or B-float32 or D-bfloat16 or F-bfloat16 or E-bfloat16", "-p", "no:cacheprovider"])
     assert proc.returncode == 0, proc.stdout[-3000:] + proc.stderr[-2000:]
     assert "passed" in proc.stdout and "failed" not in proc.stdout
 
