@@ -115,7 +115,26 @@ TINY_F = {
 }
 TINY_F_INIT = {"seed": 9, "std": 0.02, "norm_std": 0.02, "page_size": 16}
 
-ALL = {"F": (TINY_F, TINY_F_INIT), "A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT),
+# long contexts: head_dim 128 given by its own key (hidden / heads would be 48), two query heads a KV
+# head, positions up to 8,192
+TINY_G = {
+    "architectures": ["Qwen2ForCausalLM"],
+    "vocab_size": 300,
+    "hidden_size": 192,
+    "head_dim": 128,
+    "intermediate_size": 256,
+    "num_hidden_layers": 2,
+    "num_attention_heads": 4,
+    "num_key_value_heads": 2,
+    "max_position_embeddings": 8192,
+    "rope_theta": 1000000.0,
+    "rms_norm_eps": 1e-6,
+    "attention_bias": True,
+    "tie_word_embeddings": False,
+}
+TINY_G_INIT = {"seed": 10, "std": 0.03, "norm_std": 0.02, "page_size": 16}
+
+ALL = {"G": (TINY_G, TINY_G_INIT), "F": (TINY_F, TINY_F_INIT), "A": (TINY_A, TINY_A_INIT), "B": (TINY_B, TINY_B_INIT), "C": (TINY_C, TINY_C_INIT), "D": (TINY_D, TINY_D_INIT),
        "E": (TINY_E, TINY_E_INIT)}
 
 
