@@ -26,8 +26,9 @@ CUTS = {"whole": [40], "last tokens one by one": [33] + [1] * 7, "portions": [5,
 def case():
     weights = tiny_configs.make_weights(CONFIG, seed=21, std=0.02, norm_std=0.02, dtype=torch.bfloat16)
     ids = tiny_configs.make_ids(CONFIG, LENGTH, seed=22)
-    plain = plain_model.forward_logits(CONFIG, {k: v.float() for k, v in weights.items()}, ids)
-    return weights, ids, plain
+    # in float64 (sums of 18,944 terms), so that the CPU's own float32 rounding is no part of the comparison
+    plain = plain_model.forward_logits(CONFIG, {k: v.float() for k, v in weights.items()}, ids, dtype=torch.float64)
+    return weights, ids, plain.float()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -81,6 +82,43 @@ def test_a_long_portion_in_bfloat16_against_the_32_bit_path(case):
         del runner, model
         torch.cuda.empty_cache()
     harness.assert_close(got["bfloat16"], got["float32"], "bfloat16", "704 tokens and 8 decoded")
+    from torchlet_b200 import ops
+
+    ops.raise_on_wait_errors()
+
+
+@pytest.mark.parametrize("batch", [8, 40])
+def test_requests_decoding_together_at_benchmark_layer_sizes(case, batch):
+    """``batch`` requests decode together for six steps, replayed from the captured step (the
+    16- and 64-token tiles of the weight-streaming products, their K splits and the fused
+    finishing kernels at the real widths, the decode attention of many requests at once):
+    bfloat16 against the engine's 32-bit path, every request's logits of every step."""
+    from torchlet_b200.config import EngineConfig, Qwen2Config
+    from torchlet_b200.engine import ModelRunner, StepEntry
+    from torchlet_b200.engine.loading import build_model
+
+    weights, _, _ = case
+    lengths = [3 + (7 * i) % 29 for i in range(batch)]
+    prompts = [tiny_configs.make_ids(CONFIG, n + 6, seed=300 + i) for i, n in enumerate(lengths)]
+    got = {}
+    for dtype in ("float32", "bfloat16"):
+        model = build_model(Qwen2Config.from_dict(CONFIG), weights, dtype)
+        runner = ModelRunner(model, EngineConfig(dtype=dtype, max_decode_slots=batch, kv_block_size=16, max_seq_len=64,
+                                                 max_num_batched_tokens=2048, cuda_graph=True))
+        for i in range(batch):
+            runner.admit(f"r{i}")
+        runner.step([StepEntry(f"r{i}", prompts[i][:lengths[i]], []) for i in range(batch)])
+        steps = []
+        for k in range(6):
+            steps.append(runner.step([StepEntry(f"r{i}", [prompts[i][lengths[i] + k]], [0]) for i in range(batch)]).cpu().clone())
+        assert runner.graph_steps == 6
+        got[dtype] = torch.cat(steps)
+        for i in range(batch):
+            runner.finish(f"r{i}")
+        runner.cache.check()
+        del runner, model
+        torch.cuda.empty_cache()
+    harness.assert_close(got["bfloat16"], got["float32"], "bfloat16", f"{batch} requests decoding together")
     from torchlet_b200 import ops
 
     ops.raise_on_wait_errors()
