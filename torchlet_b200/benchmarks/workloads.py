@@ -169,6 +169,23 @@ def _stress_requests(count: int, seed: int, vocab: int):
     return requests, arrivals
 
 
+def _warm_up(engine, slots: int, vocab: int) -> None:
+    """Untimed: as many short requests as there are slots, of different lengths, so that the decode
+    step is captured for every batch-size bucket from the full batch down to one request; the
+    counters start again afterwards."""
+    from ..engine.scheduler import Request, SchedulerStats
+    from ..sampling import SamplingParams
+
+    rng = random.Random(99)
+    engine.generate([Request([rng.randrange(vocab) for _ in range(8)],
+                             SamplingParams(max_new_tokens=3 + i % 24, ignore_eos=True)) for i in range(slots)])
+    engine.scheduler.stats = SchedulerStats()
+    engine.runner.graph_steps = 0
+    engine.steps_ahead = 0
+    for pool in engine.runner.cache.pools:
+        pool.peak_held = 0
+
+
 def _run_stress(engine, requests, arrivals) -> dict:
     """Runs the engine's loop while requests arrive at their times.  The unit of time is one
     scheduling decision of the loop; when nothing is left to do the next request arrives at once."""
@@ -206,6 +223,7 @@ def stress05b(layers: int = 24, count: int = 256, sample: int = 6, check_float32
         engine = Engine(model, EngineConfig(dtype=dtype, max_decode_slots=slots, kv_block_size=page, max_seq_len=context,
                                             max_num_blocks=num_blocks, max_num_batched_tokens=2048))
         requests, arrivals = _stress_requests(count, seed=5, vocab=cfg["vocab_size"])
+        _warm_up(engine, slots, cfg["vocab_size"])
         run = _run_stress(engine, requests, arrivals)
         stats = engine.scheduler.stats
         engine.runner.cache.check()
