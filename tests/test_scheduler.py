@@ -111,8 +111,9 @@ def test_more_requests_than_slots_wait_in_order():
 
 def test_pages_run_out_latest_is_preempted_and_recomputed():
     # 6 usable pages of 4 tokens; two requests of 9 prompt tokens (3 pages each) then decode
+    # (admitted on the pages of their prompts alone: the admission rule below would make b wait)
     runner = FakeRunner(num_pages=7, page=4, slots=4)
-    sched = Scheduler(runner, 64, 256)
+    sched = Scheduler(runner, 64, 256, admission_headroom=None)
     a, b = req(9, new=8), req(9, new=8)
     sched.add_request(a); sched.add_request(b)
     plans = drive(sched, runner)
@@ -123,6 +124,29 @@ def test_pages_run_out_latest_is_preempted_and_recomputed():
     # outputs do not depend on preemption: token = 1000 + position
     assert a.output_tokens == [1009 + i for i in range(8)] and b.output_tokens == a.output_tokens
     assert runner.cache.pools[0].num_free == 6 and sched.stats.preemptions >= 1
+
+
+def test_admission_leaves_the_running_requests_room_to_grow():
+    """The same two requests under the admission rule (pages for all of a request's tokens and
+    one page of headroom for every running request): b waits until a has finished, nobody is
+    preempted, the outputs are the same.  With room enough both run together from the start."""
+    runner = FakeRunner(num_pages=7, page=4, slots=4)
+    sched = Scheduler(runner, 64, 256)  # admission_headroom=1
+    a, b = req(9, new=8), req(9, new=8)
+    sched.add_request(a); sched.add_request(b)
+    plans = drive(sched, runner)
+    assert not any(p.preempted for p in plans) and sched.stats.preemptions == 0
+    assert all(len(p.portions) == 1 for p in plans), "b ran beside a although the pool had no room for both to grow"
+    assert a.output_tokens == [1009 + i for i in range(8)] and b.output_tokens == a.output_tokens
+    assert runner.cache.pools[0].num_free == 6
+    roomy = FakeRunner(num_pages=12, page=4, slots=4)  # 11 usable pages: 3 + 3 and headroom
+    sched = Scheduler(roomy, 64, 256)
+    a, b = req(9, new=8), req(9, new=8)
+    sched.add_request(a); sched.add_request(b)
+    first = sched.schedule()
+    assert [p.request for p in first.portions] == [a, b]
+    with pytest.raises(ValueError):
+        Scheduler(roomy, 64, 256, admission_headroom=-1)
 
 
 def test_request_too_large_for_the_pool_fails_alone():

@@ -24,6 +24,9 @@ class EngineConfig:
     max_seq_len: Optional[int] = None  # None: max_position_embeddings
     max_num_batched_tokens: int = 2048  # token budget of one step
     cuda_graph: bool = True  # capture decode-only steps
+    # a waiting request is admitted beside running ones only if the pools have pages for all its tokens
+    # and this many for every running request to grow into (None: on the pages of its first portion)
+    admission_headroom: Optional[int] = 1
     device: str = "cuda:0"
 
     def __post_init__(self) -> None:

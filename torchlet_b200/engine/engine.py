@@ -33,7 +33,8 @@ class Engine:
         of the loop's own decisions pass a stand-in and no model)."""
         self.config = config or EngineConfig()
         self.runner = runner if runner is not None else ModelRunner(model, self.config)
-        self.scheduler = Scheduler(self.runner, self.config.max_num_batched_tokens, self.config.max_seq_len)
+        self.scheduler = Scheduler(self.runner, self.config.max_num_batched_tokens, self.config.max_seq_len,
+                                   self.config.admission_headroom)
         self.steps_ahead = 0  # decode steps launched before the tokens of the step before were read
         # the loop as an asyncio task: requests handed in and not yet seen by the loop, who waits for which
         self._task = None

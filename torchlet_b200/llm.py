@@ -42,7 +42,7 @@ class LLM:
     def __init__(self, model_dir: Union[str, Path], max_decode_slots: int = 4, kv_block_size: int = 16,
                  max_num_blocks: Optional[int] = None, dtype: str = "bfloat16",
                  max_seq_len: Optional[int] = None, max_num_batched_tokens: int = 2048,
-                 cuda_graph: bool = True, device: str = "cuda:0"):
+                 cuda_graph: bool = True, device: str = "cuda:0", admission_headroom: Optional[int] = 1):
         import torch
 
         if not torch.cuda.is_available():
@@ -57,7 +57,8 @@ class LLM:
         self.engine_config = EngineConfig(
             dtype=dtype, max_decode_slots=max_decode_slots, kv_block_size=kv_block_size,
             max_num_blocks=max_num_blocks, max_seq_len=max_seq_len,
-            max_num_batched_tokens=max_num_batched_tokens, cuda_graph=cuda_graph, device=device)
+            max_num_batched_tokens=max_num_batched_tokens, cuda_graph=cuda_graph, device=device,
+            admission_headroom=admission_headroom)
         self.model = load_model(self.model_dir, self.engine_config.dtype, device)
         self.config = self.model.config
         self.tokenizer = _load_tokenizer(self.model_dir)
