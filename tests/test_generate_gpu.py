@@ -105,6 +105,63 @@ def test_coroutines_that_arrive_one_after_the_other(tmp_path):
     assert llm.engine.runner.cache.live_requests() == [] and llm.engine._task is None
 
 
+def _write_tokenizer(folder, vocab_size):
+    """A word-level tokenizer with the special tokens and a chat template of the kind the
+    reference's model has, written locally (tokenizer.json + tokenizer_config.json)."""
+    import json
+
+    from tokenizers import Tokenizer, models, pre_tokenizers
+
+    words = ["<unk>", "<|im_start|>", "<|im_end|>", "user", "assistant", "hello", "world", "what", "is", "the",
+             "nearest", "star"]
+    words += [f"w{i}" for i in range(vocab_size - len(words))]
+    tokenizer = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tokenizer.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    tokenizer.save(str(folder / "tokenizer.json"))
+    template = ("{% for m in messages %}<|im_start|> {{ m['role'] }} {{ m['content'] }} <|im_end|> {% endfor %}"
+                "{% if add_generation_prompt %}<|im_start|> assistant {% endif %}")
+    (folder / "tokenizer_config.json").write_text(json.dumps({
+        "tokenizer_class": "PreTrainedTokenizerFast", "eos_token": "<|im_end|>", "unk_token": "<unk>",
+        "chat_template": template}))
+    return words
+
+
+def test_text_prompts_through_the_tokenizer(tmp_path):
+    """Text in, text out, as the reference's entry point (v10_triton_paged_gqa/llm.py:84-110): the
+    folder's tokenizer, its chat template around a single user turn, the stop ids from the
+    tokenizer (eos and <|im_end|>), the output decoded without special tokens; equal to the same
+    ids given as ids, also from a coroutine."""
+    import asyncio
+
+    from torchlet_b200 import LLM
+
+    folder = model_dir(tmp_path, "A")
+    words = _write_tokenizer(folder, tiny_configs.ALL["A"][0]["vocab_size"])
+    llm = LLM(folder, max_decode_slots=4, kv_block_size=16, dtype="float32", max_seq_len=128)
+    assert llm.tokenizer is not None and llm.stop_ids == {2}
+    prompts = ["hello world", "what is the nearest star"]
+    ids = llm._encode(prompts)
+    assert ids[0] == [1, 3, 5, 6, 2, 1, 4] and ids[1][:3] == [1, 3, 7] and ids[1][-2:] == [1, 4]
+    texts = llm.generate(prompts, max_new_tokens=12)
+    tokens = llm.generate(ids, max_new_tokens=12)  # the same ids as ids: the tokenizer's stop ids apply as well
+    assert all(isinstance(t, str) for t in texts) and len(texts) == 2
+    for text, produced in zip(texts, tokens):
+        assert 2 not in produced and len(produced) <= 12  # a stop token ends the request and is not emitted
+        assert text == " ".join(words[t] for t in produced if t > 2)
+    assert asyncio.run(_one_coroutine(llm, prompts)) == texts
+    cfg, w = harness.weights_for("A")
+    plain = plain_model.greedy_generate(cfg, w, ids[0], 12)
+    cut = plain.index(2) if 2 in plain else len(plain)
+    assert tokens[0] == plain[:cut]
+
+
+async def _one_coroutine(llm, prompts):
+    try:
+        return await llm.agenerate(prompts, max_new_tokens=12)
+    finally:
+        await llm.shutdown()
+
+
 def test_sampling_does_not_depend_on_the_batch(tmp_path):
     from torchlet_b200 import LLM, SamplingParams
 
