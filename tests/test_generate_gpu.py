@@ -276,6 +276,37 @@ def test_command_line(tmp_path):
     assert eval(lines[0]) == plain_model.greedy_generate(cfg, w, [1, 2, 3], 5)
 
 
+def test_command_line_writes_random_weights_and_serves_three_arrivals(tmp_path):
+    """``--random-weights SEED`` writes model.safetensors into a folder that holds only a config.json
+    (and here a tokenizer); without prompts the command line does what the reference's does
+    (v10_triton_paged_gqa/llm.py:113-140): its three prompts as three coroutines a tenth of a
+    second apart, one engine loop, three printed batches."""
+    import json
+    import subprocess
+    import sys
+
+    folder = tmp_path / "fresh"
+    folder.mkdir()
+    (folder / "config.json").write_text(json.dumps(tiny_configs.ALL["A"][0]))
+    _write_tokenizer(folder, tiny_configs.ALL["A"][0]["vocab_size"])
+    root = str(harness.tiny_configs.__file__).rsplit("/tests", 1)[0]
+    cmd = [sys.executable, "-m", "torchlet_b200.llm", "--model", str(folder), "--random-weights", "11", "--max-new-tokens",
+           "6", "--ignore-eos", "--max-seq-len", "128"]
+    out = subprocess.run(cmd, capture_output=True, text=True, cwd=root)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert (folder / "model.safetensors").is_file()
+    lines = out.stdout.splitlines()
+    assert [line for line in lines if line.startswith("batch ")] == ["batch 1:", "batch 2:", "batch 3:"]
+    batches = [eval(line) for line in lines if line.startswith("[")]
+    assert len(batches) == 3 and all(len(b) == 1 and isinstance(b[0], str) and len(b[0].split()) <= 6 for b in batches)
+    # the same folder again, now with its weights: ids in, ids out
+    again = subprocess.run([sys.executable, "-m", "torchlet_b200.llm", "--model", str(folder), "--prompt-ids", "5,6,7",
+                            "--max-new-tokens", "4", "--ignore-eos", "--max-seq-len", "128"], capture_output=True,
+                           text=True, cwd=root)
+    assert again.returncode == 0, again.stderr[-2000:]
+    assert len(eval([line for line in again.stdout.splitlines() if line.startswith("[")][0])) == 4
+
+
 def test_a_pool_larger_than_the_memory_is_refused_in_words(tmp_path):
     from torchlet_b200 import LLM
     from torchlet_b200.cache.manager import CacheError
