@@ -307,6 +307,30 @@ def test_command_line_writes_random_weights_and_serves_three_arrivals(tmp_path):
     assert len(eval([line for line in again.stdout.splitlines() if line.startswith("[")][0])) == 4
 
 
+def test_entry_point_edges(tmp_path):
+    """No inputs, no new tokens, text without a tokenizer, a request longer than the engine takes,
+    per-request sampling options, and ``LLM.from_model`` around a model that is already loaded."""
+    import asyncio
+
+    from torchlet_b200 import LLM, SamplingParams
+
+    folder = model_dir(tmp_path, "A")
+    llm = LLM(folder, max_decode_slots=2, kv_block_size=16, dtype="float32", max_seq_len=64)
+    assert llm.tokenizer is None and llm.generate([]) == [] and asyncio.run(llm.agenerate([])) == []
+    assert llm.generate([[1, 2, 3]], max_new_tokens=0) == [[]]
+    with pytest.raises(ValueError, match="tokenizer"):
+        llm.generate(["hello"])
+    with pytest.raises(ValueError, match="max_seq_len"):
+        llm.generate([[1] * 60], max_new_tokens=10)
+    assert llm.engine.runner.cache.live_requests() == [] and not llm.engine.scheduler.has_work()
+    params = [SamplingParams(max_new_tokens=3), SamplingParams(max_new_tokens=7, temperature=0.5, seed=3)]
+    outs = llm.generate([[5, 6], [7, 8, 9]], sampling_params=params)
+    assert [len(o) for o in outs] == [3, 7]
+    wrapped = LLM.from_model(llm.model, max_decode_slots=2, kv_block_size=16, max_seq_len=64)
+    assert wrapped.engine_config.dtype == "float32" and wrapped.tokenizer is None
+    assert wrapped.generate([[5, 6], [7, 8, 9]], sampling_params=params) == outs
+
+
 def test_a_pool_larger_than_the_memory_is_refused_in_words(tmp_path):
     from torchlet_b200 import LLM
     from torchlet_b200.cache.manager import CacheError
