@@ -39,6 +39,11 @@ def test_unknown_architecture_lists_known():
     ({"hidden_act": "gelu"}, "hidden_act"),
     ({"use_sliding_window": True}, "sliding_window"),
     ({"vocab_size": 0}, "positive"),
+    ({"hidden_size": 60, "num_attention_heads": 4}, "even"),  # head_dim 15
+    ({"rms_norm_eps": 0.0}, "rms_norm_eps"),
+    ({"rope_theta": -1.0}, "rope_theta"),
+    ({"use_sliding_window": True, "sliding_window": 8, "max_window_layers": 5}, "max_window_layers"),
+    ({"rope_parameters": {"rope_theta": 1e4, "rope_type": "yarn"}}, "rope_type"),
 ])
 def test_bad_configs_are_refused(patch, message):
     with pytest.raises(ValueError, match=message):
@@ -125,3 +130,29 @@ def test_tensor_names_come_from_the_layer_description():
         LayeredModel(broken)
     with pytest.raises(KeyError, match="mixer_norm"):
         renamed[0].norm("mixer_norm")
+
+
+def test_other_spellings_of_config_keys():
+    """``dtype`` beside ``torch_dtype``, a list of eos ids, a window without ``max_window_layers``."""
+    cfg = Qwen2Config.from_dict(dict(tiny_configs.TINY_A, dtype="bfloat16", eos_token_id=[7, 9]))
+    assert cfg.torch_dtype == "bfloat16" and cfg.eos_token_id == 7
+    cfg = Qwen2Config.from_dict(dict(tiny_configs.TINY_A, use_sliding_window=True, sliding_window=8))
+    assert [layer.mixer.params["window"] for layer in cfg.model_spec().layers] == [8, 8]
+
+
+def test_a_model_description_that_cannot_run_is_refused():
+    import dataclasses
+
+    from torchlet_b200.config import ScheduleEntry
+
+    spec = Qwen2Config.from_dict(tiny_configs.TINY_A).model_spec()
+    spec.validate()
+    for change, message in [
+        ({"layers": ()}, "at least one layer"),
+        ({"schedule": ()}, "schedule is empty"),
+        ({"schedule": (ScheduleEntry(0, None), ScheduleEntry(2, None))}, "names layer 2"),
+        ({"schedule": (ScheduleEntry(0, 0), ScheduleEntry(1, None))}, "earlier entry"),
+        ({"schedule": (ScheduleEntry(0, None), ScheduleEntry(1, 0), ScheduleEntry(0, 1))}, "owns no cache"),
+    ]:
+        with pytest.raises(ValueError, match=message):
+            dataclasses.replace(spec, **change).validate()

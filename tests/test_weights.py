@@ -38,6 +38,18 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes():
         assert piece in text
 
 
+def test_a_tensor_of_a_type_the_engine_does_not_hold_is_named():
+    cfg, init = tiny_configs.ALL["A"]
+    weights = tiny_configs.make_weights(cfg, **init)
+    name, other = "model.layers.0.mlp.down_proj.weight", "model.layers.1.mlp.down_proj.weight"
+    weights[name] = weights[name].to(torch.float8_e4m3fn)  # quantized weights are not taken
+    weights[other] = weights[other].to(torch.complex64)
+    with pytest.raises(WeightsError) as info:
+        check_and_normalise(weights, _expected(cfg))
+    assert sorted(info.value.wrong_dtype) == sorted([(name, torch.float8_e4m3fn), (other, torch.complex64)])
+    assert "unsupported dtype" in str(info.value)
+
+
 def test_tied_head_may_be_absent_and_dtypes_are_kept():
     cfg, init = tiny_configs.ALL["A"]
     weights = tiny_configs.make_weights(cfg, dtype=torch.bfloat16, **init)

@@ -142,7 +142,7 @@ def check_and_normalise(tensors, expected: list):
             wrong_shape.append((name, shape, spec.shape))
             continue
         is_float = isinstance(dtype, torch.dtype) and dtype.is_floating_point
-        if not isinstance(dtype, torch.dtype) or (is_float and dtype not in floats):
+        if not isinstance(dtype, torch.dtype) or dtype.is_complex or (is_float and dtype not in floats):
             wrong_dtype.append((name, dtype))
             continue
         if not lazy:
