@@ -187,3 +187,47 @@ def test_a_model_without_paged_history_needs_no_pages():
     manager.reset()
     manager.check()
     assert manager.num_free_slots == 2
+
+
+def test_check_finds_what_it_is_there_to_find():
+    """``check()`` is what the other tests lean on: every kind of damage, done to the bookkeeping by
+    hand, makes it raise and name the damage."""
+    def fresh():
+        m = CacheManager([GroupSpec(1, 8, None, (0,), 9)], 4, 3, 64)
+        m.admit("a"); m.admit("b")
+        assert m.extend("a", 9) and m.extend("b", 5)
+        m.check()
+        return m
+
+    m = fresh()
+    m._requests["b"].tables[0][0] = m._requests["a"].tables[0][0]
+    with pytest.raises(CacheError, match="held twice|differs"):
+        m.check()
+    m = fresh()
+    m.pools[0]._free.append(m.pools[0]._free[0])
+    with pytest.raises(CacheError, match="free twice"):
+        m.check()
+    m = fresh()
+    m.pools[0]._free.append(m._requests["a"].tables[0][1])
+    with pytest.raises(CacheError, match="both free and held"):
+        m.check()
+    m = fresh()
+    m.pools[0]._free.pop()
+    with pytest.raises(CacheError, match="pages lost"):
+        m.check()
+    m = fresh()
+    m.pools[0]._free[0] = 0
+    with pytest.raises(CacheError, match="page 0|lost|twice"):
+        m.check()
+    m = fresh()
+    m.table_arrays[0][m.slot_of("a"), 1] = 7 if m._requests["a"].tables[0][1] != 7 else 6
+    with pytest.raises(CacheError, match="table array differs"):
+        m.check()
+    m = fresh()
+    m._requests["b"].slot = m._requests["a"].slot
+    with pytest.raises(CacheError, match="slot|differs"):
+        m.check()
+    m = fresh()
+    m._free_slots.pop()
+    with pytest.raises(CacheError, match="slot is lost"):
+        m.check()
