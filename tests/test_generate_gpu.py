@@ -162,6 +162,39 @@ async def _one_coroutine(llm, prompts):
         await llm.shutdown()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_shutdown_while_requests_decode(tmp_path, dtype):
+    """``shutdown`` in the middle of decoding, a step launched ahead still in flight: the waiting
+    coroutine gets ``CancelledError``, every page and slot is back, and the same engine then
+    generates what a fresh one generates."""
+    import asyncio
+
+    from torchlet_b200 import LLM
+
+    folder = model_dir(tmp_path, "B")
+    prompts = prompts_for("B")
+    llm = LLM(folder, max_decode_slots=4, kv_block_size=8, dtype=dtype, max_seq_len=512)
+    fresh = llm.generate(prompts, max_new_tokens=10)
+
+    async def main():
+        task = asyncio.create_task(llm.agenerate(prompts, max_new_tokens=400, sampling_params=None))
+        while llm.engine.scheduler.stats.decode_tokens < 40:  # well into decoding, far from done
+            await asyncio.sleep(0)
+        assert llm.engine.steps_ahead > 0 and not task.done()
+        await llm.shutdown()
+        with pytest.raises(asyncio.CancelledError):
+            await task
+
+    before = llm.engine.scheduler.stats.decode_tokens
+    asyncio.run(main())
+    assert 40 <= llm.engine.scheduler.stats.decode_tokens - before + 40 < 4 * 400
+    torch.cuda.synchronize()
+    llm.engine.runner.cache.check()
+    assert llm.engine.runner.cache.live_requests() == [] and not llm.engine.scheduler.has_work()
+    assert llm.engine.runner.cache.num_free_slots == 4
+    assert llm.generate(prompts, max_new_tokens=10) == fresh
+
+
 def test_sampling_does_not_depend_on_the_batch(tmp_path):
     from torchlet_b200 import LLM, SamplingParams
 
