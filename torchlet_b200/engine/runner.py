@@ -246,6 +246,17 @@ class ModelRunner:
         entries = [e for e in entries if len(e.tokens) > 0]
         if not entries:
             return StepResult(None, None)
+        try:
+            return self._run(entries, feed_previous)
+        except BaseException:
+            # a step that broke in the middle leaves nothing for the next one: no unfinished sum
+            # waiting for a later kernel, no trust in the device's slot records
+            ops.workspace_holder = None
+            self._synced.clear()
+            self._last_graph_ids = None
+            raise
+
+    def _run(self, entries, feed_previous: bool) -> StepResult:
         if feed_previous:
             if not self.can_feed_previous(entries):
                 raise ValueError("feed_previous needs the previous step's requests, in its order, as a graph decode step")
