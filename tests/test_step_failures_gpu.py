@@ -72,3 +72,23 @@ def test_a_step_that_breaks_in_the_middle_leaves_nothing_behind(name, dtype, op,
     again = engine.generate(_requests(name, 900))
     assert [list(r.output_tokens) for r in again] == want
     engine.runner.cache.check()
+
+
+def test_a_wait_that_gave_up_inside_a_kernel_fails_the_step_not_the_engine():
+    """A bounded wait that runs out leaves a code on the device (here left by the self-test kernel,
+    whose wait nothing ends: no fault, no hang).  The engine reads the codes before it hands a
+    finished request back, fails what is live instead of returning tokens of a kernel that gave
+    up, and serves the next requests as if nothing had been."""
+    from torchlet_b200 import ops
+    from torchlet_b200.engine.scheduler import RequestState
+
+    want = [list(r.output_tokens) for r in _engine("E", "bfloat16", True).generate(_requests("E", 900))]
+    engine = _engine("E", "bfloat16", True)
+    ops.wait_selftest(77)
+    doomed = _requests("E", 400)
+    with pytest.raises(ops.KernelError, match="77"):
+        engine.generate(doomed)
+    assert all(r.state is RequestState.FINISHED for r in doomed) and all(r.error is not None for r in doomed)
+    engine.runner.cache.check()
+    assert engine.runner.cache.live_requests() == []
+    assert [list(r.output_tokens) for r in engine.generate(_requests("E", 900))] == want

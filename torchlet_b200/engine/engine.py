@@ -78,12 +78,24 @@ class Engine:
                 sampled = result.tokens.tolist() if result.tokens is not None else []
                 done += scheduler.update(plan, sampled)
                 if done:  # nothing is handed back before the kernels' own error words have been read
-                    ops.raise_on_wait_errors()
+                    self._check_kernels(done)
         except Exception as exc:
             self._fail_everything(exc)
             raise
         scheduler.drain_finished()
         return done
+
+    @staticmethod
+    def _check_kernels(done: list) -> None:
+        """Raises if a kernel has given up a bounded wait since the last check; the requests that
+        have just finished did so on tokens of such a step and end with that error as well."""
+        try:
+            ops.raise_on_wait_errors()
+        except Exception as exc:
+            for request in done:
+                if request.error is None:
+                    request.error = exc
+            raise
 
     def _fail_everything(self, exc: Exception) -> list:
         """A failed step fails every live request (the reference: engine.py:215-217)."""
@@ -192,7 +204,7 @@ class Engine:
                     values = [v for _, v in live]
                 done = scheduler.update(plan, values)
                 if done:
-                    ops.raise_on_wait_errors()  # nothing is handed back before the kernels' error words are read
+                    self._check_kernels(done)  # nothing is handed back before the kernels' error words are read
                     ended += done
                 scheduler.drain_finished()
                 yield ended
