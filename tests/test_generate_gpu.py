@@ -356,6 +356,13 @@ def test_entry_point_edges(tmp_path):
     with pytest.raises(ValueError, match="max_seq_len"):
         llm.generate([[1] * 60], max_new_tokens=10)
     assert llm.engine.runner.cache.live_requests() == [] and not llm.engine.scheduler.has_work()
+    # a prompt that fills the engine's length to the last position still gets its one token (which needs no
+    # cache position of its own), and equals the plain implementation's
+    cfg, w = harness.weights_for("A")
+    full = tiny_configs.make_ids(cfg, 64, seed=77)
+    assert llm.generate([full], max_new_tokens=1) == [plain_model.greedy_generate(cfg, w, full, 1)]
+    with pytest.raises(ValueError, match="max_seq_len"):
+        llm.generate([full], max_new_tokens=2)
     params = [SamplingParams(max_new_tokens=3), SamplingParams(max_new_tokens=7, temperature=0.5, seed=3)]
     outs = llm.generate([[5, 6], [7, 8, 9]], sampling_params=params)
     assert [len(o) for o in outs] == [3, 7]
