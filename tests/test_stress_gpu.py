@@ -20,28 +20,32 @@ CONFIG = {
 }
 
 
-def build(dtype, **engine):
+# the same with a window of 48 tokens on the second layer: two cache groups, pages given back while a request runs
+WINDOWED = dict(CONFIG, use_sliding_window=True, sliding_window=48, max_window_layers=1)
+
+
+def build(dtype, config=CONFIG, **engine):
     from torchlet_b200.config import EngineConfig, Qwen2Config
     from torchlet_b200.engine.engine import Engine
     from torchlet_b200.engine.loading import build_model
 
-    weights = tiny_configs.make_weights(CONFIG, seed=5, std=0.02, norm_std=0.01, dtype=torch.bfloat16)
-    model = build_model(Qwen2Config.from_dict(CONFIG), weights, dtype)
+    weights = tiny_configs.make_weights(config, seed=5, std=0.02, norm_std=0.01, dtype=torch.bfloat16)
+    model = build_model(Qwen2Config.from_dict(config), weights, dtype)
     return Engine(model, EngineConfig(dtype=dtype, max_seq_len=256, **engine))
 
 
-def check_against_plain(requests, dtype):
+def check_against_plain(requests, dtype, config=CONFIG):
     """Every produced token against the plain implementation, given the tokens before it: the
     greedy ones must be the plain argmax (within rounding of it in bfloat16), the sampled ones
     the argmax of the plain scores with the request's own noise."""
     import plain_model
 
-    weights = {k: v.float() for k, v in tiny_configs.make_weights(CONFIG, seed=5, std=0.02, norm_std=0.01,
+    weights = {k: v.float() for k, v in tiny_configs.make_weights(config, seed=5, std=0.02, norm_std=0.01,
                                                                    dtype=torch.bfloat16).items()}
     slack = 0.0 if dtype == "float32" else 2.5e-2
     for request in requests:
         ids = request.prompt_tokens + request.output_tokens
-        logits = plain_model.forward_logits(CONFIG, weights, ids)
+        logits = plain_model.forward_logits(config, weights, ids)
         first = len(request.prompt_tokens) - 1
         temperature = request.params.temperature
         for k, token in enumerate(request.output_tokens):
@@ -156,3 +160,32 @@ def test_run_with_a_tight_pool_and_stop_tokens(dtype, headroom):
             while alone.scheduler.has_work():
                 alone.step()
             assert fresh.output_tokens == request.output_tokens, f"request {request.request_id} depends on its batch"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_windowed_layer_under_load(dtype):
+    """The loop one step ahead, the captured decode step, a tight pool with preemptions and stop
+    tokens, now with a window on one of the two layers: its group gives pages back while requests
+    decode, the device's block tables keep the passed entries, and every produced token is still
+    the plain implementation's."""
+    from torchlet_b200.engine.scheduler import Request
+    from torchlet_b200.sampling import SamplingParams
+
+    count = 24
+    r = random.Random(21)
+    stops = tuple(r.sample(range(WINDOWED["vocab_size"]), 40))
+    requests = [Request([r.randrange(WINDOWED["vocab_size"]) for _ in range(r.randint(4, 150))],
+                        SamplingParams(max_new_tokens=r.randint(20, 90), temperature=r.choice([0.0, 0.8]), seed=700 + i,
+                                       stop_token_ids=stops)) for i in range(count)]
+    engine = build(dtype, WINDOWED, max_decode_slots=6, kv_block_size=16, max_num_blocks=36, max_num_batched_tokens=128,
+                   admission_headroom=None)
+    engine.generate(requests)
+    cache = engine.runner.cache
+    cache.check()
+    stats = engine.scheduler.stats
+    assert len(cache.groups) == 2 and {g.window for g in cache.groups} == {None, 48}
+    assert stats.finished == count and stats.failed == 0 and stats.preemptions > 0 and engine.steps_ahead > 0
+    assert engine.runner.graph_steps > 0 and cache.live_requests() == []
+    assert all(pool.num_free == pool.num_pages - 1 for pool in cache.pools)
+    assert max(len(q.prompt_tokens) + len(q.output_tokens) for q in requests) > 48 + 64, "nobody ran far past the window"
+    check_against_plain(requests, dtype, WINDOWED)
