@@ -231,6 +231,22 @@ def test_schedule_runs_a_layer_twice_and_shares_a_cache(dtype):
     assert len(runner.storage.pages[0]) == 3  # three executions own cache layers, one reads another's
 
 
+@pytest.mark.parametrize("graph", [False, True])
+def test_schedule_with_a_shared_cache_on_the_tensor_core_kernels(graph):
+    """The same schedule at tiny E's sizes in bfloat16: the execution that reads another one's cache
+    rotates its q but writes no keys or values (the fused finishing kernel's store is off), in
+    eager steps and in steps replayed from the captured decode step."""
+    schedule = ((0, None), (1, None), (0, None), (1, 1))
+    runner = make_runner("E", "bfloat16", schedule=schedule, cuda_graph=graph)
+    ids, want = plain_logits("E", 150, 13, schedule=schedule)
+    with harness.KernelCalls() as calls:
+        got = replay(runner, "s", ids, [70, 2, 45, 1] + [1] * 32)
+    assert_close(got, want, "bfloat16", "schedule with repeats, tensor-core kernels")
+    assert calls.counts["attention_generic"] == 0 and calls.counts["finish_qkv_rope"] > 0
+    assert (runner.graph_steps > 0) == graph
+    assert len(runner.storage.pages[0]) == 3
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_head_dim_128_through_the_tensor_core_attention(dtype):
     """Tiny D (head_dim 128, 3 heads a KV head): in bfloat16 prompt portions run on the
