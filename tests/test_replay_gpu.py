@@ -231,6 +231,21 @@ def test_schedule_runs_a_layer_twice_and_shares_a_cache(dtype):
     assert len(runner.storage.pages[0]) == 3  # three executions own cache layers, one reads another's
 
 
+@pytest.mark.parametrize("page", [8, 32, 64, 128])
+@pytest.mark.parametrize("name", ["D", "F"])
+def test_other_page_sizes_on_the_tensor_core_kernels(name, page):
+    """Pages of 8 to 128 tokens (what the TMA page boxes of both attention kernels take), with and
+    without a window: whole, a decode tail replayed from the captured step, and changing portions."""
+    length = LENGTHS[name][-1]
+    runner = make_runner(name, "bfloat16", num_pages=max(16, 3 * -(-length // page)), page_size=page, cuda_graph=True)
+    ids, want = plain_logits(name, length, 7)
+    with harness.KernelCalls() as calls:
+        for cuts in ([length], [length - 32] + [1] * 32, changing_cuts(length, seed=page)):
+            assert_close(replay(runner, "r", ids, cuts), want, "bfloat16", f"{name}, pages of {page}, {len(cuts)} portions")
+    assert calls.counts["attention_generic"] == 0 and calls.counts["attention_tc"] > 0 and calls.decode_splits
+    assert runner.graph_steps > 0
+
+
 @pytest.mark.parametrize("graph", [False, True])
 def test_schedule_with_a_shared_cache_on_the_tensor_core_kernels(graph):
     """The same schedule at tiny E's sizes in bfloat16: the execution that reads another one's cache
