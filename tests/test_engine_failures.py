@@ -106,6 +106,34 @@ def test_a_failed_step_fails_every_request_and_the_engine_serves_again(loop, fai
     runner.cache.check()
 
 
+@pytest.mark.parametrize("loop", ["run", "step"])
+def test_an_interrupt_from_the_keyboard_leaves_nothing_half_run(loop):
+    class Interrupted(FailingRunner):
+        def run(self, entries, feed_previous=False):
+            if self.steps_run == 3:
+                self.steps_run += 1
+                raise KeyboardInterrupt
+            return super().run(entries, feed_previous)
+
+    runner = Interrupted()
+    engine = _engine(runner)
+    requests = _requests()
+    engine.add_requests(requests)
+    with pytest.raises(KeyboardInterrupt):
+        if loop == "run":
+            engine.run()
+        else:
+            while engine.scheduler.has_work():
+                engine.step()
+    assert all(r.state is RequestState.FINISHED for r in requests) and not engine.scheduler.has_work()
+    assert any(isinstance(r.error, KeyboardInterrupt) for r in requests)
+    runner.cache.check()
+    assert runner.cache.live_requests() == [] and runner.cache.num_free_slots == 3
+    fresh = Request(list(range(11)), SamplingParams(max_new_tokens=4))
+    engine.generate([fresh])
+    assert fresh.error is None and fresh.output_tokens == [1011, 1012, 1013, 1014]
+
+
 def test_without_a_failure_both_loops_agree():
     outputs = []
     for loop in ("run", "step"):

@@ -79,7 +79,7 @@ class Engine:
                 done += scheduler.update(plan, sampled)
                 if done:  # nothing is handed back before the kernels' own error words have been read
                     self._check_kernels(done)
-        except Exception as exc:
+        except BaseException as exc:  # also an interrupt from the keyboard: nothing stays half-run
             self._fail_everything(exc)
             raise
         scheduler.drain_finished()
@@ -208,7 +208,9 @@ class Engine:
                     ended += done
                 scheduler.drain_finished()
                 yield ended
-        except Exception as exc:  # a failed step fails every live request
+        except GeneratorExit:  # the driver stops the loop between two iterations (shutdown): its business
+            raise
+        except BaseException as exc:  # a failed step (or an interrupt from the keyboard) fails every live request
             self._fail_everything(exc)
             raise
 
