@@ -156,3 +156,22 @@ def test_a_model_description_that_cannot_run_is_refused():
     ]:
         with pytest.raises(ValueError, match=message):
             dataclasses.replace(spec, **change).validate()
+
+
+def test_a_config_json_with_every_key_a_published_folder_carries():
+    """The keys of a Qwen2.5 folder's config.json beyond the ones the reference reads
+    (v10_triton_paged_gqa/model/qwen2_5.py:25-36): the window keys with the window switched off,
+    token ids, a null rope_scaling, bookkeeping keys of the library that wrote the file.  They are
+    accepted, the window stays off, and nothing of them changes a size."""
+    raw = {"architectures": ["Qwen2ForCausalLM"], "attention_dropout": 0.0, "bos_token_id": 151643, "eos_token_id": 151645,
+           "hidden_act": "silu", "hidden_size": 896, "initializer_range": 0.02, "intermediate_size": 4864,
+           "max_position_embeddings": 32768, "max_window_layers": 21, "model_type": "qwen2", "num_attention_heads": 14,
+           "num_hidden_layers": 24, "num_key_value_heads": 2, "rms_norm_eps": 1e-06, "rope_theta": 1000000.0,
+           "sliding_window": 32768, "tie_word_embeddings": True, "torch_dtype": "bfloat16", "transformers_version": "4.43.1",
+           "use_cache": True, "use_sliding_window": False, "vocab_size": 151936, "rope_scaling": None}
+    cfg = config_from_dict(raw)
+    spec = cfg.model_spec()
+    assert isinstance(cfg, Qwen2Config) and cfg.head_dim == 64 and cfg.eos_token_id == 151645
+    assert len(spec.layers) == 24 and all(layer.mixer.params["window"] is None for layer in spec.layers)
+    assert spec.tie_word_embeddings and spec.vocab_size == 151936
+    assert Qwen2Config.from_dict(cfg.to_dict()).to_dict() == cfg.to_dict()
