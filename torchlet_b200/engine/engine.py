@@ -145,7 +145,9 @@ class Engine:
         ``poll``: a callable asked before every scheduling decision for the requests that have
         arrived since the last call (a list, possibly empty), as the reference's loop drains its
         queue every iteration (v10_triton_paged_gqa/scheduler.py:122-128); it returns None once
-        no more will come.  With it the loop serves requests that arrive while others run."""
+        no more will come.  With it the loop serves requests that arrive while others run.  While
+        nothing is running ``poll`` is asked again at once: a source that has nothing yet should
+        wait inside its own call (the asyncio task of ``start`` waits for an event instead)."""
         ended = []
         for chunk in self._loop(poll):
             if chunk is not Engine.IDLE:

@@ -195,7 +195,9 @@ class Scheduler:
         first portion alone, and under a tight pool the last admitted ones are preempted again and
         again (measured at Qwen2.5-0.5B sizes, 1,024 requests: 454 preemptions and 223 k recomputed
         tokens against 45 and 22 k with a headroom of one page, output tokens a second +3 %).
-        With nothing running a request is always admitted: whether it fits at all shows when it runs."""
+        With nothing running a request is always admitted: whether it fits at all shows when it runs.
+        (Every group is asked for the pages of all the tokens, a windowed one too, which will hold
+        fewer at a time: the rule errs on the side of waiting.)"""
         if self.admission_headroom is None or not self.running:
             return True
         pages = -(-request.num_tokens // self.cache.page_size)
