@@ -21,6 +21,7 @@ import functools
 import os
 
 ROWS = 64
+MIN_KEYS_A_SPLIT = 192  # as MIN_TILES_A_SPLIT x 64 keys in csrc/attention_mma.cu
 # TORCHLET_B200_ATTENTION_BESIDE=0: in a mixed step the decode attention waits for the prompt
 # portions' kernel to end before it starts (for measurements)
 SIDE_BY_SIDE = os.environ.get("TORCHLET_B200_ATTENTION_BESIDE", "1") != "0"
@@ -34,7 +35,8 @@ def _sm_count(device_index: int) -> int:
 def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int, device=None) -> int:
     """CTAs the grid of a decode step holds for the keys of one (request, KV head): as many as
     fill ONE wave (three CTAs are resident per SM), at most 64, and no more than the longest
-    request the step may meet could use at 128 keys a split.  ``max_kv_len`` is that longest
+    request the step may meet could use at 192 keys a split (three of the kernel's key tiles; 128
+    and 256 were measured: 192 is 0.4-0.9 % of a decode step better at batch 1 to 4).  ``max_kv_len`` is that longest
     length: the step's own longest request, or, where the step is captured in a CUDA graph, the
     engine's length limit.  How many of them a request really uses is decided on the device from
     its own length (csrc/attention_mma.cu, ``effective_splits``), so a grid sized for the limit
@@ -42,7 +44,7 @@ def decode_splits(num_requests: int, num_kv_heads: int, max_kv_len: int, device=
     index = torch.cuda.current_device() if device is None or device.index is None else device.index
     resident = 3 * _sm_count(index)
     room = max(1, resident // max(1, num_requests * num_kv_heads))
-    return max(1, min(room, -(-max_kv_len // 128), 64))
+    return max(1, min(room, -(-max_kv_len // MIN_KEYS_A_SPLIT), 64))
 
 
 def prompt_splits(ctas: int, max_kv_len: int, device=None) -> int:
